@@ -1,0 +1,292 @@
+// Routed experts: top-k routing, the plan that sorts (token, slot) pairs by expert, and the plain
+// SIMT grouped products.  Nothing here reads a size back to the host: grids are sized for the worst
+// case and blocks past the planned tile count return.
+//
+//   scores = sigmoid(logits); choice = scores + bias (selection only); top-k by (choice desc, expert
+//   asc); w = scores[idx]; w /= sum(w) + 1e-20 if renorm and k > 1; w *= scale
+//   (src/quanta/minimax/moe.py:36-56).
+//   expert e on row x: down_e( silu(gate_e x) * up_e x ), times w, summed over the k slots in slot
+//   order by the next norm kernel (src/quanta/minimax/moe.py:59-88).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// routing: one warp per token
+// ---------------------------------------------------------------------------------------------
+template <int NPL>   // experts per lane, E <= 32*NPL
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                   int* __restrict__ idx_out, float* __restrict__ w_out, int T, int E,
+                                   int k, int renorm, float scale) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float* lg = logits + (size_t)t * E;
+  float choice[NPL];
+  unsigned taken = 0u;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    if (e < E) {
+      const float s = 1.f / (1.f + expf(-lg[e]));
+      choice[i] = bias ? s + bias[e] : s;
+    } else {
+      choice[i] = -INFINITY;
+      taken |= 1u << i;
+    }
+  }
+  float sum = 0.f;
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      // i ascending is expert index ascending within the lane: the first maximum wins a tie
+      if (!((taken >> i) & 1u) && (bi == 0x7fffffff || choice[i] > bv)) {
+        bv = choice[i];
+        bi = lane + 32 * i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
+      if (take) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    const float sc = 1.f / (1.f + expf(-lg[bi]));
+    sum += sc;
+    if (lane == 0) {
+      idx_out[(size_t)t * k + r] = bi;
+      w_out[(size_t)t * k + r] = sc;
+    }
+  }
+  __syncwarp();
+  const float denom = (renorm && k > 1) ? sum + 1e-20f : 1.f;
+  for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = w_out[(size_t)t * k + r] / denom * scale;
+}
+
+extern "C" int qb_router_topk(const float* logits, const float* bias, int* idx_out, float* w_out, int T,
+                              int E, int k, int renorm, float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (k <= 0 || k > E) return QB_ERR_BAD_ARG;
+  if (E > 1024) return QB_ERR_UNSUPPORTED;
+  const int warps = 4, blocks = (T + warps - 1) / warps;
+#define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, bias, idx_out, w_out, T, E, k, renorm, scale)
+  if (E <= 32) QB_ROUTE(1);
+  else if (E <= 64) QB_ROUTE(2);
+  else if (E <= 128) QB_ROUTE(4);
+  else if (E <= 256) QB_ROUTE(8);
+  else if (E <= 512) QB_ROUTE(16);
+  else QB_ROUTE(32);
+#undef QB_ROUTE
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// plan: counts per expert -> offsets, tile list, pairs sorted by expert
+//   plan layout (int32): counts[E] | cursor[E] | offsets[E+1] | num_tiles[1] | pad
+// ---------------------------------------------------------------------------------------------
+__global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ counts,
+                                 int* status) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    const int e = idx[i];
+    if (e < 0 || e >= E) { qb_set_status(status, QB_STATUS_BAD_EXPERT, e, 4); continue; }
+    atomicAdd(&counts[e], 1);
+  }
+}
+
+// one block of 1024 threads; thread e owns expert e
+__global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict__ offsets,
+                                int* __restrict__ num_tiles, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int E, int BM, int max_tiles) {
+  __shared__ int s_cnt[1024];
+  __shared__ int s_til[1024];
+  const int e = threadIdx.x;
+  const int c = e < E ? counts[e] : 0;
+  const int nt = (c + BM - 1) / BM;
+  s_cnt[e] = c;
+  s_til[e] = nt;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    int a = 0, b = 0;
+    if (e >= o) { a = s_cnt[e - o]; b = s_til[e - o]; }
+    __syncthreads();
+    s_cnt[e] += a;
+    s_til[e] += b;
+    __syncthreads();
+  }
+  const int off = s_cnt[e] - c, toff = s_til[e] - nt;     // exclusive prefixes
+  if (e < E) offsets[e] = off;
+  if (e == E - 1) { offsets[E] = s_cnt[e]; *num_tiles = min(s_til[e], max_tiles); }
+  for (int i = 0; i < nt; ++i) {
+    if (toff + i < max_tiles) {
+      tile_expert[toff + i] = e;
+      tile_row0[toff + i] = off + i * BM;
+    }
+  }
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ idx, int n_pairs, int E,
+                                   const int* __restrict__ offsets, int* __restrict__ cursor,
+                                   int* __restrict__ sorted_pair) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    const int e = idx[i];
+    if (e < 0 || e >= E) continue;
+    const int p = offsets[e] + atomicAdd(&cursor[e], 1);
+    sorted_pair[p] = i;
+  }
+}
+
+extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan, int* sorted_pair,
+                           int* tile_expert, int* tile_row0, int max_tiles, int* status,
+                           cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (E > 1024) return QB_ERR_UNSUPPORTED;
+  int* counts = plan;
+  int* cursor = plan + E;
+  int* offsets = plan + 2 * E;
+  int* num_tiles = plan + 3 * E + 1;
+  cudaError_t err = cudaMemsetAsync(plan, 0, sizeof(int) * (size_t)(3 * E + 2), stream);
+  if (err != cudaSuccess) return (int)err;
+  const int blocks = min((n_pairs + 255) / 256, 1024);
+  moe_count_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, counts, status);
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, offsets, num_tiles, tile_expert, tile_row0, E, BM, max_tiles);
+  moe_scatter_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, offsets, cursor, sorted_pair);
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// grouped products, SIMT.  Tile = 32 sorted rows of one expert x 64 output features, k slices of 16.
+//   MODE 1: act[p, j]   = silu(x[tok(p)] . W13[e][j]) * (x[tok(p)] . W13[e][I + j]),  j < I
+//   MODE 2: y[pair(p), n] = w[pair(p)] * (act[p] . W2[e][n]),  n < H
+// Each output is one sequential float32 sum over the inner dimension.
+// ---------------------------------------------------------------------------------------------
+constexpr int MG_BM = 32, MG_BN = 64, MG_BK = 16;
+
+template <typename X, typename W, typename O, int MODE>
+__global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __restrict__ weights,
+                                        O* __restrict__ out, const int* __restrict__ sorted_pair,
+                                        const float* __restrict__ pair_w, const int* __restrict__ plan,
+                                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                                        int E, int top_k, int K, int N) {
+  // MODE 1: K = hidden, N = I (weights [E, 2N, K]); MODE 2: K = I, N = hidden (weights [E, N, K])
+  const int* offsets = plan + 2 * E;
+  const int num_tiles = plan[3 * E + 1];
+  const int tile = blockIdx.y;
+  if (tile >= num_tiles) return;
+  const int e = tile_expert[tile];
+  const int row0 = tile_row0[tile];
+  const int row_end = offsets[e + 1];
+  const int n0 = blockIdx.x * MG_BN;
+  __shared__ float Xs[MG_BK][MG_BM + 1];
+  __shared__ float Ws[MODE == 1 ? 2 : 1][MG_BK][MG_BN + 4];
+  __shared__ int src_row[MG_BM];
+  const int tid = threadIdx.x;
+  if (tid < MG_BM) {
+    const int p = row0 + tid;
+    int r = -1;
+    if (p < row_end) r = (MODE == 1) ? sorted_pair[p] / top_k : p;
+    src_row[tid] = r;
+  }
+  __syncthreads();
+  const W* wbase = weights + (size_t)e * (MODE == 1 ? 2 : 1) * N * K;
+  const int tx = tid % 16, ty = tid / 16;   // rows ty*2.., cols tx*4..
+  float acc[MODE == 1 ? 2 : 1][2][4];
+#pragma unroll
+  for (int a = 0; a < (MODE == 1 ? 2 : 1); ++a)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[a][i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += MG_BK) {
+    // X tile: 32 x 16 = 512 elements, 2 per thread
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int id = tid + q * 256;
+      const int r = id / MG_BK, kk = id % MG_BK;
+      const int sr = src_row[r];
+      Xs[kk][r] = (sr >= 0 && k0 + kk < K) ? qb_to_float<X>(x[(size_t)sr * K + k0 + kk]) : 0.f;
+    }
+    // W tile(s): 64 x 16 = 1024 elements, 4 per thread
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int id = tid + q * 256;
+      const int r = id / MG_BK, kk = id % MG_BK;
+      const int gn = n0 + r;
+      const bool ok = gn < N && k0 + kk < K;
+      Ws[0][kk][r] = ok ? qb_to_float<W>(wbase[(size_t)gn * K + k0 + kk]) : 0.f;
+      if (MODE == 1) Ws[MODE == 1 ? 1 : 0][kk][r] = ok ? qb_to_float<W>(wbase[(size_t)(N + gn) * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MG_BK; ++kk) {
+      float a[2], b[4];
+      a[0] = Xs[kk][ty * 2];
+      a[1] = Xs[kk][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[0][kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[0][i][j] = fmaf(a[i], b[j], acc[0][i][j]);
+      if (MODE == 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Ws[MODE == 1 ? 1 : 0][kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[MODE == 1 ? 1 : 0][i][j] = fmaf(a[i], b[j], acc[MODE == 1 ? 1 : 0][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int p = row0 + ty * 2 + i;
+    if (p >= row_end) continue;
+    if (MODE == 1) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gn = n0 + tx * 4 + j;
+        if (gn >= N) continue;
+        const float g = acc[0][i][j], u = acc[MODE == 1 ? 1 : 0][i][j];
+        out[(size_t)p * N + gn] = qb_from_float<O>(g / (1.f + expf(-g)) * u);
+      }
+    } else {
+      const int pair = sorted_pair[p];
+      const float w = pair_w[pair];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gn = n0 + tx * 4 + j;
+        if (gn < N) out[(size_t)pair * N + gn] = qb_from_float<O>(w * acc[0][i][j]);
+      }
+    }
+  }
+}
+
+// x: [T, H] activations (MODE 1) or [pairs, I] act rows (MODE 2).
+extern "C" int qb_moe_grouped_simt(int mode, const void* x, int x_dtype, const void* weights, int w_dtype,
+                                   void* out, int out_dtype, const int* sorted_pair, const float* pair_w,
+                                   const int* plan, const int* tile_expert, const int* tile_row0,
+                                   int max_tiles, int E, int top_k, int K, int N, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (max_tiles > 65535) return QB_ERR_UNSUPPORTED;
+  dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+  QB_DISPATCH_DTYPE(x_dtype, X, QB_DISPATCH_DTYPE(w_dtype, W, QB_DISPATCH_DTYPE(out_dtype, O, {
+    if (mode == 1)
+      moe_grouped_simt_kernel<X, W, O, 1><<<grid, 256, 0, stream>>>(
+          (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
+          top_k, K, N);
+    else if (mode == 2)
+      moe_grouped_simt_kernel<X, W, O, 2><<<grid, 256, 0, stream>>>(
+          (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
+          top_k, K, N);
+    else
+      return QB_ERR_BAD_ARG;
+  })));
+  QB_LAUNCH_CHECK();
+  return 0;
+}

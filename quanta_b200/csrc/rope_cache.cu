@@ -1,0 +1,126 @@
+// q/k RMSNorm + partial rotary position encoding + write of K and V into the paged cache, one kernel.
+//
+// Input is the fused projection row [q | k | v] of every token of the step.  For each token:
+//   q, k  <- RMSNorm (none | over all heads of the row | per head), float32
+//            (src/quanta/minimax/model_m3.py:15-17 / src/quanta/minimax/attention.py:172-182)
+//   q, k  <- rotate-half on the first `rd` dims of each head, pair j using position axis
+//            pair_axis[j] and angle float(pos) * inv_freq[j]  (src/quanta/minimax/model_m3.py:83-96)
+//   q     -> q_out [T, nq, hd];  k, v -> cache pages [page, kv_head, slot, hd] through the block table
+// One rounding to the activation dtype, at the store.  One block per token.
+#include "common.cuh"
+
+#define NORM_NONE 0
+#define NORM_PER_LAYER 1
+#define NORM_PER_HEAD 2
+
+template <typename A>
+__global__ void qknorm_rope_write_kernel(
+    const A* __restrict__ qkv, A* __restrict__ q_out, A* __restrict__ k_cache, A* __restrict__ v_cache,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, int norm_kind, float eps,
+    const float* __restrict__ inv_freq, const int* __restrict__ pair_axis,
+    const int* __restrict__ positions, int n_axes, const int* __restrict__ tok_pos,
+    const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int T, int nq,
+    int nkv, int hd, int rd, int page_size, int num_pages, int* status) {
+  extern __shared__ float smem[];
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  const int qn = nq * hd, kn = nkv * hd;
+  float* buf = smem;                 // [qn + kn]  q then k
+  float* cs = buf + qn + kn;         // [rd/2] cos, [rd/2] sin
+  float* scratch = cs + rd;          // 32 + (nq + nkv) head statistics
+  float* head_r = scratch + 32;
+  const A* row = qkv + (size_t)t * (qn + 2 * kn);
+  const int half = rd / 2;
+
+  for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) buf[i] = qb_to_float<A>(row[i]);
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    const int ax = pair_axis ? pair_axis[j] : 0;
+    const float ang = (float)positions[(size_t)t * n_axes + ax] * inv_freq[j];
+    float s, c;
+    sincosf(ang, &s, &c);
+    cs[j] = c;
+    cs[half + j] = s;
+  }
+  __syncthreads();
+
+  if (norm_kind == NORM_PER_LAYER) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) sq += buf[i] * buf[i];
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) sk += buf[qn + i] * buf[qn + i];
+    const float tq = qb_block_sum(sq, scratch);
+    const float tk = qb_block_sum(sk, scratch);
+    const float rq = rsqrtf(tq / (float)qn + eps), rk = rsqrtf(tk / (float)kn + eps);
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) buf[i] = q_norm_w[i] * (buf[i] * rq);
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) buf[qn + i] = k_norm_w[i] * (buf[qn + i] * rk);
+    __syncthreads();
+  } else if (norm_kind == NORM_PER_HEAD) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < nq + nkv; h += nwarps) {
+      float s = 0.f;
+      for (int d = lane; d < hd; d += 32) s += buf[h * hd + d] * buf[h * hd + d];
+      s = qb_warp_sum(s);
+      if (lane == 0) head_r[h] = rsqrtf(s / (float)hd + eps);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) {
+      const int h = i / hd, d = i % hd;
+      const float w = h < nq ? q_norm_w[d] : k_norm_w[d];
+      buf[i] = w * (buf[i] * head_r[h]);
+    }
+    __syncthreads();
+  }
+
+  // rotation: each (head, pair) is owned by one thread
+  for (int i = threadIdx.x; i < (nq + nkv) * half; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    const float a = buf[h * hd + j], b = buf[h * hd + half + j];
+    const float c = cs[j], s = cs[half + j];
+    buf[h * hd + j] = a * c - b * s;
+    buf[h * hd + half + j] = b * c + a * s;
+  }
+  __syncthreads();
+
+  A* qo = q_out + (size_t)t * qn;
+  for (int i = threadIdx.x; i < qn; i += blockDim.x) qo[i] = qb_from_float<A>(buf[i]);
+
+  if (k_cache == nullptr) return;
+  const int pos = tok_pos[t];
+  const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 2);
+    return;
+  }
+  const int slot = pos % page_size;
+  const A* vrow = row + qn + kn;
+  for (int i = threadIdx.x; i < kn; i += blockDim.x) {
+    const int h = i / hd, d = i % hd;
+    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
+    k_cache[dst] = qb_from_float<A>(buf[qn + i]);
+    v_cache[dst] = vrow[i];
+  }
+}
+
+extern "C" int qb_qknorm_rope_write(
+    const void* qkv, int dtype, void* q_out, void* k_cache, void* v_cache, const float* q_norm_w,
+    const float* k_norm_w, int norm_kind, float eps, const float* inv_freq, const int* pair_axis,
+    const int* positions, int n_axes, const int* tok_pos, const int* tok_req, const int* block_table,
+    int bt_stride, int T, int nq, int nkv, int hd, int rd, int page_size, int num_pages, int* status,
+    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0) return QB_ERR_BAD_ARG;
+  if (norm_kind != NORM_NONE && (q_norm_w == nullptr || k_norm_w == nullptr)) return QB_ERR_BAD_ARG;
+  const size_t smem = (size_t)((nq + nkv) * hd + rd + 32 + nq + nkv) * sizeof(float);
+  if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
+  QB_DISPATCH_DTYPE(dtype, A, {
+    auto kern = qknorm_rope_write_kernel<A>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<T, 256, smem, stream>>>((const A*)qkv, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w, k_norm_w,
+                                   norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos, tok_req,
+                                   block_table, bt_stride, T, nq, nkv, hd, rd, page_size, num_pages, status);
+  });
+  QB_LAUNCH_CHECK();
+  return 0;
+}

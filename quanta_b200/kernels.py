@@ -1,0 +1,233 @@
+"""Python face of the CUDA kernels: argument checks, pointers, launch on torch's current stream.
+
+Every function here launches hand-written sm_100a code from ``csrc``; there is no CPU or library
+fallback, and a missing or unbuildable extension raises at the first call.  Tensors must be CUDA,
+contiguous and of the stated dtype; a violated precondition is a ``ValueError`` before anything is
+launched.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+NORM_NONE, NORM_PER_LAYER, NORM_PER_HEAD = 0, 1, 2
+
+_STATUS_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool (block table)",
+                3: "expert id outside the expert table", 4: "a bounded device wait ran out"}
+_KERNEL_TEXT = {1: "embedding", 2: "rope/cache write", 3: "paged attention", 4: "expert plan",
+                5: "expert product", 6: "decode attention", 7: "prefill attention"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    return _build.load()
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise ValueError(f"dtype {t.dtype} is not float32 or bfloat16") from None
+
+
+def _p(t: torch.Tensor | None):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise ValueError("kernel arguments must be CUDA tensors")
+    if not t.is_contiguous():
+        raise ValueError("kernel arguments must be contiguous")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc == -1:
+        raise ValueError(f"{what}: bad argument")
+    if rc == -2:
+        raise ValueError(f"{what}: a size outside what the kernel supports")
+    raise KernelError(f"{what}: CUDA error {rc}")
+
+
+def _want(t: torch.Tensor, dtype, name: str) -> None:
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def new_status(device) -> torch.Tensor:
+    """Status words the kernels write when they meet an index they cannot honour."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def raise_on_status(status_host) -> None:
+    code = int(status_host[0])
+    if code:
+        raise KernelError(f"device reported: {_STATUS_TEXT.get(code, code)} (value {int(status_host[1])}) in "
+                          f"{_KERNEL_TEXT.get(int(status_host[2]), 'kernel ' + str(int(status_host[2])))}")
+
+
+# ------------------------------------------------------------------------------------------------
+def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
+    _want(h, torch.float32, "h"); _want(ids, torch.int32, "ids")
+    T, H = h.shape
+    V = table.shape[0]
+    if table.shape[1] != H or ids.numel() != T:
+        raise ValueError("embedding: shape mismatch")
+    _check(lib().qb_embedding(_p(h), _p(table), _code(table), _p(ids), T, H, V, _p(status), _stream()),
+           "embedding")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor | None, rows: torch.Tensor | None = None, store_h: bool = True) -> None:
+    """``h += sum_s delta[:, s]`` (float32) and ``out = weight * h * rsqrt(mean(h^2) + eps)``.
+
+    ``delta`` is ``[T, H]`` or ``[T, S, H]`` or None; ``rows`` (int32) selects token rows, in which case
+    ``out`` has one row per entry.  ``out`` None only folds the delta into ``h``."""
+    _want(h, torch.float32, "h"); _want(weight, torch.float32, "weight")
+    T, H = h.shape
+    S = 1
+    if delta is not None:
+        if delta.dim() == 3:
+            S = delta.shape[1]
+        if delta.shape[0] != T or delta.shape[-1] != H:
+            raise ValueError("add_rmsnorm: delta shape mismatch")
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    if out is not None and (out.shape[0] != n or out.shape[1] != H):
+        raise ValueError("add_rmsnorm: out shape mismatch")
+    if weight.numel() != H:
+        raise ValueError("add_rmsnorm: weight shape mismatch")
+    _check(lib().qb_add_rmsnorm(_p(h), _p(delta), _code(delta) if delta is not None else F32, S, _p(weight),
+                                _p(out), _code(out) if out is not None else F32, _p(rows), n, H,
+                                ctypes.c_float(eps), int(store_h), _stream()), "add_rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    n, two_i = gate_up.shape
+    if out.shape != (n, two_i // 2) or out.dtype != gate_up.dtype:
+        raise ValueError("silu_mul: shape/dtype mismatch")
+    _check(lib().qb_silu_mul(_p(gate_up), _p(out), _code(out), n, two_i // 2, _stream()), "silu_mul")
+
+
+def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kind: int, eps: float,
+                      inv_freq, pair_axis, positions, tok_pos, tok_req, block_table, nq: int, nkv: int,
+                      hd: int, rd: int, page_size: int, status) -> None:
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+        raise ValueError("qknorm_rope_write: qkv width mismatch")
+    if q_out.dtype != qkv.dtype or q_out.numel() != T * nq * hd:
+        raise ValueError("qknorm_rope_write: q_out mismatch")
+    num_pages = 0
+    if k_cache is not None:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise ValueError("qknorm_rope_write: cache dtype differs from activations")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
+            raise ValueError("qknorm_rope_write: cache shape mismatch")
+        num_pages = k_cache.shape[0]
+    _want(inv_freq, torch.float32, "inv_freq")
+    if inv_freq.numel() != rd // 2:
+        raise ValueError("qknorm_rope_write: inv_freq length")
+    n_axes = 1 if positions.dim() == 1 else positions.shape[1]
+    for t, n in ((positions, "positions"), (tok_pos, "tok_pos"), (tok_req, "tok_req"), (block_table, "block_table")):
+        _want(t, torch.int32, n)
+    if pair_axis is not None:
+        _want(pair_axis, torch.int32, "pair_axis")
+    if norm_kind != NORM_NONE:
+        want = (nq * hd, nkv * hd) if norm_kind == NORM_PER_LAYER else (hd, hd)
+        if q_norm_w.numel() != want[0] or k_norm_w.numel() != want[1]:
+            raise ValueError("qknorm_rope_write: norm weight length does not fit the norm kind")
+    _check(lib().qb_qknorm_rope_write(
+        _p(qkv), _code(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_kind,
+        ctypes.c_float(eps), _p(inv_freq), _p(pair_axis), _p(positions), n_axes, _p(tok_pos), _p(tok_req),
+        _p(block_table), block_table.shape[1], T, nq, nkv, hd, rd, page_size, num_pages, _p(status),
+        _stream()), "qknorm_rope_write")
+
+
+def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float,
+                         window: int, status) -> None:
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    if hd2 != hd or out.shape != q.shape or out.dtype != q.dtype or k_cache.dtype != q.dtype:
+        raise ValueError("paged_attention: shape/dtype mismatch")
+    _check(lib().qb_paged_attention_simt(
+        _p(q), _code(q), _p(k_cache), _p(v_cache), _p(out), _p(tok_pos), _p(tok_req), _p(block_table),
+        block_table.shape[1], T, nq, nkv, hd, page_size, num_pages, ctypes.c_float(scale), int(window),
+        _p(status), _stream()), "paged_attention_simt")
+
+
+def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M,N] = a[M,K] @ b[N,K].T`` in float32 on the CUDA cores, fixed summation order."""
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K or out.shape != (M, N):
+        raise ValueError("gemm_nt_simt: shape mismatch")
+    _check(lib().qb_gemm_nt_simt(_p(a), _code(a), _p(b), _code(b), _p(out), _code(out), M, N, K, K, K, N,
+                                 _stream()), "gemm_nt_simt")
+
+
+def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> None:
+    _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
+    T, E = logits.shape
+    k = idx_out.shape[1]
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+    _check(lib().qb_router_topk(_p(logits), _p(bias), _p(idx_out), _p(w_out), T, E, k, int(renorm),
+                                ctypes.c_float(scale), _stream()), "router_topk")
+
+
+MOE_SIMT_BM = 32
+
+
+def moe_plan_sizes(n_pairs: int, n_experts: int, bm: int) -> tuple[int, int]:
+    """(plan words, max tiles) for ``n_pairs`` (token, slot) pairs."""
+    return 3 * n_experts + 4, (n_pairs + bm - 1) // bm + min(n_experts, n_pairs)
+
+
+def moe_plan(idx, n_experts: int, bm: int, plan, sorted_pair, tile_expert, tile_row0, status) -> None:
+    n_pairs = idx.numel()
+    max_tiles = tile_expert.numel()
+    _check(lib().qb_moe_plan(_p(idx), n_pairs, n_experts, bm, _p(plan), _p(sorted_pair), _p(tile_expert),
+                             _p(tile_row0), max_tiles, _p(status), _stream()), "moe_plan")
+
+
+def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
+                     n_experts: int, top_k: int) -> None:
+    """mode 1: ``out[p, :I] = silu(x[tok] W13_e[:I]^T) * (x[tok] W13_e[I:]^T)``; mode 2:
+    ``out[pair] = w[pair] * (x[p] W2_e^T)``; rows p sorted by expert (see ``moe_plan``)."""
+    K = x.shape[1]
+    N = out.shape[1]
+    want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
+    if tuple(weights.shape) != want:
+        raise ValueError(f"moe_grouped: weights {tuple(weights.shape)} != {want}")
+    _check(lib().qb_moe_grouped_simt(mode, _p(x), _code(x), _p(weights), _code(weights), _p(out), _code(out),
+                                     _p(sorted_pair), _p(pair_w), _p(plan), _p(tile_expert), _p(tile_row0),
+                                     tile_expert.numel(), n_experts, top_k, K, N, _stream()), "moe_grouped_simt")
+
+
+def sample_rows(logits, fparams, iparams, out) -> None:
+    _want(logits, torch.float32, "logits"); _want(fparams, torch.float32, "fparams")
+    _want(iparams, torch.int32, "iparams"); _want(out, torch.int32, "out")
+    n, V = logits.shape
+    _check(lib().qb_sample_rows(_p(logits), n, V, _p(fparams), _p(iparams), _p(out), _stream()), "sample_rows")
+
+
+def apply_penalties(logits, prev, prev_off, pparams) -> None:
+    _want(logits, torch.float32, "logits")
+    n, V = logits.shape
+    _check(lib().qb_apply_penalties(_p(logits), n, V, _p(prev), _p(prev_off), _p(pparams), _stream()),
+           "apply_penalties")

@@ -1,0 +1,89 @@
+"""Grouped-query softmax attention over the paged cache.
+
+Formula, in order (src/quanta/minimax/attention.py:166-204): q/k/v projections without bias; q/k
+RMSNorm before the rotation, either over the concatenated heads (``"per_layer"``, weight
+``[heads*head_dim]``) or per head (``"per_head"``, weight ``[head_dim]``); rotation of the first
+``rotary_dim`` dims by the position encoding part; K (rotated) and V appended to the cache; scores
+``q.k * scale`` over the keys at positions <= the query's (and inside the window, if any), softmax in
+float32, ``P V``; output projection.  q head ``h`` reads kv head ``h // (n_q / n_kv)``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..matmul import linear
+from .base import KVCacheSpec, Mixer, TensorSpec, make, register
+
+_NORM_KIND = {None: kernels.NORM_NONE, "per_layer": kernels.NORM_PER_LAYER, "per_head": kernels.NORM_PER_HEAD}
+
+
+@register("mixer", "gqa_attention")
+class GQAttention(Mixer):
+    def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                 position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None):
+        if n_q_heads % n_kv_heads:
+            raise ValueError(f"{n_q_heads} q heads are not a multiple of {n_kv_heads} kv heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        if qk_norm not in _NORM_KIND:
+            raise ValueError(f"qk_norm {qk_norm!r} is not None, 'per_layer' or 'per_head'")
+        self.hidden, self.nq, self.nkv, self.hd = int(hidden_size), int(n_q_heads), int(n_kv_heads), int(head_dim)
+        self.scale, self.qk_norm, self.eps = float(scale), qk_norm, float(qk_norm_eps)
+        self.window = window
+        self.position = make("position", position) if isinstance(position, tuple) else position
+        self.names = dict(names)      # q, k, v, o, and q_norm, k_norm when normed
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    def children(self):
+        return [self.position]
+
+    def tensor_specs(self):
+        n, H, hd = self.names, self.hidden, self.hd
+        specs = [TensorSpec(n["q"], (self.nq * hd, H)), TensorSpec(n["k"], (self.nkv * hd, H)),
+                 TensorSpec(n["v"], (self.nkv * hd, H)), TensorSpec(n["o"], (H, self.nq * hd))]
+        if self.qk_norm == "per_layer":
+            specs += [TensorSpec(n["q_norm"], (self.nq * hd,), "f32", "gain"),
+                      TensorSpec(n["k_norm"], (self.nkv * hd,), "f32", "gain")]
+        elif self.qk_norm == "per_head":
+            specs += [TensorSpec(n["q_norm"], (hd,), "f32", "gain"), TensorSpec(n["k_norm"], (hd,), "f32", "gain")]
+        return specs
+
+    def load(self, fetch):
+        n = self.names
+        q = fetch(n["q"])
+        self.w_qkv = torch.empty(((self.nq + 2 * self.nkv) * self.hd, self.hidden), dtype=q.dtype, device=q.device)
+        a, b = self.nq * self.hd, (self.nq + self.nkv) * self.hd
+        self.w_qkv[:a].copy_(q)
+        del q
+        self.w_qkv[a:b].copy_(fetch(n["k"]))
+        self.w_qkv[b:].copy_(fetch(n["v"]))
+        self.w_o = fetch(n["o"])
+        if self.qk_norm is not None:
+            self.q_norm_w, self.k_norm_w = fetch(n["q_norm"]), fetch(n["k_norm"])
+
+    def cache_spec(self):
+        return KVCacheSpec(self.nkv, self.hd, self.window)
+
+    def forward(self, x, ctx, cache, state):
+        T = x.shape[0]
+        qkv = linear(x, self.w_qkv)
+        q = torch.empty((T, self.nq, self.hd), dtype=x.dtype, device=x.device)
+        tables = self.position.rotary_tables(x.device)
+        if tables is None:
+            inv_freq = torch.empty(0, dtype=torch.float32, device=x.device)
+            pair_axis, rd = None, 0
+        else:
+            inv_freq, pair_axis, rd, _ = tables
+        kernels.qknorm_rope_write(
+            qkv, q, cache.k if cache.write else None, cache.v if cache.write else None, self.q_norm_w,
+            self.k_norm_w, _NORM_KIND[self.qk_norm], self.eps, inv_freq, pair_axis, ctx.positions, ctx.tok_pos,
+            ctx.tok_req, cache.block_table, self.nq, self.nkv, self.hd, rd, cache.page_size, ctx.status)
+        out = torch.empty_like(q)
+        self.attend(q, cache, out, ctx)
+        return linear(out.view(T, self.nq * self.hd), self.w_o)
+
+    def attend(self, q, cache, out, ctx):
+        kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
+                                     self.scale, self.window or 0, ctx.status)

@@ -1,0 +1,157 @@
+"""What a part is, and the registries parts are chosen from.
+
+A model is put together from parts of five kinds: ``mixer`` (attention here), ``feed_forward``
+(dense or routed experts), ``norm``, ``position`` (position encoding) and ``block`` (how a layer
+arranges the other four).  A part takes every size and constant as a constructor parameter, names
+the checkpoint tensors it needs (``tensor_specs``), receives them (``load``) and runs on the tokens
+of one step (``forward``).  No part knows which model it is in; an architecture is a function from
+its configuration to a ``ModelSpec`` that names parts and parameters layer by layer.
+
+Registering a new part: ``@register("mixer", "my_mixer") class MyMixer(Mixer): ...`` in any module
+that is imported before the model is built.  The framework's files do not change.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+_REGISTRY: dict[str, dict[str, type]] = {k: {} for k in KINDS}
+
+
+def register(kind: str, name: str) -> Callable[[type], type]:
+    if kind not in _REGISTRY:
+        raise KeyError(f"unknown part kind {kind!r}; kinds: {KINDS}")
+
+    def deco(cls: type) -> type:
+        _REGISTRY[kind][name] = cls
+        return cls
+
+    return deco
+
+
+def registered(kind: str) -> list[str]:
+    return sorted(_REGISTRY[kind])
+
+
+def make(kind: str, choice) -> Any:
+    """Instantiate ``(name, params)`` of the given kind."""
+    name, params = choice
+    try:
+        cls = _REGISTRY[kind][name]
+    except KeyError:
+        raise KeyError(f"no {kind} part named {name!r}; registered: {registered(kind)}") from None
+    return cls(**params)
+
+
+# ------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class TensorSpec:
+    """One checkpoint tensor a part needs.
+
+    ``kind``: ``"matrix"`` is held in the model's compute dtype (bfloat16 or float32); ``"f32"`` is
+    held in float32 whatever the compute dtype (norm gains, router gate and bias: a tensor stored in
+    32-bit stays so); ``"i32"`` integer tables.  ``init`` tells the random-weights mode how to draw
+    it: ``"normal"`` N(0, 0.02), ``"gain"`` 1 + U(-0.1, 0.1), ``"bias"`` U(-0.05, 0.05).
+    """
+    name: str
+    shape: tuple[int, ...]
+    kind: str = "matrix"
+    init: str = "normal"
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """A mixer's need of paged keys and values: layers with equal specs share pages and block tables."""
+    n_kv_heads: int
+    head_dim: int
+    window: int | None = None          # None: all keys are kept; W: only the last W positions
+
+
+@dataclass
+class LayerCache:
+    """What a mixer sees of the cache in one step: its own K/V pages and its group's block table."""
+    k: torch.Tensor                    # [num_pages, n_kv, page_size, head_dim]
+    v: torch.Tensor
+    page_size: int
+    block_table: torch.Tensor          # int32 [requests in the step, pages per request]
+    write: bool = True                 # False: this layer reads a cache another layer wrote
+
+
+@dataclass
+class StepContext:
+    """Per-step facts every part may read.  All tensors are on the device; ``T`` tokens in the step."""
+    n_tokens: int
+    positions: torch.Tensor            # int32 [T, axes]   position fed to the position encoding
+    tok_pos: torch.Tensor              # int32 [T]         index of the token in its request's cache
+    tok_req: torch.Tensor              # int32 [T]         row of the token's request in this step
+    req_slot: torch.Tensor             # int32 [R]         state slot of each request of the step
+    req_start: torch.Tensor            # int32 [R+1]       first token row of each request
+    req_len_after: torch.Tensor        # int32 [R]         tokens cached once the step is done
+    status: torch.Tensor               # int32 [4]         device error words
+    dtype: torch.dtype                 # activation dtype
+    max_new_tokens_per_req: int = 0    # largest portion in the step
+    max_len_after: int = 0             # largest req_len_after (host copy, for launch sizing)
+    host: dict = field(default_factory=dict)   # host copies of the small arrays, for parts that need them
+
+
+class Part:
+    """Base of every part."""
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def load(self, fetch: Callable[[str], torch.Tensor]) -> None:
+        """Receive the tensors named in ``tensor_specs``: ``fetch(name)`` returns the device tensor in
+        the dtype its kind asks for."""
+
+    def children(self) -> list["Part"]:
+        return []
+
+
+class Norm(Part):
+    def forward(self, h: torch.Tensor, delta, out, rows=None, store_h=True) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Turns positions into what a mixer consumes.  ``rotary_tables`` returns ``(inv_freq float32
+    [rd/2], pair_axis int32 [rd/2] or None, rotary_dim, n_axes)`` or None when nothing is rotated."""
+
+    n_axes = 1
+
+    def rotary_tables(self, device):
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self) -> KVCacheSpec | None:
+        return None
+
+    def state_spec(self) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
+        """Per-request state of fixed size: name -> (shape, dtype).  The cache manager keeps one row per
+        state slot, zeroed when a request takes the slot."""
+        return {}
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache | None,
+                state: dict[str, torch.Tensor]) -> torch.Tensor:
+        """``x`` [T, hidden] in the activation dtype -> the layer's contribution to the residual stream,
+        [T, hidden] or [T, S, hidden] (S partial results the next norm sums in order)."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of norm, mixer and feed-forward in one layer.  ``forward`` takes the residual stream
+    ``h`` (float32) and the not-yet-added contribution of the layer before, and returns the new pending
+    contribution; every addition to ``h`` happens inside a norm kernel."""
+
+    def forward(self, h, pending, ctx, cache, state):
+        raise NotImplementedError

@@ -1,0 +1,112 @@
+"""Feed-forward parts: sigmoid-routed SwiGLU experts, and a dense SwiGLU.
+
+Routed experts (src/quanta/minimax/moe.py:36-88): router logits in float32 from a float32 gate;
+``sigmoid`` scores; a correction bias added for the choice only; top-k (ties to the lower expert
+index); weights are the bias-free scores, renormalised (``+ 1e-20``) and scaled; each chosen expert is
+``down(silu(gate x) * up x)`` (``w1`` gate, ``w3`` up, ``w2`` down); the weight is applied after
+``down``; the k results are summed in float32 in slot order.  No shared expert.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..matmul import linear
+from .base import FeedForward, TensorSpec, register
+
+
+@register("feed_forward", "sigmoid_topk_experts")
+class SigmoidTopKExperts(FeedForward):
+    def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, use_bias: bool,
+                 renormalize: bool, scaling: float, names: dict):
+        if top_k > n_experts:
+            raise ValueError(f"top_k {top_k} > {n_experts} experts")
+        if n_experts > 1024:
+            raise ValueError(f"{n_experts} experts: the routing kernels take at most 1024")
+        self.H, self.I, self.E, self.k = int(hidden_size), int(expert_size), int(n_experts), int(top_k)
+        self.use_bias, self.renorm, self.scaling = bool(use_bias), bool(renormalize), float(scaling)
+        self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
+        self.gate_w = self.bias = self.w13 = self.w2 = None
+
+    def tensor_specs(self):
+        n = self.names
+        specs = [TensorSpec(n["gate"], (self.E, self.H), "f32", "normal")]
+        if self.use_bias:
+            specs.append(TensorSpec(n["bias"], (self.E,), "f32", "bias"))
+        for e in range(self.E):
+            specs += [TensorSpec(n["w1"].format(e=e), (self.I, self.H)),
+                      TensorSpec(n["w3"].format(e=e), (self.I, self.H)),
+                      TensorSpec(n["w2"].format(e=e), (self.H, self.I))]
+        return specs
+
+    def load(self, fetch):
+        n = self.names
+        self.gate_w = fetch(n["gate"])
+        self.bias = fetch(n["bias"]) if self.use_bias else None
+        first = fetch(n["w1"].format(e=0))
+        dt, dev = first.dtype, first.device
+        # gate rows then up rows of each expert, so one tile of the first product holds both
+        self.w13 = torch.empty((self.E, 2 * self.I, self.H), dtype=dt, device=dev)
+        self.w2 = torch.empty((self.E, self.H, self.I), dtype=dt, device=dev)
+        for e in range(self.E):
+            self.w13[e, : self.I].copy_(first if e == 0 else fetch(n["w1"].format(e=e)))
+            self.w13[e, self.I:].copy_(fetch(n["w3"].format(e=e)))
+            self.w2[e].copy_(fetch(n["w2"].format(e=e)))
+        del first
+
+    def route(self, x):
+        """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
+        T = x.shape[0]
+        logits = torch.empty((T, self.E), dtype=torch.float32, device=x.device)
+        kernels.gemm_nt_simt(x, self.gate_w, logits)
+        idx = torch.empty((T, self.k), dtype=torch.int32, device=x.device)
+        w = torch.empty((T, self.k), dtype=torch.float32, device=x.device)
+        kernels.router_topk(logits, self.bias, idx, w, self.renorm, self.scaling)
+        return idx, w
+
+    def forward(self, x, ctx):
+        T, dev = x.shape[0], x.device
+        idx, w = self.route(x)
+        n_pairs = T * self.k
+        bm = kernels.MOE_SIMT_BM
+        plan_words, max_tiles = kernels.moe_plan_sizes(n_pairs, self.E, bm)
+        ints = torch.empty(plan_words + n_pairs + 2 * max_tiles, dtype=torch.int32, device=dev)
+        plan = ints[:plan_words]
+        sorted_pair = ints[plan_words: plan_words + n_pairs]
+        tile_expert = ints[plan_words + n_pairs: plan_words + n_pairs + max_tiles]
+        tile_row0 = ints[plan_words + n_pairs + max_tiles:]
+        kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+        act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
+        kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
+        y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
+        kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
+                                 tile_expert, tile_row0, self.E, self.k)
+        return y
+
+
+@register("feed_forward", "swiglu_dense")
+class SwiGLUDense(FeedForward):
+    """``down(silu(gate x) * up x)`` with library products and a fused activation kernel."""
+
+    def __init__(self, hidden_size: int, inner_size: int, names: dict):
+        self.H, self.I, self.names = int(hidden_size), int(inner_size), dict(names)
+        self.w_gu = self.w_down = None
+
+    def tensor_specs(self):
+        n = self.names
+        return [TensorSpec(n["gate"], (self.I, self.H)), TensorSpec(n["up"], (self.I, self.H)),
+                TensorSpec(n["down"], (self.H, self.I))]
+
+    def load(self, fetch):
+        g = fetch(self.names["gate"])
+        self.w_gu = torch.empty((2 * self.I, self.H), dtype=g.dtype, device=g.device)
+        self.w_gu[: self.I].copy_(g)
+        self.w_gu[self.I:].copy_(fetch(self.names["up"]))
+        self.w_down = fetch(self.names["down"])
+
+    def forward(self, x, ctx):
+        gu = linear(x, self.w_gu)
+        act = torch.empty((x.shape[0], self.I), dtype=x.dtype, device=x.device)
+        kernels.silu_mul(gu, act)
+        return linear(act, self.w_down)
