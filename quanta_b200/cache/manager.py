@@ -157,9 +157,10 @@ class CacheManager:
         return max(0, length - g.window + 1) // self.page_size
 
     def pages_needed(self, rid, new_length: int) -> list[int]:
-        """New pages each group must get so that positions ``[0, new_length)`` can be written."""
+        """New pages each group must get so that positions ``[0, new_length)`` can be written (a
+        request the manager does not know yet holds none)."""
         want_pages = -(-new_length // self.page_size)
-        return [max(0, want_pages - len(g.tables[rid])) for g in self.groups]
+        return [max(0, want_pages - len(g.tables.get(rid, ()))) for g in self.groups]
 
     def can_reserve(self, wants: dict) -> bool:
         """``wants``: request id -> new length.  True if every group can serve all of them together."""

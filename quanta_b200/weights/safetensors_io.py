@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 
 import torch
@@ -62,7 +63,9 @@ class SafetensorsFile:
         if numel == 0:
             return torch.empty(shape, dtype=tdt)
         buf = memoryview(self._mm)[self.base + b:self.base + e]
-        return torch.frombuffer(buf, dtype=tdt).reshape(shape)   # read-only view of the mapping
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the mapping is read-only; nothing writes to it
+            return torch.frombuffer(buf, dtype=tdt).reshape(shape)
 
     def close(self):
         try:
