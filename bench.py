@@ -1,0 +1,275 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens a second of the MiniMax-M3 engine at the M2-family layer sizes.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on standard output.  A "step" is one decode step of the whole batch.  The default run
+has the layer sizes of the baseline's third configuration (hidden 3072, 48 q / 8 kv heads of 128,
+rotary 64, 256 experts top-8 of width 1536, vocabulary 200064) with seeded random weights, 16 of the
+model's 62 layers (about 120 GB of bfloat16 weights), a batch of 8 requests that have each read a
+2,048-token prompt, and a cache sized for the 4,096-token context.
+
+* ``value``: decoded tokens a second, timed on the device with CUDA events around every step (the
+  step function and the sampling kernel), after warm-up steps.  Each step reads tens of GB of
+  weights, far more than the 126 MB L2, so no flush is needed between steps (said in ``config``).
+* ``e2e``: the same through the Python entry point (``LLM``): host token ids in, sampled ids out,
+  every step with its pinned host->device copy of the step's integers and device->host read of
+  the sampled ids.
+* ``prefill``: one 2,048-token prompt as one step: tokens a second, and flops / time / tensor peak.
+* ``roofline``: bytes the decode step has to read (each weight it uses once, counted from the
+  experts the router really chose, plus the cache of the live requests) / time / copy bandwidth.
+* ``points``: decode at batch 1 and 64.
+Peaks are read from MEASURED_PEAKS.json when the driver wrote it, else the stated fallback.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FULL_LAYERS = 62
+SIZES = dict(vocab_size=200064, hidden_size=3072, intermediate_size=1536, num_attention_heads=48,
+             num_key_value_heads=8, head_dim=128, rotary_dim=64, rope_theta=5e6, use_qk_norm=True,
+             qk_norm_type="per_layer", num_local_experts=256, num_experts_per_tok=8, use_routing_bias=True,
+             rms_norm_eps=1e-6, tie_word_embeddings=False, architectures=["MiniMaxM3ForCausalLM"],
+             model_type="minimax_m3")
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            raw = json.loads(p.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            return out, "measured"
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def prefill_flops(c, layers: int, T: int) -> float:
+    H, hd, nq, nkv = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"]
+    proj = 2 * T * H * (nq + 2 * nkv) * hd + 2 * T * nq * hd * H
+    attn = 2 * 2 * nq * hd * T * (T + 1) / 2
+    router = 2 * T * H * c["num_local_experts"]
+    experts = 2 * T * c["num_experts_per_tok"] * 3 * H * c["intermediate_size"]
+    return layers * (proj + attn + router + experts) + 2 * H * c["vocab_size"]
+
+
+def decode_bytes(model, c, layers: int, ctx_tokens: list[int], distinct_experts: list[int]) -> float:
+    """Bytes one decode step has to read: every weight it uses once + the cache of the live requests."""
+    H, hd, nq, nkv, I = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"], c["intermediate_size"]
+    attn_w = 2 * (H * (nq + 2 * nkv) * hd + nq * hd * H)
+    router_w = 4 * c["num_local_experts"] * H
+    expert_w = 2 * 3 * H * I
+    kv = sum(ctx_tokens) * 2 * nkv * hd * 2
+    per_layer_fixed = attn_w + router_w + kv
+    head = 2 * H * c["vocab_size"]
+    return layers * per_layer_fixed + expert_w * sum(distinct_experts) + head
+
+
+def run_ours(args) -> dict:
+    import torch
+    from quanta_b200 import kernels
+    from quanta_b200.config import MiniMaxM3Config
+    from quanta_b200.engine.generate import LLM
+    from quanta_b200.engine.model import random_model
+    from quanta_b200.engine.scheduler import Request, SamplingParams
+    from quanta_b200.engine.step import StepEntry
+    from quanta_b200.parts.moe import SigmoidTopKExperts
+    import random
+
+    pk, pk_src = peaks()
+    layers, B, prompt_len, context = args.layers, args.batch, args.prompt_len, args.context
+    raw = dict(SIZES, num_hidden_layers=layers)
+    cfg = MiniMaxM3Config.from_dict(raw)
+    t0 = time.time()
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    print(f"[bench] model of {layers} layers built in {time.time() - t0:.0f} s, "
+          f"{torch.cuda.memory_allocated() / 1e9:.1f} GB on the device", file=sys.stderr, flush=True)
+    page = 16
+    max_b = max([B] + ([1, 64] if args.points else []))
+    llm = LLM(model, page_size=page, num_pages=max_b * context // page, max_requests=max_b,
+              max_step_tokens=max(prompt_len, max_b), prefill_chunk=prompt_len, max_position=context)
+    eng = llm.engine
+    rng = random.Random(0)
+    V = cfg.vocab_size
+
+    def toks(n):
+        return [rng.randrange(V) for _ in range(n)]
+
+    greedy_out = torch.empty(64, dtype=torch.int32, device="cuda:0")
+
+    def timed_steps(make_entries, n_warm, n_timed, sample_rows):
+        """Device time of each of n_timed steps (ms)."""
+        evs = []
+        for i in range(n_warm + n_timed):
+            entries = make_entries(i)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            lg = eng.step(entries)
+            if sample_rows:
+                kernels.sample_rows(lg, None, None, greedy_out[: lg.shape[0]])
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        eng.check()
+        return [a.elapsed_time(b) for a, b in evs[n_warm:]]
+
+    # ---- prefill: one 2,048-token prompt as one step ----
+    pre_ms = []
+    for i in range(3 + 3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p = toks(prompt_len)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepEntry(("pf", i), p, (prompt_len - 1,))], end=[("pf", i)])
+        b.record()
+        torch.cuda.synchronize()
+        pre_ms.append(a.elapsed_time(b))
+    pre = statistics.median(pre_ms[3:])
+    pf = prefill_flops(raw, layers, prompt_len)
+    prefill = {"value": round(prompt_len / pre * 1e3, 1), "tokens": prompt_len, "ms": round(pre, 3),
+               "frac": round(pf / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+
+    # ---- decode, device-timed ----
+    def decode_run(batch, n_warm, n_timed):
+        rids = [("d", batch, i) for i in range(batch)]
+        for rid in rids:
+            eng.step([StepEntry(rid, toks(prompt_len), ())])
+        kernels.LAUNCHES = 0
+        ms = timed_steps(lambda i: [StepEntry(rid, [rng.randrange(V)], (0,)) for rid in rids], n_warm, n_timed, True)
+        launches = kernels.LAUNCHES * n_timed // (n_warm + n_timed)
+        ctx = [eng.manager.length(rid) for rid in rids]
+        distinct = []
+        for blk in model.blocks:
+            ff = blk.feed_forward
+            if isinstance(ff, SigmoidTopKExperts) and ff.last_counts is not None:
+                distinct.append(int((ff.last_counts > 0).sum()))
+        for rid in rids:
+            eng.release(rid)
+        return ms, launches, ctx, distinct
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, ctx, distinct = decode_run(B, args.warmup, args.steps)
+    clock_info = clocks.stop()
+    step_ms = statistics.fmean(ms)
+    value = B / step_ms * 1e3
+    need = decode_bytes(model, raw, layers, ctx, distinct)
+    achieved = need / (step_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(need), "peaks": pk_src}
+    print(f"[bench] decode b{B}: {value:.1f} tok/s, {step_ms:.3f} ms/step, roofline {roofline}", file=sys.stderr, flush=True)
+
+    points = {}
+    if args.points:
+        for b in (1, 64):
+            pms, _, _, _ = decode_run(b, 3, max(4, args.steps // 4))
+            points[f"decode_b{b}"] = round(b / statistics.fmean(pms) * 1e3, 1)
+            print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
+
+    # ---- end to end through the Python entry point ----
+    n_new = args.warmup + args.steps + 1
+    reqs = [Request(rid=("e", i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new)) for i in range(B)]
+    llm.run(reqs)
+    log = llm.step_log
+    dec = [s for s in log if s["tokens"] == s["sampled"] == B][args.warmup:]
+    e2e_val = None
+    if len(dec) >= 2:
+        e2e_val = B * (len(dec) - 1) / (dec[-1]["t_end"] - dec[0]["t_end"])
+    e2e = {"value": round(e2e_val, 1) if e2e_val else None, "unit": "tokens/s",
+           "h2d_bytes_per_step": dec[-1]["h2d_bytes"] if dec else None,
+           "d2h_bytes_per_step": dec[-1]["d2h_bytes"] if dec else None}
+
+    config = {"model": "MiniMax-M3 (M2-family sizes), random weights", "layers": layers, "layers_full": FULL_LAYERS,
+              "hidden": 3072, "q_heads": 48, "kv_heads": 8, "head_dim": 128, "rotary_dim": 64, "experts": 256,
+              "top_k": 8, "expert_width": 1536, "vocab": 200064, "global_batch": B, "seq_len": context,
+              "prompt_len": prompt_len, "kv_block": page, "parallelism": "single GPU",
+              "l2": "no flush: each step reads >20 GB of weights, inputs larger than L2",
+              "weights_gb": round(torch.cuda.memory_allocated() / 1e9, 1)}
+    return {"metric": "decode tokens/s (batch 8, 2048-token prompts, context 4096)", "value": round(value, 1),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded uniform token ids, seeded random weights)",
+            "config": config, "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+            "gpu_launches": int(launches * args.steps), "clocks": clock_info, "impl": "ours"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=16, help="layers built (the model has 62)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pmrjge/quanta runs on Apple MLX only (mlx is not installable here; its build backend "
+                          "uv_build is absent too), it has no CUDA path"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    out = run_ours(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -34,12 +34,18 @@ def register_architecture(names, config_cls, build_spec) -> Architecture:
     return arch
 
 
+def _load_builtin() -> None:
+    from .. import models  # noqa: F401  (each architecture module registers itself on import)
+
+
 def known_architectures() -> list[str]:
+    _load_builtin()
     return sorted(_BY_NAME)
 
 
 def resolve(raw_config: dict) -> Architecture:
     """Architecture for a raw ``config.json`` dictionary; unknown names raise with the known list."""
+    _load_builtin()
     candidates = list(raw_config.get("architectures") or [])
     if raw_config.get("model_type"):
         candidates.append(str(raw_config["model_type"]))

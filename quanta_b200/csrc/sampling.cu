@@ -106,10 +106,12 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, int V, cons
   __shared__ float s_above;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
-  const float temperature = fparams[r * 4 + 0], top_p = fparams[r * 4 + 1], min_p = fparams[r * 4 + 2];
-  const int top_k = iparams[r * 4 + 0];
-  const uint32_t k0 = (uint32_t)iparams[r * 4 + 1], k1 = (uint32_t)iparams[r * 4 + 2];
-  const uint32_t draw = (uint32_t)iparams[r * 4 + 3];
+  // null parameters: every row is greedy
+  const float temperature = fparams ? fparams[r * 4 + 0] : 0.f;
+  const float top_p = fparams ? fparams[r * 4 + 1] : 1.f, min_p = fparams ? fparams[r * 4 + 2] : 0.f;
+  const int top_k = iparams ? iparams[r * 4 + 0] : 0;
+  const uint32_t k0 = iparams ? (uint32_t)iparams[r * 4 + 1] : 0u, k1 = iparams ? (uint32_t)iparams[r * 4 + 2] : 0u;
+  const uint32_t draw = iparams ? (uint32_t)iparams[r * 4 + 3] : 0u;
 
   if (temperature <= 0.f) {
     float bv = -INFINITY; int bi = -1;

@@ -53,6 +53,7 @@ class Engine:
         self.vocab_size = model.spec.vocab_size
         self.steps = 0
         self.tokens_run = 0
+        self.last_h2d_bytes = 0
 
     # ---- requests -----------------------------------------------------------------------------------
     def _admit(self, rid) -> None:
@@ -152,6 +153,7 @@ class Engine:
         flat_all = [x for p in pieces for x in p]
         host[:total] = torch.tensor(flat_all, dtype=torch.int32)
         dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = total * 4
         out, off = [], 0
         for p in pieces:
             out.append(dev[off: off + len(p)])

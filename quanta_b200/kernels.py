@@ -53,8 +53,13 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(rc: int, what: str) -> None:
+LAUNCHES = 0        # kernels of this library launched so far (a plain counter; reset it to count a region)
+
+
+def _check(rc: int, what: str, n_kernels: int = 1) -> None:
+    global LAUNCHES
     if rc == 0:
+        LAUNCHES += n_kernels
         return
     if rc == -1:
         raise ValueError(f"{what}: bad argument")
@@ -202,7 +207,7 @@ def moe_plan(idx, n_experts: int, bm: int, plan, sorted_pair, tile_expert, tile_
     n_pairs = idx.numel()
     max_tiles = tile_expert.numel()
     _check(lib().qb_moe_plan(_p(idx), n_pairs, n_experts, bm, _p(plan), _p(sorted_pair), _p(tile_expert),
-                             _p(tile_row0), max_tiles, _p(status), _stream()), "moe_plan")
+                             _p(tile_row0), max_tiles, _p(status), _stream()), "moe_plan", 3)
 
 
 def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
@@ -220,8 +225,10 @@ def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile
 
 
 def sample_rows(logits, fparams, iparams, out) -> None:
-    _want(logits, torch.float32, "logits"); _want(fparams, torch.float32, "fparams")
-    _want(iparams, torch.int32, "iparams"); _want(out, torch.int32, "out")
+    """``fparams``/``iparams`` None: every row is greedy (first maximum)."""
+    _want(logits, torch.float32, "logits"); _want(out, torch.int32, "out")
+    if fparams is not None:
+        _want(fparams, torch.float32, "fparams"); _want(iparams, torch.int32, "iparams")
     n, V = logits.shape
     _check(lib().qb_sample_rows(_p(logits), n, V, _p(fparams), _p(iparams), _p(out), _stream()), "sample_rows")
 

@@ -28,6 +28,7 @@ class SigmoidTopKExperts(FeedForward):
         self.use_bias, self.renorm, self.scaling = bool(use_bias), bool(renormalize), float(scaling)
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
         self.gate_w = self.bias = self.w13 = self.w2 = None
+        self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
 
     def tensor_specs(self):
         n = self.names
@@ -77,6 +78,7 @@ class SigmoidTopKExperts(FeedForward):
         tile_expert = ints[plan_words + n_pairs: plan_words + n_pairs + max_tiles]
         tile_row0 = ints[plan_words + n_pairs + max_tiles:]
         kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+        self.last_counts = plan[: self.E]
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
         kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)

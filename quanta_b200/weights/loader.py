@@ -44,6 +44,26 @@ class FolderSource:
         self.ckpt.close()
 
 
+class DictSource:
+    """Tensors handed over in memory, by name."""
+
+    def __init__(self, tensors: dict):
+        self.tensors = dict(tensors)
+
+    def names(self) -> list[str]:
+        return list(self.tensors)
+
+    def meta(self, name: str):
+        t = self.tensors[name]
+        return _ST_NAME.get(t.dtype, str(t.dtype)), tuple(t.shape)
+
+    def read(self, name: str, device) -> torch.Tensor:
+        return self.tensors[name]
+
+    def close(self):
+        pass
+
+
 def _seed_for(seed: int, name: str) -> int:
     return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little") & (2 ** 63 - 1)
 

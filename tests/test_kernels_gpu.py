@@ -1,0 +1,326 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same operation, at sizes
+other than the engine's tiny models: head sizes in steps of 16, odd head counts and groups, widths
+and vocabularies that are no power of two.  Inputs are built so that a fault would show: one far key
+made to dominate, a window's edge, pages in scrambled order."""
+
+import math
+import random
+
+import pytest
+import torch
+
+from tests.plain import minimax_m3_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def K():
+    from quanta_b200 import kernels
+    return kernels
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embedding(table_dtype):
+    V, H, T = 1001, 328, 37
+    table = torch.randn(V, H, device=DEV).to(table_dtype)
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    h = torch.empty(T, H, device=DEV)
+    st = K().new_status(DEV)
+    K().embedding(h, table, ids, st)
+    assert torch.equal(h, table[ids.long()].float())
+    assert int(st[0]) == 0
+    ids[5] = V + 3                              # refused, recorded, row zeroed; nothing faults
+    K().embedding(h, table, ids, st)
+    assert st.tolist()[:3] == [1, V + 3, 1] and float(h[5].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("H", [72, 3072, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(H, out_dtype):
+    T, S, eps = 19, 3, 1e-5
+    h = torch.randn(T, H, device=DEV)
+    delta = torch.randn(T, S, H, device=DEV)
+    w = 1 + 0.1 * torch.randn(H, device=DEV)
+    h0 = h.clone()
+    out = torch.empty(T, H, device=DEV, dtype=out_dtype)
+    K().add_rmsnorm(h, delta, w, eps, out)
+    want_h = h0.clone()
+    for s in range(S):
+        want_h += delta[:, s]
+    assert torch.allclose(h, want_h, atol=1e-6)
+    want = P.rms_norm(want_h, w, eps)
+    assert torch.allclose(out.float(), want.to(out_dtype).float(), **tol(out_dtype))
+    # rows subset, h untouched, bfloat16 delta
+    rows = torch.tensor([7, 0, 18], device=DEV, dtype=torch.int32)
+    d16 = torch.randn(T, H, device=DEV).bfloat16()
+    h1 = h.clone()
+    out3 = torch.empty(3, H, device=DEV, dtype=out_dtype)
+    K().add_rmsnorm(h, d16, w, eps, out3, rows=rows, store_h=False)
+    assert torch.equal(h, h1)
+    want3 = P.rms_norm(h1[rows.long()] + d16[rows.long()].float(), w, eps)
+    assert torch.allclose(out3.float(), want3.to(out_dtype).float(), **tol(out_dtype))
+
+
+def _paged(kc, vc, table, req, length, kvh):
+    """Gather a request's keys/values [length, hd] of one kv head from the pages."""
+    P_ = kc.shape[2]
+    ks = [kc[table[req][p // P_], kvh, p % P_] for p in range(length)]
+    vs = [vc[table[req][p // P_], kvh, p % P_] for p in range(length)]
+    return torch.stack(ks).float(), torch.stack(vs).float()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rd,norm,page", [(6, 3, 48, 24, "per_head", 4), (5, 5, 16, 16, None, 16),
+                                                     (12, 2, 128, 64, "per_layer", 8), (7, 1, 80, 0, "per_layer", 3)])
+def test_qknorm_rope_write(dtype, nq, nkv, hd, rd, norm, page):
+    k = K()
+    T, theta, eps = 23, 12345.0, 1e-5
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV).to(dtype)
+    if norm == "per_layer":
+        qw, kw = 1 + 0.1 * torch.randn(nq * hd, device=DEV), 1 + 0.1 * torch.randn(nkv * hd, device=DEV)
+    else:
+        qw, kw = 1 + 0.1 * torch.randn(hd, device=DEV), 1 + 0.1 * torch.randn(hd, device=DEV)
+    # two requests; positions start anywhere; pages scrambled
+    lens = [(0, 9), (57, 14)]                     # (first position, tokens) per request
+    pos = torch.tensor([p for a, n in lens for p in range(a, a + n)], dtype=torch.int32)
+    req = torch.tensor([r for r, (a, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    max_pages = max(-(-(a + n) // page) for a, n in lens)
+    num_pages = 2 * max_pages + 3
+    ids = list(range(num_pages))
+    random.Random(0).shuffle(ids)
+    table = torch.tensor([ids[:max_pages], ids[max_pages:2 * max_pages]], dtype=torch.int32)
+    kc = torch.zeros(num_pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nq, hd, device=DEV, dtype=dtype)
+    inv = (1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / max(rd, 1)))).to(DEV) if rd else \
+        torch.empty(0, device=DEV)
+    st = k.new_status(DEV)
+    kind = {None: k.NORM_NONE, "per_layer": k.NORM_PER_LAYER, "per_head": k.NORM_PER_HEAD}[norm]
+    k.qknorm_rope_write(qkv, q_out, kc, vc, qw if norm else None, kw if norm else None, kind, eps, inv, None,
+                        pos.to(DEV), pos.to(DEV), req.to(DEV), table.to(DEV), nq, nkv, hd, rd, page, st)
+    assert int(st[0]) == 0
+    x = qkv.float().cpu()
+    q = x[:, : nq * hd].reshape(T, nq, hd)
+    kk = x[:, nq * hd: (nq + nkv) * hd].reshape(T, nkv, hd)
+    v = x[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    if norm:
+        q = P.qk_norm(q, qw.cpu(), nq, hd, norm, eps)
+        kk = P.qk_norm(kk, kw.cpu(), nkv, hd, norm, eps)
+    if rd:
+        q, kk = P.partial_rope(q, pos, rd, theta), P.partial_rope(kk, pos, rd, theta)
+    assert torch.allclose(q_out.float().cpu(), q.to(dtype).float(), **tol(dtype))
+    for t in range(T):
+        pg, sl = int(table[req[t], pos[t] // page]), int(pos[t]) % page
+        assert torch.allclose(kc[pg, :, sl].float().cpu(), kk[t].to(dtype).float(), **tol(dtype))
+        assert torch.equal(vc[pg, :, sl].cpu(), v[t].to(dtype))
+    if rd < hd:      # dims past rotary_dim are exactly the normed values
+        kk2 = x[:, nq * hd: (nq + nkv) * hd].reshape(T, nkv, hd)
+        if norm is None:
+            assert torch.equal(q_out.cpu()[..., rd:], x[:, : nq * hd].reshape(T, nq, hd)[..., rd:].to(dtype))
+    # a block table entry outside the pool is refused, not followed
+    bad = table.clone()
+    bad[1, 0] = num_pages + 5
+    bad[1, 1:] = num_pages + 5
+    bad[0, :] = -1
+    k.qknorm_rope_write(qkv, q_out, kc, vc, qw if norm else None, kw if norm else None, kind, eps, inv, None,
+                        pos.to(DEV), pos.to(DEV), req.to(DEV), bad.to(DEV), nq, nkv, hd, rd, page, st)
+    assert int(st[0]) == 2
+
+
+def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
+    T, nq, hd = q.shape
+    nkv = kc.shape[1]
+    out = torch.zeros(T, nq, hd)
+    for t in range(T):
+        p, r = int(tok_pos[t]), int(tok_req[t])
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nq):
+            ks, vs = _paged(kc.cpu(), vc.cpu(), table, r, p + 1, h // (nq // nkv))
+            s = (ks[lo:] @ q[t, h].float().cpu()) * scale
+            out[t, h] = torch.softmax(s, 0) @ vs[lo:]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 3, 48, 4, 0), (4, 4, 16, 16, 0), (12, 2, 128, 8, 0),
+                                                   (5, 1, 256, 5, 0), (6, 2, 64, 4, 11)])
+def test_paged_attention(dtype, nq, nkv, hd, page, window):
+    k = K()
+    torch.manual_seed(1)
+    spans = [(0, 13), (70, 1), (33, 9), (129, 1)]          # (first position, tokens): prompt portions beside decode tokens
+    tok_pos = torch.tensor([p for a, n in spans for p in range(a, a + n)], dtype=torch.int32)
+    tok_req = torch.tensor([r for r, (a, n) in enumerate(spans) for _ in range(n)], dtype=torch.int32)
+    T = tok_pos.numel()
+    max_pages = max(-(-(a + n) // page) for a, n in spans)
+    num_pages = len(spans) * max_pages
+    ids = list(range(num_pages))
+    random.Random(2).shuffle(ids)
+    table = torch.tensor([ids[r * max_pages:(r + 1) * max_pages] for r in range(len(spans))], dtype=torch.int32)
+    kc = torch.randn(num_pages, nkv, page, hd, device=DEV).to(dtype)
+    vc = torch.randn(num_pages, nkv, page, hd, device=DEV).to(dtype)
+    q = torch.randn(T, nq, hd, device=DEV).to(dtype)
+    # make one far key stand out for the last token of request 3: its score dominates, so a kernel that
+    # skips or misplaces that key is far off
+    far = 5 if not window else 129 - window + 1      # the oldest key still inside the window
+    pg, sl = int(table[3, far // page]), far % page
+    kc[pg, :, sl] = 0
+    kc[pg, :, sl, 0] = 30.0
+    q[T - 1, :, 0] = 8.0
+    scale = hd ** -0.5
+    out = torch.empty_like(q)
+    st = k.new_status(DEV)
+    k.paged_attention_simt(q, kc, vc, out, tok_pos.to(DEV), tok_req.to(DEV), table.to(DEV), scale, window, st)
+    assert int(st[0]) == 0
+    want = attention_reference(q, kc, vc, table.tolist(), tok_pos, tok_req, scale, window)
+    assert torch.allclose(out.float().cpu(), want, **tol(dtype))
+    # the far key carried the last token's output
+    assert torch.allclose(out[T - 1, 0].float().cpu(), vc[pg, 0, sl].float().cpu(), atol=0.05)
+    if window:       # one position further back is outside the window: it must not count
+        pg2, sl2 = int(table[3, (far - 1) // page]), (far - 1) % page
+        kc[pg2, :, sl2] = 0
+        kc[pg2, :, sl2, 0] = 60.0
+        k.paged_attention_simt(q, kc, vc, out, tok_pos.to(DEV), tok_req.to(DEV), table.to(DEV), scale, window, st)
+        assert torch.allclose(out[T - 1].float().cpu(), want[T - 1], **tol(dtype))
+
+
+@pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
+def test_gemm_nt_simt(a_dtype, b_dtype):
+    M, N, K_ = 45, 257, 1003
+    a = torch.randn(M, K_, device=DEV).to(a_dtype)
+    b = torch.randn(N, K_, device=DEV).to(b_dtype)
+    out = torch.empty(M, N, device=DEV)
+    K().gemm_nt_simt(a, b, out)
+    want = a.double() @ b.double().T
+    assert torch.allclose(out.double(), want, atol=1e-3, rtol=1e-5)
+    # a row's result does not depend on the rest of the batch: bit-identical alone
+    out1 = torch.empty(1, N, device=DEV)
+    K().gemm_nt_simt(a[17:18].contiguous(), b, out1)
+    assert torch.equal(out1[0], out[17])
+
+
+@pytest.mark.parametrize("E,k,bias,renorm,scale", [(8, 2, True, True, 1.0), (100, 7, False, True, 2.5),
+                                                   (256, 8, True, True, 1.0), (33, 1, True, True, 1.0),
+                                                   (520, 5, True, False, 0.5)])
+def test_router_topk(E, k, bias, renorm, scale):
+    T = 29
+    logits = torch.randn(T, E, device=DEV)
+    logits[3, :] = 0.25                     # a full tie: lower expert indices win
+    b = (0.05 * torch.randn(E, device=DEV)) if bias else None
+    if bias:
+        b[: E // 2] = 0.0
+    idx = torch.empty(T, k, device=DEV, dtype=torch.int32)
+    w = torch.empty(T, k, device=DEV)
+    K().router_topk(logits, b, idx, w, renorm, scale)
+    scores = torch.sigmoid(logits)
+    choice = scores + b[None] if bias else scores
+    want_idx = torch.argsort(-choice, dim=-1, stable=True)[:, :k]
+    want_w = torch.gather(scores, 1, want_idx)
+    if renorm and k > 1:
+        want_w = want_w / (want_w.sum(-1, keepdim=True) + 1e-20)
+    want_w = want_w * scale
+    assert torch.equal(idx.long(), want_idx)
+    assert torch.allclose(w, want_w, atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2)])
+def test_expert_products(dtype, T, H, I, E, k):
+    kern = K()
+    torch.manual_seed(3)
+    x = torch.randn(T, H, device=DEV).to(dtype)
+    w13 = (0.1 * torch.randn(E, 2 * I, H, device=DEV)).to(dtype)
+    w2 = (0.1 * torch.randn(E, H, I, device=DEV)).to(dtype)
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    if T > 30:
+        idx[:30, 0] = 5                       # one expert with many rows (several tiles), some with none
+        idx[:30, 1:] = torch.where(idx[:30, 1:] == 5, (idx[:30, 1:] + 1) % E, idx[:30, 1:])
+        idx[:30, 1] = torch.where(idx[:30, 1] == idx[:30, 0], 6, idx[:30, 1])
+    pw = torch.rand(T, k, device=DEV)
+    n_pairs = T * k
+    words, max_tiles = kern.moe_plan_sizes(n_pairs, E, kern.MOE_SIMT_BM)
+    plan = torch.empty(words, device=DEV, dtype=torch.int32)
+    sorted_pair = torch.empty(n_pairs, device=DEV, dtype=torch.int32)
+    te = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
+    tr = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
+    st = kern.new_status(DEV)
+    kern.moe_plan(idx, E, kern.MOE_SIMT_BM, plan, sorted_pair, te, tr, st)
+    counts = torch.bincount(idx.flatten().long(), minlength=E)
+    assert plan[:E].tolist() == counts.tolist()
+    assert sorted(sorted_pair.tolist()) == list(range(n_pairs))
+    flat = idx.flatten()
+    assert all(int(flat[p]) <= int(flat[q]) for p, q in zip(sorted_pair.tolist(), sorted_pair.tolist()[1:]))
+    act = torch.empty(n_pairs, I, device=DEV, dtype=dtype)
+    kern.moe_grouped_simt(1, x, w13, act, sorted_pair, pw, plan, te, tr, E, k)
+    y = torch.full((T, k, H), float("nan"), device=DEV)
+    kern.moe_grouped_simt(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, k)
+    xf = x.float()
+    want = torch.empty(T, k, H, device=DEV)
+    for t in range(T):
+        for s in range(k):
+            e = int(idx[t, s])
+            g = xf[t] @ w13[e, :I].float().T
+            u = xf[t] @ w13[e, I:].float().T
+            a = (g * torch.sigmoid(g) * u).to(dtype).float()
+            want[t, s] = pw[t, s] * (a @ w2[e].float().T)
+    assert torch.allclose(y, want, **tol(dtype))
+    assert int(st[0]) == 0
+
+
+def test_sampling_matches_plain():
+    kern = K()
+    import numpy as np
+    V, n = 1003, 12
+    torch.manual_seed(4)
+    logits = (3 * torch.randn(n, V)).float()
+    logits[2, 100] = logits[2, 7] = 50.0                    # greedy tie: first index
+    cases = [dict(temperature=0.0), dict(temperature=0.8, seed=1), dict(temperature=0.0),
+             dict(temperature=1.3, seed=2 ** 40 + 17), dict(temperature=0.7, top_k=5, seed=3),
+             dict(temperature=1.0, top_p=0.6, seed=4), dict(temperature=1.0, min_p=0.2, seed=5),
+             dict(temperature=0.9, top_k=50, top_p=0.8, min_p=0.05, seed=6), dict(temperature=2.0, top_k=1, seed=7),
+             dict(temperature=1.0, top_p=0.999, seed=8), dict(temperature=0.5, seed=9), dict(temperature=1.0, top_k=V + 5, seed=10)]
+    f = torch.tensor([[c.get("temperature", 0.0), c.get("top_p", 1.0), c.get("min_p", 0.0), 0.0] for c in cases])
+    mismatches = 0
+    for draw in (0, 1, 77):
+        i = torch.tensor([[c.get("top_k", 0), c.get("seed", 0) & 0xFFFFFFFF, c.get("seed", 0) >> 32, draw] for c in cases],
+                         dtype=torch.int64).to(torch.int32)
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        kern.sample_rows(logits.to(DEV), f.to(DEV), i.to(DEV), out)
+        for r, c in enumerate(cases):
+            want = P.sample(logits[r].numpy(), draw=draw, **c)
+            if int(out[r]) != want:
+                mismatches += 1
+                # only a near tie of (logit + noise) may differ
+                lg = logits[r].numpy() * np.float32(1 / c["temperature"]) + P.gumbel_noise(c["seed"], draw, V)
+                assert abs(lg[int(out[r])] - lg[want]) < 1e-4, (r, draw, c)
+    assert mismatches <= 1
+    greedy = torch.empty(n, dtype=torch.int32, device=DEV)
+    kern.sample_rows(logits.to(DEV), None, None, greedy)
+    assert greedy.tolist() == logits.argmax(-1).tolist() and int(greedy[2]) == 7
+
+
+def test_sampling_distribution_and_penalties():
+    kern = K()
+    import numpy as np
+    p = torch.tensor([0.5, 0.25, 0.15, 0.1])
+    n = 4000
+    logits = torch.log(p).repeat(n, 1).to(DEV)
+    f = torch.tensor([[1.0, 1.0, 0.0, 0.0]]).repeat(n, 1).to(DEV)
+    i = torch.tensor([[0, 11, 0, d] for d in range(n)], dtype=torch.int32).to(DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    kern.sample_rows(logits, f, i, out)
+    freq = torch.bincount(out.long().cpu(), minlength=4).float() / n
+    assert float((freq - p).abs().max()) < 0.03
+    want = [P.sample(torch.log(p).numpy(), temperature=1.0, seed=11, draw=d) for d in range(50)]
+    assert out[:50].tolist() == want
+    lg = torch.tensor([[2.0, -2.0, 1.0, 0.5], [1.0, 1.0, 1.0, 1.0]], device=DEV)
+    prev = torch.tensor([0, 1, 1, 3], dtype=torch.int32, device=DEV)
+    off = torch.tensor([0, 3, 4], dtype=torch.int32, device=DEV)
+    pp = torch.tensor([[2.0, 0.5, 0.25], [1.0, 0.0, 0.0]], device=DEV)
+    kern.apply_penalties(lg, prev, off, pp)
+    w0 = P.apply_penalties(np.array([2.0, -2.0, 1.0, 0.5], dtype=np.float32), [0, 1, 1], 2.0, 0.5, 0.25)
+    assert np.allclose(lg[0].cpu().numpy(), w0) and lg[1].tolist() == [1.0] * 4

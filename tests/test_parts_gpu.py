@@ -1,0 +1,361 @@
+"""Each part alone against the plain implementation; the run order as data (a layer named twice, a
+layer reading another layer's cache); a toy mixer with state of its own, a toy feed-forward and a toy
+position encoding registered from this file and built and stepped without a change to the framework;
+and greedy / sampled generation through the entry point."""
+
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests import helpers as H
+from tests.conftest import TINY
+from tests.plain import minimax_m3_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _ctx(T, pos=None, req=None, dtype=torch.float32):
+    from quanta_b200 import kernels
+    from quanta_b200.parts.base import StepContext
+    pos = torch.arange(T, dtype=torch.int32) if pos is None else pos
+    req = torch.zeros(T, dtype=torch.int32) if req is None else req
+    return StepContext(n_tokens=T, positions=pos.view(T, 1).to(DEV), tok_pos=pos.to(DEV), tok_req=req.to(DEV),
+                       req_slot=torch.zeros(1, dtype=torch.int32, device=DEV),
+                       req_start=torch.tensor([0, T], dtype=torch.int32, device=DEV),
+                       req_len_after=torch.tensor([T], dtype=torch.int32, device=DEV),
+                       status=kernels.new_status(DEV), dtype=dtype, max_new_tokens_per_req=T, max_len_after=T)
+
+
+def _loaded(model_dirs, name, dtype="float32"):
+    from quanta_b200.engine.model import load_model
+    return load_model(model_dirs[name], dtype=dtype)[0]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_norm_attention_experts_alone(model_dirs, plain_models, name):
+    from quanta_b200.parts.base import LayerCache
+    model = _loaded(model_dirs, name)
+    weights, cfg = plain_models[name]
+    blk = model.blocks[1]
+    T, Hd = 21, cfg["H"]
+    torch.manual_seed(0)
+    x = torch.randn(T, Hd)
+    ctx = _ctx(T)
+    p = "model.layers.1."
+    # norm
+    h = x.clone().to(DEV)
+    out = torch.empty(T, Hd, device=DEV)
+    blk.mixer_norm.forward(h, None, out)
+    assert torch.allclose(out.cpu(), P.rms_norm(x, weights[p + "input_layernorm.weight"], cfg["eps"]), atol=1e-5)
+    # mixer: whole sequence through the paged cache
+    page = 4
+    n_pages = -(-T // page)
+    spec = blk.mixer.cache_spec()
+    kc = torch.zeros(n_pages, spec.n_kv_heads, page, spec.head_dim, device=DEV)
+    cache = LayerCache(kc, torch.zeros_like(kc), page, torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1))
+    got = blk.mixer.forward(x.to(DEV), ctx, cache, {})
+    W = lambda n: weights[p + "self_attn." + n].float()     # noqa: E731
+    q = (x @ W("q_proj.weight").T).reshape(T, cfg["nq"], cfg["hd"])
+    k = (x @ W("k_proj.weight").T).reshape(T, cfg["nkv"], cfg["hd"])
+    v = (x @ W("v_proj.weight").T).reshape(T, cfg["nkv"], cfg["hd"])
+    if cfg["qk_norm"]:
+        q = P.qk_norm(q, W("q_norm.weight"), cfg["nq"], cfg["hd"], cfg["qk_norm_type"], cfg["eps"])
+        k = P.qk_norm(k, W("k_norm.weight"), cfg["nkv"], cfg["hd"], cfg["qk_norm_type"], cfg["eps"])
+    pos = torch.arange(T)
+    q, k = P.partial_rope(q, pos, cfg["rd"], cfg["theta"]), P.partial_rope(k, pos, cfg["rd"], cfg["theta"])
+    want = P.causal_attention(q, k, v, None, torch.float32) @ W("o_proj.weight").T
+    assert torch.allclose(got.cpu(), want, atol=2e-5)
+    # feed-forward: router alone, then the whole part (summed over its k slots)
+    ffn = blk.feed_forward
+    m = p + "block_sparse_moe."
+    bias = weights[m + "e_score_correction_bias"] if cfg["bias"] else None
+    idx, w = ffn.route(x.to(DEV))
+    widx, ww = P.router(x, weights[m + "gate.weight"], bias, cfg["k"], cfg["renorm"], cfg["scale"])
+    assert torch.equal(idx.cpu().long(), widx) and torch.allclose(w.cpu(), ww, atol=1e-6)
+    y = ffn.forward(x.to(DEV), ctx)
+    experts = [tuple(weights[f"{m}experts.{e}.{n}.weight"] for n in ("w1", "w3", "w2")) for e in range(cfg["E"])]
+    want = P.moe(x, weights[m + "gate.weight"], bias, experts, cfg["k"], cfg["renorm"], cfg["scale"], None, torch.float32)
+    assert y.shape == (T, cfg["k"], Hd)
+    assert torch.allclose(y.sum(1).cpu(), want, atol=2e-5)
+    assert int(ctx.status[0]) == 0
+
+
+def test_rotary_part_with_sections_equals_the_plain_ladder():
+    from quanta_b200.parts.rotary import PartialRotary
+    plain_ = PartialRotary(48, 24, 25000.0)
+    sect = PartialRotary(48, 24, 25000.0, sections=[4, 4, 4])
+    inv, axis, rd, n_axes = sect.rotary_tables(DEV)
+    assert n_axes == 3 and axis.tolist() == [0] * 4 + [1] * 4 + [2] * 4 and rd == 24
+    assert torch.equal(inv.cpu(), P.rope_inv_freq(24, 25000.0)) and torch.equal(inv, plain_.rotary_tables(DEV)[0])
+    with pytest.raises(ValueError, match="sum"):
+        PartialRotary(48, 24, 1e4, sections=[4, 4])
+
+
+def test_dense_swiglu_part():
+    from quanta_b200.parts.moe import SwiGLUDense
+    torch.manual_seed(1)
+    Hd, I, T = 72, 100, 9
+    ws = {"g": 0.1 * torch.randn(I, Hd), "u": 0.1 * torch.randn(I, Hd), "d": 0.1 * torch.randn(Hd, I)}
+    part = SwiGLUDense(Hd, I, {"gate": "g", "up": "u", "down": "d"})
+    part.load(lambda n: ws[n].to(DEV))
+    x = torch.randn(T, Hd)
+    got = part.forward(x.to(DEV), _ctx(T))
+    assert torch.allclose(got.cpu(), P.expert_swiglu(x, ws["g"], ws["u"], ws["d"], None, torch.float32), atol=1e-5)
+
+
+def _spec_with_schedule(name, schedule):
+    from quanta_b200.config import MiniMaxM3Config, resolve
+    raw = TINY[name]
+    spec = resolve(raw).build_spec(MiniMaxM3Config.from_dict(raw))
+    spec.schedule = schedule
+    spec.__post_init__()
+    return spec
+
+
+def test_run_order_is_data_a_layer_twice(model_dirs, plain_models):
+    """Schedule [0, 1, 0]: layer 0's weights run twice, each run with a cache of its own."""
+    from quanta_b200.engine.model import Model
+    from quanta_b200.engine.step import Engine
+    from quanta_b200.parts.spec import ScheduleEntry
+    from quanta_b200.weights import FolderSource
+    spec = _spec_with_schedule("A", [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)])
+    model = Model(spec, dtype="float32").load(FolderSource(model_dirs["A"]))
+    eng = Engine(model, num_pages=32, page_size=4, max_requests=4)
+    assert len(eng.kv) == 3
+    reqs = {"a": H.random_tokens(29, 512, 1), "b": H.random_tokens(18, 512, 2)}
+    want = H.plain_logits(plain_models["A"], reqs, schedule=[0, 1, 0])
+    for cut in (H.cut_whole(reqs), H.cut_portions(reqs), H.cut_mixed(reqs, 2, seed=1)):
+        got = H.replay(eng, cut)
+        assert H.first_wrong(got, want, 2e-5) is None
+
+
+def test_a_layer_reads_another_layers_cache(model_dirs):
+    """Schedule entry 2 runs layer 1's weights on the K/V that entry 0 wrote (it writes none).  The
+    result must not depend on how the tokens are cut, and must differ from the unshared model."""
+    from quanta_b200.engine.model import Model
+    from quanta_b200.engine.step import Engine
+    from quanta_b200.parts.spec import ScheduleEntry
+    from quanta_b200.weights import FolderSource
+    spec = _spec_with_schedule("A", [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1, read_cache_of=0)])
+    model = Model(spec, dtype="float32").load(FolderSource(model_dirs["A"]))
+    eng = Engine(model, num_pages=32, page_size=4, max_requests=4)
+    assert sorted(eng.kv) == [0, 1]
+    reqs = {"a": H.random_tokens(27, 512, 3)}
+    whole = H.replay(eng, H.cut_whole(reqs))
+    for cut in (H.cut_tail_decode(reqs, 10), H.cut_portions(reqs)):
+        got = H.replay(eng, cut)
+        assert H.first_wrong(got, whole, 2e-5) is None
+    with pytest.raises(ValueError, match="does not run before"):
+        _spec_with_schedule("A", [ScheduleEntry(0, read_cache_of=1), ScheduleEntry(1)])
+
+
+# ---- toy parts, defined here, registered, built and stepped --------------------------------------------
+def _register_toys():
+    from quanta_b200.parts.base import FeedForward, Mixer, PositionEncoding, TensorSpec, register
+
+    @register("mixer", "toy_running_mean")
+    class RunningMean(Mixer):
+        """Output = (decayed running sum of the projected inputs of this request so far) ; the sum and a
+        count live in the request's state slot, so portions must carry them across steps."""
+
+        def __init__(self, hidden_size, weight_name, decay):
+            self.H, self.weight_name, self.decay = hidden_size, weight_name, decay
+            self.w = None
+
+        def tensor_specs(self):
+            return [TensorSpec(self.weight_name, (self.H, self.H))]
+
+        def load(self, fetch):
+            self.w = fetch(self.weight_name)
+
+        def state_spec(self):
+            return {"sum": ((self.H,), torch.float32), "count": ((1,), torch.float32)}
+
+        def forward(self, x, ctx, cache, state):
+            proj = (x.float() @ self.w.float().T)
+            out = torch.empty_like(proj)
+            starts, slots = ctx.host["req_start"], ctx.host["req_slot"]
+            for r, slot in enumerate(slots):                     # a toy: plain torch, one request at a time
+                s = state["sum"][slot]
+                for t in range(starts[r], starts[r + 1]):
+                    s.mul_(self.decay).add_(proj[t])
+                    state["count"][slot] += 1
+                    out[t] = s / state["count"][slot]
+            return out.to(x.dtype)
+
+    @register("feed_forward", "toy_two_way_routing")
+    class TwoWay(FeedForward):
+        """Routes each token to one of two scalings by the sign of its first feature."""
+
+        def __init__(self, hidden_size, scales):
+            self.scales = scales
+
+        def forward(self, x, ctx):
+            pick = (x[:, :1] > 0).to(x.dtype)
+            return x * (pick * self.scales[0] + (1 - pick) * self.scales[1])
+
+    @register("position", "toy_linear_ladder")
+    class LinearLadder(PositionEncoding):
+        """Another position encoding: frequencies fall linearly instead of geometrically."""
+
+        def __init__(self, rotary_dim):
+            self.rd = rotary_dim
+
+        def rotary_tables(self, device):
+            inv = (1.0 - torch.arange(self.rd // 2, dtype=torch.float32) / (self.rd // 2)).to(device)
+            return inv, None, self.rd, 1
+
+
+def _toy_plain(ws, ids, decay, scales, eps):
+    """Whole-sequence plain version of the toy model: embedding, [norm, running mean, norm, two-way] x 2."""
+    h = ws["emb"][torch.tensor(ids)].float()
+    for L in range(2):
+        x = P.rms_norm(h, ws[f"n{L}a"], eps)
+        proj = x @ ws[f"m{L}"].float().T
+        s, outs = torch.zeros(h.shape[1]), []
+        for t in range(len(ids)):
+            s = s * decay + proj[t]
+            outs.append(s / (t + 1))
+        h = h + torch.stack(outs)
+        x = P.rms_norm(h, ws[f"n{L}b"], eps)
+        pick = (x[:, :1] > 0).float()
+        h = h + x * (pick * scales[0] + (1 - pick) * scales[1])
+    return P.rms_norm(h, ws["nf"], eps) @ ws["emb"].float().T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps():
+    from quanta_b200.engine.model import Model
+    from quanta_b200.engine.step import Engine
+    from quanta_b200.parts.spec import ModelSpec
+    from quanta_b200.weights import DictSource, RandomSource
+    _register_toys()
+    Hd, V, eps, decay, scales = 40, 97, 1e-5, 0.9, (0.5, -0.25)
+    norm = lambda n: ("rms_norm", dict(width=Hd, eps=eps, weight_name=n))      # noqa: E731
+    layers = [("pre_norm", dict(hidden_size=Hd, mixer=("toy_running_mean", dict(hidden_size=Hd, weight_name=f"m{L}", decay=decay)),
+                                feed_forward=("toy_two_way_routing", dict(hidden_size=Hd, scales=scales)),
+                                mixer_norm=norm(f"n{L}a"), feed_forward_norm=norm(f"n{L}b"))) for L in range(2)]
+    spec = ModelSpec(name="toy", vocab_size=V, hidden_size=Hd, embedding_name="emb", layers=layers,
+                     final_norm=norm("nf"), head_name=None, tied_head=True)
+    model = Model(spec, dtype="float32")
+    src = RandomSource(model.tensor_specs(), seed=3, matrix_dtype=torch.float32)
+    ws = {n: src.read(n, "cpu") for n in src.names()}
+    model.load(DictSource(ws))
+    eng = Engine(model, num_pages=4, page_size=4, max_requests=3)
+    assert eng.manager.groups == [] and set(eng.state[0]) == {"sum", "count"}     # no pages, but state slots
+    reqs = {"a": H.random_tokens(19, V, 1), "b": H.random_tokens(11, V, 2), "c": H.random_tokens(7, V, 3)}
+    want = {}
+    for rid, toks in reqs.items():
+        lg = _toy_plain(ws, toks, decay, scales, eps)
+        want.update({(rid, i): lg[i] for i in range(len(toks))})
+    for cut in (H.cut_whole(reqs), H.cut_portions(reqs), H.cut_mixed(reqs, 3, seed=2), H.cut_mixed(reqs, 2, seed=9)):
+        got = H.replay(eng, cut)       # a slot is zeroed when the next request takes it
+        assert H.first_wrong(got, want, 1e-4) is None
+
+
+def test_toy_position_encoding_in_the_real_attention(model_dirs):
+    """The attention mixer takes any registered position encoding: here a linear frequency ladder."""
+    from quanta_b200.parts.attention import GQAttention
+    from quanta_b200.parts.base import LayerCache
+    _register_toys()
+    torch.manual_seed(5)
+    Hd, nq, nkv, hd, rd, T = 48, 4, 2, 16, 8, 11
+    ws = {n: 0.2 * torch.randn(*s) for n, s in [("q", (nq * hd, Hd)), ("k", (nkv * hd, Hd)), ("v", (nkv * hd, Hd)), ("o", (Hd, nq * hd))]}
+    att = GQAttention(Hd, nq, nkv, hd, hd ** -0.5, ("toy_linear_ladder", dict(rotary_dim=rd)), None, 1e-6,
+                      {"q": "q", "k": "k", "v": "v", "o": "o"})
+    att.load(lambda n: ws[n].to(DEV))
+    x = torch.randn(T, Hd)
+    kc = torch.zeros(3, nkv, 4, hd, device=DEV)
+    cache = LayerCache(kc, torch.zeros_like(kc), 4, torch.arange(3, dtype=torch.int32, device=DEV).view(1, -1))
+    got = att.forward(x.to(DEV), _ctx(T), cache, {})
+    inv = 1.0 - torch.arange(rd // 2, dtype=torch.float32) / (rd // 2)
+
+    def rope(t):
+        ang = torch.arange(T, dtype=torch.float32)[:, None] * inv[None]
+        c, s = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+        a, b = t[..., : rd // 2], t[..., rd // 2: rd]
+        return torch.cat([a * c - b * s, b * c + a * s, t[..., rd:]], -1)
+    q = rope((x @ ws["q"].T).reshape(T, nq, hd))
+    k = rope((x @ ws["k"].T).reshape(T, nkv, hd))
+    v = (x @ ws["v"].T).reshape(T, nkv, hd)
+    want = P.causal_attention(q, k, v, None, torch.float32) @ ws["o"].T
+    assert torch.allclose(got.cpu(), want, atol=2e-5)
+
+
+# ---- generation through the entry point ------------------------------------------------------------------
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16")])
+def test_greedy_generation_matches_plain(model_dirs, plain_models, name, dtype):
+    from quanta_b200 import generate
+    from quanta_b200.engine.generate import LLM
+    weights, cfg = plain_models[name]
+    vocab = TINY[name]["vocab_size"]
+    prompts = [H.random_tokens(n, vocab, 40 + i) for i, n in enumerate((5, 11, 16))]
+    llm = LLM(model_dirs[name], dtype=dtype, page_size=4, num_pages=40, max_requests=4, max_step_tokens=12, prefill_chunk=6)
+    got = generate(llm, prompts, max_new_tokens=8, eos_id=[])
+    act = None if dtype == "float32" else torch.bfloat16
+    for p, g in zip(prompts, got):
+        want = P.generate(weights, cfg, p, max_new_tokens=8, act=act)
+        if dtype == "float32":
+            assert g == want
+        else:
+            # bfloat16: the first token must agree unless the top two logits are within rounding
+            lg = P.forward_logits(weights, cfg, p, act=act)[-1]
+            top2 = torch.topk(lg, 2).values
+            assert g[0] == want[0] or float(top2[0] - top2[1]) < 0.02
+    one = generate(llm, prompts[1], max_new_tokens=8, eos_id=[])
+    assert one == got[1]                                       # alone or in a batch: the same tokens
+    with pytest.raises(ValueError, match="empty"):
+        generate(llm, [], max_new_tokens=2)
+    assert llm.engine.manager.stats()["live_requests"] == 0
+
+
+def test_sampled_generation_is_seeded_and_matches_plain(model_dirs, plain_models):
+    from quanta_b200 import generate
+    from quanta_b200.engine.generate import LLM
+    name = "B"
+    weights, cfg = plain_models[name]
+    prompts = [H.random_tokens(7, 1000, 1), H.random_tokens(23, 1000, 2)]
+    llm = LLM(model_dirs[name], dtype="float32", page_size=8, num_pages=16, max_requests=2, max_step_tokens=8, prefill_chunk=6)
+    kw = dict(max_new_tokens=6, temperature=0.8, seed=1234, eos_id=[])
+    a = generate(llm, prompts, **kw)
+    b = generate(llm, prompts, **kw)
+    c = generate(llm, prompts, **{**kw, "seed": 99})
+    assert a == b and a != c
+    for p, g in zip(prompts, a):
+        assert g == P.generate(weights, cfg, p, max_new_tokens=6, temperature=0.8, seed=1234)
+    d = generate(llm, prompts[0], max_new_tokens=6, temperature=0.8, seed=1234, top_k=20, top_p=0.9, min_p=0.01,
+                 repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1, eos_id=[])
+    assert d == P.generate(weights, cfg, prompts[0], max_new_tokens=6, temperature=0.8, seed=1234, top_k=20, top_p=0.9,
+                           min_p=0.01, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1)
+
+
+def test_eos_and_few_pages(model_dirs, plain_models):
+    """An eos id ends a request and is not returned; with too few pages requests are preempted and
+    recomputed, and the tokens are the same as with plenty."""
+    from quanta_b200 import generate
+    from quanta_b200.engine.generate import LLM
+    name = "A"
+    weights, cfg = plain_models[name]
+    prompts = [H.random_tokens(9, 512, 70 + i) for i in range(3)]
+    roomy = LLM(model_dirs[name], dtype="float32", page_size=4, num_pages=64, max_requests=4)
+    want = generate(roomy, prompts, max_new_tokens=12, eos_id=[])
+    tight = LLM(model_dirs[name], dtype="float32", page_size=4, num_pages=11, max_requests=4, prefill_chunk=8)
+    got = generate(tight, prompts, max_new_tokens=12, eos_id=[])
+    assert got == want and tight.last_stats["preemptions"] >= 1
+    stop = want[0][4]
+    cut = generate(roomy, prompts[0], max_new_tokens=12, eos_id=stop)
+    assert cut == want[0][: want[0].index(stop)]
+
+
+def test_command_line(model_dirs):
+    cmd = [sys.executable, "-m", "quanta_b200", "generate", "--model", str(model_dirs["A"]), "--dtype", "float32",
+           "--prompt-ids", "5,17,3", "--max-new-tokens", "4", "--block-size", "4", "--num-pages", "16", "--eos-id", "600"]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    toks = [int(t) for t in r.stdout.strip().split(",")]
+    from quanta_b200 import generate
+    assert toks == generate(str(model_dirs["A"]), [5, 17, 3], max_new_tokens=4, dtype="float32", page_size=4, num_pages=16, eos_id=[])
