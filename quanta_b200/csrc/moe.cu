@@ -85,7 +85,8 @@ extern "C" int qb_router_topk(const float* logits, const float* bias, int* idx_o
 
 // ---------------------------------------------------------------------------------------------
 // plan: counts per expert -> offsets, tile list, pairs sorted by expert
-//   plan layout (int32): counts[E] | cursor[E] | offsets[E+1] | num_tiles[1] | pad
+//   plan layout (int32): counts[E] | cursor[E] | offsets[E+1] | num_tiles | num_active | pad |
+//                        active[E] (experts that have rows, ascending)   -- 4E+4 words
 // ---------------------------------------------------------------------------------------------
 __global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ counts,
                                  int* status) {
@@ -98,27 +99,32 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int E
 
 // one block of 1024 threads; thread e owns expert e
 __global__ void moe_scan_kernel(const int* __restrict__ counts, int* __restrict__ offsets,
-                                int* __restrict__ num_tiles, int* __restrict__ tile_expert,
-                                int* __restrict__ tile_row0, int E, int BM, int max_tiles) {
+                                int* __restrict__ num_tiles, int* __restrict__ active,
+                                int* __restrict__ tile_expert, int* __restrict__ tile_row0, int E, int BM,
+                                int max_tiles) {
   __shared__ int s_cnt[1024];
   __shared__ int s_til[1024];
+  __shared__ int s_act[1024];
   const int e = threadIdx.x;
   const int c = e < E ? counts[e] : 0;
   const int nt = (c + BM - 1) / BM;
   s_cnt[e] = c;
   s_til[e] = nt;
+  s_act[e] = c > 0;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
-    int a = 0, b = 0;
-    if (e >= o) { a = s_cnt[e - o]; b = s_til[e - o]; }
+    int a = 0, b = 0, d = 0;
+    if (e >= o) { a = s_cnt[e - o]; b = s_til[e - o]; d = s_act[e - o]; }
     __syncthreads();
     s_cnt[e] += a;
     s_til[e] += b;
+    s_act[e] += d;
     __syncthreads();
   }
   const int off = s_cnt[e] - c, toff = s_til[e] - nt;     // exclusive prefixes
   if (e < E) offsets[e] = off;
-  if (e == E - 1) { offsets[E] = s_cnt[e]; *num_tiles = min(s_til[e], max_tiles); }
+  if (c > 0) active[s_act[e] - 1] = e;                    // experts with rows, in index order
+  if (e == E - 1) { offsets[E] = s_cnt[e]; num_tiles[0] = min(s_til[e], max_tiles); num_tiles[1] = s_act[e]; }
   for (int i = 0; i < nt; ++i) {
     if (toff + i < max_tiles) {
       tile_expert[toff + i] = e;
@@ -147,11 +153,12 @@ extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan
   int* cursor = plan + E;
   int* offsets = plan + 2 * E;
   int* num_tiles = plan + 3 * E + 1;
-  cudaError_t err = cudaMemsetAsync(plan, 0, sizeof(int) * (size_t)(3 * E + 2), stream);
+  cudaError_t err = cudaMemsetAsync(plan, 0, sizeof(int) * (size_t)(3 * E + 4), stream);
   if (err != cudaSuccess) return (int)err;
   const int blocks = min((n_pairs + 255) / 256, 1024);
   moe_count_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, counts, status);
-  moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, offsets, num_tiles, tile_expert, tile_row0, E, BM, max_tiles);
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(counts, offsets, num_tiles, plan + 3 * E + 4, tile_expert, tile_row0, E,
+                                          BM, max_tiles);
   moe_scatter_kernel<<<blocks, 256, 0, stream>>>(idx, n_pairs, E, offsets, cursor, sorted_pair);
   QB_LAUNCH_CHECK();
   return 0;

@@ -75,7 +75,10 @@ class GQAttention(Mixer):
             inv_freq = torch.empty(0, dtype=torch.float32, device=x.device)
             pair_axis, rd = None, 0
         else:
-            inv_freq, pair_axis, rd, _ = tables
+            inv_freq, pair_axis, rd, n_axes = tables
+            if ctx.positions.dim() != 2 or ctx.positions.shape[1] < n_axes:
+                raise ValueError(f"the position encoding reads {n_axes} position axes; the step gives "
+                                 f"{tuple(ctx.positions.shape)}")
         kernels.qknorm_rope_write(
             qkv, q, cache.k if cache.write else None, cache.v if cache.write else None, self.q_norm_w,
             self.k_norm_w, _NORM_KIND[self.qk_norm], self.eps, inv_freq, pair_axis, ctx.positions, ctx.tok_pos,

@@ -80,10 +80,16 @@ class SigmoidTopKExperts(FeedForward):
         kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
         self.last_counts = plan[: self.E]
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
-        kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
-        kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
-                                 tile_expert, tile_row0, self.E, self.k)
+        if kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16:
+            # bfloat16: expert weights streamed once through the tensor cores
+            kernels.moe_stream(1, x, self.w13, act, sorted_pair, w.view(-1), plan, self.E, self.k, T)
+            kernels.moe_stream(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan, self.E,
+                               self.k, T)
+        else:
+            kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
+            kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
+                                     tile_expert, tile_row0, self.E, self.k)
         return y
 
 

@@ -228,9 +228,12 @@ def test_router_topk(E, k, bias, renorm, scale):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2)])
-def test_expert_products(dtype, T, H, I, E, k):
+@pytest.mark.parametrize("path", ["simt", "stream"])
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2)])
+def test_expert_products(dtype, T, H, I, E, k, path):
     kern = K()
+    if path == "stream" and dtype != torch.bfloat16:
+        pytest.skip("the streaming kernel is the bfloat16 path")
     torch.manual_seed(3)
     x = torch.randn(T, H, device=DEV).to(dtype)
     w13 = (0.1 * torch.randn(E, 2 * I, H, device=DEV)).to(dtype)
@@ -255,9 +258,16 @@ def test_expert_products(dtype, T, H, I, E, k):
     flat = idx.flatten()
     assert all(int(flat[p]) <= int(flat[q]) for p, q in zip(sorted_pair.tolist(), sorted_pair.tolist()[1:]))
     act = torch.empty(n_pairs, I, device=DEV, dtype=dtype)
-    kern.moe_grouped_simt(1, x, w13, act, sorted_pair, pw, plan, te, tr, E, k)
     y = torch.full((T, k, H), float("nan"), device=DEV)
-    kern.moe_grouped_simt(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, k)
+    if path == "simt":
+        kern.moe_grouped_simt(1, x, w13, act, sorted_pair, pw, plan, te, tr, E, k)
+        kern.moe_grouped_simt(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, k)
+    else:
+        assert kern.moe_stream_supported(x, H, I)
+        kern.moe_stream(1, x, w13, act, sorted_pair, pw.view(-1), plan, E, k, T)
+        kern.moe_stream(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, E, k, T)
+        active = plan[3 * E + 4: 3 * E + 4 + int(plan[3 * E + 2])].tolist()
+        assert active == [e for e in range(E) if int(counts[e]) > 0]
     xf = x.float()
     want = torch.empty(T, k, H, device=DEV)
     for t in range(T):

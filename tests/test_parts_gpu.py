@@ -19,12 +19,13 @@ DEV = "cuda:0"
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _ctx(T, pos=None, req=None, dtype=torch.float32):
+def _ctx(T, pos=None, req=None, dtype=torch.float32, n_axes=1):
     from quanta_b200 import kernels
     from quanta_b200.parts.base import StepContext
     pos = torch.arange(T, dtype=torch.int32) if pos is None else pos
     req = torch.zeros(T, dtype=torch.int32) if req is None else req
-    return StepContext(n_tokens=T, positions=pos.view(T, 1).to(DEV), tok_pos=pos.to(DEV), tok_req=req.to(DEV),
+    positions = pos.view(T, 1).repeat(1, n_axes).contiguous()      # a text token feeds its position to every axis
+    return StepContext(n_tokens=T, positions=positions.to(DEV), tok_pos=pos.to(DEV), tok_req=req.to(DEV),
                        req_slot=torch.zeros(1, dtype=torch.int32, device=DEV),
                        req_start=torch.tensor([0, T], dtype=torch.int32, device=DEV),
                        req_len_after=torch.tensor([T], dtype=torch.int32, device=DEV),
@@ -45,7 +46,7 @@ def test_norm_attention_experts_alone(model_dirs, plain_models, name):
     T, Hd = 21, cfg["H"]
     torch.manual_seed(0)
     x = torch.randn(T, Hd)
-    ctx = _ctx(T)
+    ctx = _ctx(T, n_axes=blk.mixer.position.n_axes)
     p = "model.layers.1."
     # norm
     h = x.clone().to(DEV)
