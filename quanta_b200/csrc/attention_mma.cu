@@ -1,0 +1,457 @@
+// Paged causal attention on the tensor cores (bfloat16 in, float32 softmax and accumulation).
+//
+// Two kernels share one inner loop (flash style: S = Q K^T by mma.m16n8k16, online softmax in
+// float32 with exp2, O += P V with P rounded to bfloat16):
+//
+//  * span kernel: a tile of 64 query rows of ONE request and ONE kv head, where a row is a
+//    (token, q head of the group) pair, so grouped heads fill the 16-row MMA operand.  Each row is
+//    masked by its own token's position, so prompt portions of any length run, from the cache that
+//    earlier steps and this step's rope kernel wrote.  K/V blocks of 64 keys are gathered page by
+//    page into shared memory with cp.async, double buffered.
+//  * decode kernel: one query token, one kv head and one fixed split of 256 keys per block, 64 keys
+//    per warp; the partial (max, sum, O) of each split goes to scratch and a merge kernel adds the
+//    splits in index order.  Split boundaries are multiples of 256 in absolute position, so a token's
+//    result does not depend on the batch.
+//
+// (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
+// probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
+// head_dim: any multiple of 16 up to 256 (template padding 64 / 128 / 256, dims past head_dim are zero).
+#include "common.cuh"
+
+namespace {
+
+constexpr int AT_BN = 64;            // keys per block (span kernel) and per warp (decode kernel)
+constexpr int AT_WARPS = 4;
+constexpr int AT_BM = 16 * AT_WARPS; // query rows per span tile
+constexpr int AT_SPLIT = AT_BN * AT_WARPS;   // keys per decode split
+constexpr int AT_PAD = 8;            // +16 bytes a row: ldmatrix rows fall on distinct banks
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather `n_keys` key rows starting at absolute position key0 of one request / kv head from the
+// pages into shared memory rows [n_keys][HDP + AT_PAD] (dims >= hd and keys outside [0, key_end] are
+// zero).  All threads of the block take part.
+template <int HDP>
+__device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ cache,
+                                              const int* __restrict__ bt, int key0, int n_keys, int key_end,
+                                              int kvh, int nkv, int hd, int page_size, int num_pages, int* status) {
+  constexpr int CH = HDP / 8;        // 16-byte chunks per row
+  for (int c = threadIdx.x; c < n_keys * CH; c += blockDim.x) {
+    const int r = c / CH, d = (c % CH) * 8;
+    const int key = key0 + r;
+    bool ok = key >= 0 && key <= key_end && d < hd;
+    const __nv_bfloat16* src = cache;
+    if (ok) {
+      const int page = bt[key / page_size];
+      if (page < 0 || page >= num_pages) {
+        qb_set_status(status, QB_STATUS_BAD_PAGE, page, 7);
+        ok = false;
+      } else {
+        src = cache + (((size_t)page * nkv + kvh) * page_size + key % page_size) * hd + d;
+      }
+    }
+    cp_async16(dst + (size_t)r * (HDP + AT_PAD) + d, src, ok);
+  }
+}
+
+// One warp: 16 query rows against AT_BN keys held in shared memory.
+//   qs: the warp's 16 rows [16][HDP+PAD]; ks, vs: [AT_BN][HDP+PAD]
+//   row_hi[2], row_lo[2]: last / first visible key of the thread's two rows (g and g+8), absolute
+//   key0: absolute position of ks row 0.   m, l, o: running max (log2 domain), partial sum, output.
+template <int HDP>
+__device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv_bfloat16* ks, const __nv_bfloat16* vs,
+                                             int key0, const int (&row_lo)[2], const int (&row_hi)[2],
+                                             float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HDP / 8][4]) {
+  constexpr int LD = HDP + AT_PAD;
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  float s[AT_BN / 8][4];
+#pragma unroll
+  for (int i = 0; i < AT_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < HDP / 16; ++kk) {
+    uint32_t a[4];
+    ldmatrix_x4(a, qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+    for (int nt = 0; nt < AT_BN / 16; ++nt) {
+      uint32_t b[4];
+      ldmatrix_x4(b, ks + (size_t)(nt * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+      mma16816(s[2 * nt], a, b[0], b[1]);
+      mma16816(s[2 * nt + 1], a, b[2], b[3]);
+    }
+  }
+  // scale, mask, running max
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < AT_BN / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + i * 8 + q * 2 + (e & 1), r = e >> 1;
+      const float v = (key >= row_lo[r] && key <= row_hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
+      s[i][e] = v;
+      mx[r] = fmaxf(mx[r], v);
+    }
+  float corr[2], msafe[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float mn = fmaxf(m[r], mx[r]);
+    msafe[r] = mn == -INFINITY ? 0.f : mn;
+    corr[r] = exp2f(m[r] - msafe[r]);          // m = -inf: 0
+    m[r] = mn;
+    l[r] *= corr[r];
+  }
+#pragma unroll
+  for (int i = 0; i < HDP / 8; ++i) {
+    o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+  }
+#pragma unroll
+  for (int i = 0; i < AT_BN / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = exp2f(s[i][e] - msafe[e >> 1]);
+      s[i][e] = p;
+      l[e >> 1] += p;
+    }
+  // O += P V
+#pragma unroll
+  for (int j = 0; j < AT_BN / 16; ++j) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+    a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+    a[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+    a[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+    for (int dt = 0; dt < HDP / 16; ++dt) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vs + (size_t)(j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dt * 16 + 8 * (lane >> 4));
+      mma16816(o[2 * dt], a, b[0], b[1]);
+      mma16816(o[2 * dt + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// span kernel.  tiles[t] = {request row, first token row of the span, tokens in the span, first
+// flattened row (token*G + head) of this tile}.  grid (n_tiles, n_kv).
+// ------------------------------------------------------------------------------------------------
+template <int HDP>
+__global__ void __launch_bounds__(AT_WARPS * 32)
+attn_span_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                 const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                 const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
+                 const int* __restrict__ tiles, int nq, int nkv, int hd, int page_size, int num_pages,
+                 float scale_log2, int window, int* status) {
+  constexpr int LD = HDP + AT_PAD;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [AT_BM][LD]
+  __nv_bfloat16* kbuf = qs + AT_BM * LD;                                        // [2][AT_BN][LD]
+  __nv_bfloat16* vbuf = kbuf + 2 * AT_BN * LD;                                  // [2][AT_BN][LD]
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
+  const int kvh = blockIdx.y, G = nq / nkv;
+  const int n_rows = min(AT_BM, n_tok * G - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
+  const int* bt = block_table + (size_t)req * bt_stride;
+
+  // Q rows -> shared memory (zero past head_dim and past the last row)
+  for (int c = tid; c < AT_BM * (HDP / 8); c += blockDim.x) {
+    const int r = c / (HDP / 8), d = (c % (HDP / 8)) * 8;
+    const int R = row0 + r;
+    const bool ok = r < n_rows && d < hd;
+    const __nv_bfloat16* src = q;
+    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd + d;
+    cp_async16(qs + (size_t)r * LD + d, src, ok);
+  }
+  // visible key range of this thread's two rows, and of the whole tile
+  int row_lo[2], row_hi[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int lr = warp * 16 + g + 8 * r;
+    if (lr < n_rows) {
+      const int p = tok_pos[tok0 + (row0 + lr) / G];
+      row_hi[r] = p;
+      row_lo[r] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    } else {
+      row_hi[r] = -1;
+      row_lo[r] = 0;
+    }
+  }
+  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
+  const int key_end = tok_pos[last_tok];
+  const int p_first = tok_pos[first_tok];
+  const int key_begin = (window > 0 && p_first - window + 1 > 0) ? (p_first - window + 1) / AT_BN * AT_BN : 0;
+  const int n_blocks = (key_end - key_begin) / AT_BN + 1;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HDP / 8][4];
+#pragma unroll
+  for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  load_kv_block<HDP>(kbuf, k_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status);
+  load_kv_block<HDP>(vbuf, v_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status);
+  cp_async_commit();
+  for (int b = 0; b < n_blocks; ++b) {
+    const int cur = b & 1;
+    if (b + 1 < n_blocks) {
+      const int k0n = key_begin + (b + 1) * AT_BN;
+      load_kv_block<HDP>(kbuf + (cur ^ 1) * AT_BN * LD, k_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
+                         num_pages, status);
+      load_kv_block<HDP>(vbuf + (cur ^ 1) * AT_BN * LD, v_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
+                         num_pages, status);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = key_begin + b * AT_BN;
+    // a warp whose rows all end before this block (or start after it) has nothing to add
+    int any_hi = max(row_hi[0], row_hi[1]);
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 4));
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 8));
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 16));
+    if (any_hi >= key0)
+      attend_block<HDP>(qs + (size_t)warp * 16 * LD, kbuf + cur * AT_BN * LD, vbuf + cur * AT_BN * LD, key0, row_lo,
+                        row_hi, scale_log2, m, l, o);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int lr = warp * 16 + g + 8 * r;
+    if (lr >= n_rows) continue;
+    const int R = row0 + lr;
+    __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+#pragma unroll
+    for (int i = 0; i < HDP / 8; ++i) {
+      const int d = i * 8 + qd * 2;
+      if (d < hd) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode kernel: grid (n_splits_max, n_kv, n_decode_tokens); dec_tok[z] = token row.  The block has
+// W warps (4, or 2 for head_dim > 128) and owns the W*64 keys [split*W*64, (split+1)*W*64).
+// scratch: part_o float [n_dec][nq][n_splits_max][hd], part_ml float [n_dec][nq][n_splits_max][2]
+// ------------------------------------------------------------------------------------------------
+template <int HDP>
+__global__ void __launch_bounds__(AT_WARPS * 32)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                   const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const int* __restrict__ dec_tok, const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
+                   const int* __restrict__ block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
+                   int num_pages, float scale_log2, int window, int n_splits_max, int* status) {
+  constexpr int LD = HDP + AT_PAD;
+  const int n_warps = blockDim.x >> 5, split_keys = n_warps * AT_BN;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [16][LD]
+  __nv_bfloat16* kbuf = qs + 16 * LD;                                           // [split_keys][LD]
+  __nv_bfloat16* vbuf = kbuf + (size_t)split_keys * LD;                         // [split_keys][LD]
+  float* red = reinterpret_cast<float*>(vbuf + (size_t)split_keys * LD);        // [n_warps][16][HDP + 2]
+  const int z = blockIdx.z, t = dec_tok[z];
+  const int kvh = blockIdx.y, split = blockIdx.x, G = nq / nkv;
+  const int pos = tok_pos[t];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int key0 = split * split_keys;
+  if (key0 > pos || key0 + split_keys <= lo) return;          // this split holds no visible key
+  const int* bt = block_table + (size_t)tok_req[t] * bt_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
+  const int n_keys = min(split_keys, pos - key0 + 1);
+  const int keys_pad = (n_keys + AT_BN - 1) / AT_BN * AT_BN;
+
+  load_kv_block<HDP>(kbuf, k_cache, bt, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status);
+  load_kv_block<HDP>(vbuf, v_cache, bt, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status);
+  cp_async_commit();
+
+  for (int rb = 0; rb < G; rb += 16) {                        // 16 heads of the group at a time
+    __syncthreads();
+    for (int c = tid; c < 16 * (HDP / 8); c += blockDim.x) {
+      const int r = c / (HDP / 8), d = (c % (HDP / 8)) * 8;
+      const bool ok = rb + r < G && d < hd;
+      const __nv_bfloat16* src = ok ? q + ((size_t)t * nq + kvh * G + rb + r) * hd + d : q;
+      cp_async16(qs + (size_t)r * LD + d, src, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HDP / 8][4];
+#pragma unroll
+    for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    int row_lo[2], row_hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const bool ok = rb + g + 8 * r < G;
+      row_hi[r] = ok ? pos : -1;
+      row_lo[r] = lo;
+    }
+    if (warp * AT_BN < n_keys)
+      attend_block<HDP>(qs, kbuf + (size_t)warp * AT_BN * LD, vbuf + (size_t)warp * AT_BN * LD, key0 + warp * AT_BN,
+                        row_lo, row_hi, scale_log2, m, l, o);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // every warp leaves (m, l, O) of its 64 keys; rows are merged in warp order
+    float* mine = red + (size_t)warp * 16 * (HDP + 2);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float* row = mine + (size_t)(g + 8 * r) * (HDP + 2);
+      if (qd == 0) { row[HDP] = m[r]; row[HDP + 1] = l[r]; }
+#pragma unroll
+      for (int i = 0; i < HDP / 8; ++i) {
+        row[i * 8 + qd * 2] = o[i][2 * r];
+        row[i * 8 + qd * 2 + 1] = o[i][2 * r + 1];
+      }
+    }
+    __syncthreads();
+    for (int c = tid; c < 16 * hd; c += blockDim.x) {
+      const int r = c / hd, d = c % hd;
+      if (rb + r >= G) continue;
+      float M = -INFINITY;
+      for (int w = 0; w < n_warps; ++w) M = fmaxf(M, red[((size_t)w * 16 + r) * (HDP + 2) + HDP]);
+      float acc = 0.f, L = 0.f;
+      for (int w = 0; w < n_warps; ++w) {
+        const float* row = red + ((size_t)w * 16 + r) * (HDP + 2);
+        const float f = row[HDP] == -INFINITY ? 0.f : exp2f(row[HDP] - M);
+        acc += f * row[d];
+        L += f * row[HDP + 1];
+      }
+      const int head = kvh * G + rb + r;
+      const size_t slot = ((size_t)z * nq + head) * n_splits_max + split;
+      part_o[slot * hd + d] = acc;
+      if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+    }
+  }
+}
+
+// out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits that hold visible keys
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  __nv_bfloat16* __restrict__ out, const int* __restrict__ dec_tok,
+                                  const int* __restrict__ tok_pos, int nq, int hd, int window, int n_splits_max,
+                                  int split_keys) {
+  const int z = blockIdx.y, t = dec_tok[z], head = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int s_first = lo / split_keys, s_last = min(pos / split_keys, n_splits_max - 1);
+  const size_t base = ((size_t)z * nq + head) * n_splits_max;
+  float M = -INFINITY;
+  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f, L = 0.f;
+    for (int s = s_first; s <= s_last; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+      acc += f * part_o[(base + s) * hd + d];
+      L += f * part_ml[(base + s) * 2 + 1];
+    }
+    out[((size_t)t * nq + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+template <typename Kern>
+int set_smem(Kern kern, size_t smem) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
+                            const int* block_table, int bt_stride, const int* tiles, int n_tiles, int nq, int nkv,
+                            int hd, int page_size, int num_pages, float scale, int window, int* status,
+                            cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535) return QB_ERR_UNSUPPORTED;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_tiles, nkv);
+#define QB_SPAN(HDP)                                                                                       \
+  do {                                                                                                     \
+    const size_t smem = (size_t)(AT_BM + 4 * AT_BN) * (HDP + AT_PAD) * 2;                                   \
+    int rc = set_smem(attn_span_kernel<HDP>, smem);                                                        \
+    if (rc) return rc;                                                                                     \
+    attn_span_kernel<HDP><<<grid, AT_WARPS * 32, smem, stream>>>(                                          \
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,              \
+        (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv, hd, page_size, num_pages,     \
+        scale_log2, window, status);                                                                       \
+  } while (0)
+  if (hd <= 64) QB_SPAN(64);
+  else if (hd <= 128) QB_SPAN(128);
+  else QB_SPAN(256);
+#undef QB_SPAN
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// Keys per decode split for a head size (the Python side sizes the scratch with it).
+extern "C" int qb_attn_decode_split_keys(int hd) { return (hd <= 128 ? AT_WARPS : 2) * AT_BN; }
+
+// Scratch, in floats: part_o n_dec*nq*n_splits_max*hd, part_ml n_dec*nq*n_splits_max*2, where
+// n_splits_max >= ceil(longest context / split keys).
+extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
+                              float* part_ml, const int* dec_tok, int n_dec, const int* tok_pos, const int* tok_req,
+                              const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
+                              int num_pages, float scale, int window, int n_splits_max, int* status,
+                              cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535 || n_dec > 65535 || n_splits_max <= 0)
+    return QB_ERR_UNSUPPORTED;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int warps = hd <= 128 ? AT_WARPS : 2, split_keys = warps * AT_BN;
+  dim3 grid(n_splits_max, nkv, n_dec);
+#define QB_DEC(HDP)                                                                                        \
+  do {                                                                                                     \
+    const size_t smem = (size_t)(16 + 2 * split_keys) * (HDP + AT_PAD) * 2 + (size_t)warps * 16 * (HDP + 2) * 4; \
+    int rc = set_smem(attn_decode_kernel<HDP>, smem);                                                      \
+    if (rc) return rc;                                                                                     \
+    attn_decode_kernel<HDP><<<grid, warps * 32, smem, stream>>>(                                           \
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_o, part_ml, \
+        dec_tok, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, num_pages, scale_log2,   \
+        window, n_splits_max, status);                                                                     \
+  } while (0)
+  if (hd <= 64) QB_DEC(64);
+  else if (hd <= 128) QB_DEC(128);
+  else QB_DEC(256);
+#undef QB_DEC
+  attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, tok_pos, nq,
+                                                         hd, window, n_splits_max, split_keys);
+  QB_LAUNCH_CHECK();
+  return 0;
+}

@@ -147,7 +147,11 @@ class Engine:
                 flat.extend([-1] * (max_pages - len(row[:max_pages])))
             tables.append(flat)
         positions = tok_pos if self.n_axes == 1 else [p for p in tok_pos for _ in range(self.n_axes)]
-        pieces = [token_ids, tok_pos, tok_req, positions, req_start, req_len_after, req_slot, want_rows, *tables]
+        dec_rows = [req_start[r] for r in range(R) if req_start[r + 1] - req_start[r] == 1]
+        spans = [(r, req_start[r], req_start[r + 1] - req_start[r]) for r in range(R)
+                 if req_start[r + 1] - req_start[r] > 1]
+        pieces = [token_ids, tok_pos, tok_req, positions, req_start, req_len_after, req_slot, want_rows, dec_rows,
+                  *tables]
         total = sum(len(p) for p in pieces)
         host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=True)
         flat_all = [x for p in pieces for x in p]
@@ -158,13 +162,14 @@ class Engine:
         for p in pieces:
             out.append(dev[off: off + len(p)])
             off += len(p)
-        d_ids, d_pos, d_req, d_positions, d_start, d_len, d_slot, d_want = out[:8]
-        d_tables = [t.view(R, max_pages) for t in out[8:]]
+        d_ids, d_pos, d_req, d_positions, d_start, d_len, d_slot, d_want, d_dec = out[:9]
+        d_tables = [t.view(R, max_pages) for t in out[9:]]
         ctx = StepContext(
             n_tokens=T, positions=d_positions.view(T, self.n_axes), tok_pos=d_pos, tok_req=d_req, req_slot=d_slot,
             req_start=d_start, req_len_after=d_len, status=self.status, dtype=self.model.dtype,
             max_new_tokens_per_req=max(len(e.tokens) for e in entries), max_len_after=max_len_after,
-            host={"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot})
+            host={"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot},
+            dec_tok=d_dec if dec_rows else None, n_dec=len(dec_rows), spans=spans)
         caches = []
         for pos, entry in enumerate(self.model.schedule):
             src = pos if entry.read_cache_of is None else entry.read_cache_of

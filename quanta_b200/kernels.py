@@ -175,6 +175,44 @@ def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table
         _p(status), _stream()), "paged_attention_simt")
 
 
+ATTN_SPAN_ROWS = 64          # query rows (token x head-of-group) per tile of the span kernel
+
+
+def attn_decode_split_keys(hd: int) -> int:
+    return int(lib().qb_attn_decode_split_keys(int(hd)))
+
+
+def attn_span(q, k_cache, v_cache, out, tok_pos, block_table, tiles, scale: float, window: int, status) -> None:
+    """bfloat16 tensor-core attention for prompt portions.  ``tiles`` int32 [n, 4]: request row, first
+    token row of the portion, tokens in the portion, first flattened (token*G + head) row of the tile."""
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    _want(q, torch.bfloat16, "q"); _want(k_cache, torch.bfloat16, "k_cache"); _want(tiles, torch.int32, "tiles")
+    if hd2 != hd or out.shape != q.shape or out.dtype != q.dtype:
+        raise ValueError("attn_span: shape/dtype mismatch")
+    _check(lib().qb_attn_span(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(tok_pos), _p(block_table),
+                              block_table.shape[1], _p(tiles), tiles.shape[0], nq, nkv, hd, page_size, num_pages,
+                              ctypes.c_float(scale), int(window), _p(status), _stream()), "attn_span")
+
+
+def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec: int, tok_pos, tok_req, block_table,
+                scale: float, window: int, n_splits_max: int, status) -> None:
+    """bfloat16 tensor-core attention for single tokens, split over the keys; ``part_o`` / ``part_ml``
+    are float32 scratch of at least n_dec*nq*n_splits_max*hd and n_dec*nq*n_splits_max*2 elements."""
+    T, nq, hd = q.shape
+    num_pages, nkv, page_size, hd2 = k_cache.shape
+    _want(q, torch.bfloat16, "q"); _want(k_cache, torch.bfloat16, "k_cache")
+    _want(part_o, torch.float32, "part_o"); _want(part_ml, torch.float32, "part_ml"); _want(dec_tok, torch.int32, "dec_tok")
+    if hd2 != hd or out.shape != q.shape or out.dtype != q.dtype:
+        raise ValueError("attn_decode: shape/dtype mismatch")
+    if part_o.numel() < n_dec * nq * n_splits_max * hd or part_ml.numel() < n_dec * nq * n_splits_max * 2:
+        raise ValueError("attn_decode: scratch too small")
+    _check(lib().qb_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_ml), _p(dec_tok),
+                                int(n_dec), _p(tok_pos), _p(tok_req), _p(block_table), block_table.shape[1], nq, nkv,
+                                hd, page_size, num_pages, ctypes.c_float(scale), int(window), int(n_splits_max),
+                                _p(status), _stream()), "attn_decode", 2)
+
+
 def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
     """``out[M,N] = a[M,K] @ b[N,K].T`` in float32 on the CUDA cores, fixed summation order."""
     M, K = a.shape

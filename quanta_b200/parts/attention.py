@@ -88,5 +88,40 @@ class GQAttention(Mixer):
         return linear(out.view(T, self.nq * self.hd), self.w_o)
 
     def attend(self, q, cache, out, ctx):
-        kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
-                                     self.scale, self.window or 0, ctx.status)
+        """float32: the SIMT kernel, every token alike.  bfloat16: tensor-core kernels, one for single
+        tokens (split over the keys) and one for portions (tiles of 64 token-by-head rows)."""
+        window = self.window or 0
+        if q.dtype != torch.bfloat16:
+            kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
+                                         self.scale, window, ctx.status)
+            return
+        dec_tok, n_dec, spans = step_work(ctx, q.device)
+        if n_dec:
+            split = kernels.attn_decode_split_keys(self.hd)
+            n_splits = max(1, -(-ctx.max_len_after // split))
+            part_o = torch.empty(n_dec * self.nq * n_splits * self.hd, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(n_dec * self.nq * n_splits * 2, dtype=torch.float32, device=q.device)
+            kernels.attn_decode(q, cache.k, cache.v, out, part_o, part_ml, dec_tok, n_dec, ctx.tok_pos, ctx.tok_req,
+                                cache.block_table, self.scale, window, n_splits, ctx.status)
+        if spans:
+            G = self.nq // self.nkv
+            key = ("span_tiles", G)
+            if key not in ctx.work:
+                rows = kernels.ATTN_SPAN_ROWS
+                tiles = [[r, t0, n, r0] for (r, t0, n) in spans for r0 in range(0, n * G, rows)]
+                ctx.work[key] = torch.tensor(tiles, dtype=torch.int32).to(q.device, non_blocking=True)
+            kernels.attn_span(q, cache.k, cache.v, out, ctx.tok_pos, cache.block_table, ctx.work[key], self.scale,
+                              window, ctx.status)
+
+
+def step_work(ctx, device):
+    """(token rows of single-token requests, their number, portions of the other requests)."""
+    if ctx.spans is None and ctx.dec_tok is None:
+        starts = ctx.host.get("req_start") or [0, ctx.n_tokens]
+        dec, spans = [], []
+        for r in range(len(starts) - 1):
+            n = starts[r + 1] - starts[r]
+            (dec.append(starts[r]) if n == 1 else spans.append((r, starts[r], n)))
+        ctx.spans, ctx.n_dec = spans, len(dec)
+        ctx.dec_tok = torch.tensor(dec, dtype=torch.int32).to(device, non_blocking=True) if dec else None
+    return ctx.dec_tok, ctx.n_dec, ctx.spans or []

@@ -96,6 +96,13 @@ class StepContext:
     max_new_tokens_per_req: int = 0    # largest portion in the step
     max_len_after: int = 0             # largest req_len_after (host copy, for launch sizing)
     host: dict = field(default_factory=dict)   # host copies of the small arrays, for parts that need them
+    # how the step's tokens fall into requests, for mixers that treat single tokens and portions
+    # differently: rows of requests that bring exactly one token, and (request row, first token row,
+    # tokens) of the others.  None: derived from host["req_start"], or one portion holding everything.
+    dec_tok: torch.Tensor | None = None        # int32 [n_dec] token rows (device)
+    n_dec: int = 0
+    spans: list | None = None
+    work: dict = field(default_factory=dict)   # per-step scratch shared by the layers (tile lists and the like)
 
 
 class Part:
