@@ -13,20 +13,26 @@
 // routing: one warp per token
 // ---------------------------------------------------------------------------------------------
 template <int NPL>   // experts per lane, E <= 32*NPL
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                   int* __restrict__ idx_out, float* __restrict__ w_out, int T, int E,
-                                   int k, int renorm, float scale) {
+__global__ void router_topk_kernel(const float* __restrict__ logits, int n_partials,
+                                   const float* __restrict__ bias, int* __restrict__ idx_out,
+                                   float* __restrict__ w_out, int T, int E, int k, int renorm, float scale) {
+  // logits: [n_partials][T][E]; the partial products of the inner dimension are added in index order
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
-  float choice[NPL];
+  const size_t pstride = (size_t)T * E;
+  float choice[NPL], score[NPL];
   unsigned taken = 0u;
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
+    score[i] = 0.f;
     if (e < E) {
-      const float s = 1.f / (1.f + expf(-lg[e]));
+      float x = lg[e];
+      for (int p = 1; p < n_partials; ++p) x += lg[p * pstride + e];
+      const float s = 1.f / (1.f + expf(-x));
+      score[i] = s;
       choice[i] = bias ? s + bias[e] : s;
     } else {
       choice[i] = -INFINITY;
@@ -52,8 +58,14 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
       const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi));
       if (take) { bv = ov; bi = oi; }
     }
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    const float sc = 1.f / (1.f + expf(-lg[bi]));
+    float mine = 0.f;
+    if ((bi & 31) == lane) {
+      taken |= 1u << (bi >> 5);
+#pragma unroll
+      for (int i = 0; i < NPL; ++i)
+        if (i == (bi >> 5)) mine = score[i];
+    }
+    const float sc = __shfl_sync(0xffffffffu, mine, bi & 31);     // the bias-free score of the chosen expert
     sum += sc;
     if (lane == 0) {
       idx_out[(size_t)t * k + r] = bi;
@@ -65,13 +77,13 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
   for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = w_out[(size_t)t * k + r] / denom * scale;
 }
 
-extern "C" int qb_router_topk(const float* logits, const float* bias, int* idx_out, float* w_out, int T,
-                              int E, int k, int renorm, float scale, cudaStream_t stream) {
+extern "C" int qb_router_topk(const float* logits, int n_partials, const float* bias, int* idx_out, float* w_out,
+                              int T, int E, int k, int renorm, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (k <= 0 || k > E) return QB_ERR_BAD_ARG;
+  if (k <= 0 || k > E || n_partials <= 0) return QB_ERR_BAD_ARG;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
   const int warps = 4, blocks = (T + warps - 1) / warps;
-#define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, bias, idx_out, w_out, T, E, k, renorm, scale)
+#define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale)
   if (E <= 32) QB_ROUTE(1);
   else if (E <= 64) QB_ROUTE(2);
   else if (E <= 128) QB_ROUTE(4);

@@ -23,7 +23,7 @@ constexpr int MS_ROWS = 16;     // output features per block
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -31,7 +31,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
@@ -102,27 +102,46 @@ moe_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[m][t][i] = 0.f;
 
-#pragma unroll 4
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
-      const int k = kb * 32 + q * 8;
-      const bool k_ok = k < K;
-      uint4 wa[NM], wb[NM];
+    // Weights are fetched a group of U k-blocks ahead of the MMAs that use them, in two register
+    // buffers, so that a thread always has a group of 16-byte loads in flight.
+    constexpr int U = MODE == 1 ? 2 : 4;
+    uint4 bufA[U][NM][2], bufB[U][NM][2];
+    auto fetch = [&](uint4 (&buf)[U][NM][2], int kb0) {
 #pragma unroll
-      for (int m = 0; m < NM; ++m) {
-        wa[m] = (k_ok && ra_ok) ? ld_stream16(wrow[m][0] + k) : make_uint4(0u, 0u, 0u, 0u);
-        wb[m] = (k_ok && rb_ok) ? ld_stream16(wrow[m][1] + k) : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        const int xr = t * 8 + g;
-        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
-        if (xr < smem_rows) xb = *reinterpret_cast<const uint4*>(xs + (size_t)xr * x_stride + k);
+      for (int u = 0; u < U; ++u) {
+        const int k = (kb0 + u) * 32 + q * 8;
+        const bool k_ok = kb0 + u < kb_end && k < K;
 #pragma unroll
         for (int m = 0; m < NM; ++m) {
-          mma_bf16_16816(acc[m][t], wa[m].x, wb[m].x, wa[m].y, wb[m].y, xb.x, xb.y);
-          mma_bf16_16816(acc[m][t], wa[m].z, wb[m].z, wa[m].w, wb[m].w, xb.z, xb.w);
+          buf[u][m][0] = (k_ok && ra_ok) ? ld_stream16(wrow[m][0] + k) : make_uint4(0u, 0u, 0u, 0u);
+          buf[u][m][1] = (k_ok && rb_ok) ? ld_stream16(wrow[m][1] + k) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
+    };
+    auto consume = [&](const uint4 (&buf)[U][NM][2], int kb0) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (kb0 + u >= kb_end) break;
+        const int k = (kb0 + u) * 32 + q * 8;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const int xr = t * 8 + g;
+          uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+          if (xr < smem_rows) xb = *reinterpret_cast<const uint4*>(xs + (size_t)xr * x_stride + k);
+#pragma unroll
+          for (int m = 0; m < NM; ++m) {
+            mma_bf16_16816(acc[m][t], buf[u][m][0].x, buf[u][m][1].x, buf[u][m][0].y, buf[u][m][1].y, xb.x, xb.y);
+            mma_bf16_16816(acc[m][t], buf[u][m][0].z, buf[u][m][1].z, buf[u][m][0].w, buf[u][m][1].w, xb.z, xb.w);
+          }
+        }
+      }
+    };
+    fetch(bufA, kb_begin);
+    for (int kb = kb_begin; kb < kb_end; kb += 2 * U) {
+      fetch(bufB, kb + U);
+      consume(bufA, kb);
+      fetch(bufA, kb + 2 * U);
+      consume(bufB, kb + U);
     }
 
     // partial sums of warps 1.. go through shared memory and are added in warp order by warp 0

@@ -6,6 +6,10 @@ two: it prefills one request alone, src/quanta/minimax/batched_runtime_m3.py:409
 token for each of B requests, :172-187.)  The step reserves pages, packs the small integer arrays
 into one pinned buffer, copies it once, runs the model on exactly these tokens, and returns float32
 logits at the wanted places.  Nothing inside synchronises with the host.
+
+Steps in which every request brings exactly one token (decoding) are launch-bound when run kernel
+by kernel, so they are captured once per (batch size, context bucket) in a CUDA graph and replayed:
+the graph reads its integers from a fixed device buffer that each step overwrites.
 """
 
 from __future__ import annotations
@@ -15,7 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import kernels
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, OutOfPages, OutOfSlots
 from ..parts.base import LayerCache, PositionEncoding, StepContext
 
 
@@ -26,8 +30,21 @@ class StepEntry:
     want: tuple = ()          # indices into ``tokens`` whose logits are returned
 
 
+class _DecodeGraph:
+    """A captured decode step for one (batch size, context bucket)."""
+
+    def __init__(self):
+        self.graph = None
+        self.seen = 0             # eager runs at this shape before the capture
+        self.dev = None           # the fixed device buffer of the step's integers
+        self.host = None          # its pinned host twin
+        self.logits = None
+        self.launches = 0
+
+
 class Engine:
-    def __init__(self, model, *, num_pages: int, page_size: int = 16, max_requests: int = 64):
+    def __init__(self, model, *, num_pages: int, page_size: int = 16, max_requests: int = 64,
+                 use_graphs: bool = True):
         if not model.loaded:
             raise RuntimeError("the model has no weights yet")
         self.model = model
@@ -54,6 +71,10 @@ class Engine:
         self.steps = 0
         self.tokens_run = 0
         self.last_h2d_bytes = 0
+        # graphs only when every part says its step reads nothing from the host
+        self.use_graphs = bool(use_graphs) and all(getattr(p, "graph_safe", False) for p in model.parts())
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self.graph_replays = 0
 
     # ---- requests -----------------------------------------------------------------------------------
     def _admit(self, rid) -> None:
@@ -76,8 +97,9 @@ class Engine:
     # ---- the step -------------------------------------------------------------------------------------
     def step(self, entries: list[StepEntry], end=()) -> torch.Tensor | None:
         """Run one batch.  Returns logits ``[wanted, vocab]`` float32 on the device, in the order of the
-        entries and of each entry's ``want``; None if nothing is wanted.  ``end`` lists requests that
-        are finished after this step: their pages and slot are given back."""
+        entries and of each entry's ``want``; None if nothing is wanted.  The tensor may be overwritten
+        by the next step.  ``end`` lists requests that are finished after this step: their pages and
+        slot are given back."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         mgr = self.manager
         seen = set()
@@ -95,22 +117,21 @@ class Engine:
                     raise ValueError(f"request {e.rid!r}: wanted place {w} outside its {len(e.tokens)} tokens")
         new = [e.rid for e in entries if not mgr.has(e.rid)]
         if len(new) > mgr.slots.free_count:
-            from ..cache.manager import OutOfSlots
             raise OutOfSlots(f"{len(new)} new request(s), {mgr.slots.free_count} free state slots")
+        wants = {e.rid: (mgr.length(e.rid) if mgr.has(e.rid) else 0) + len(e.tokens) for e in entries}
+        if not mgr.can_reserve(wants):
+            raise OutOfPages(f"the step needs more pages than are free: {mgr.stats()['groups']}")
         for rid in new:
             self._admit(rid)
-        wants = {e.rid: mgr.length(e.rid) + len(e.tokens) for e in entries}
-        if not mgr.can_reserve(wants):
-            for rid in new:
-                mgr.free(rid)
-            from ..cache.manager import OutOfPages
-            raise OutOfPages(f"the step needs more pages than are free: {mgr.stats()['groups']}")
         for rid, n in wants.items():
             mgr.reserve(rid, n)
 
         logits = None
         if entries:
-            logits = self._run(entries)
+            if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+                logits = self._run_decode(entries)
+            else:
+                logits = self._run(entries)
             for e in entries:
                 mgr.advance(e.rid, len(e.tokens))
             self.steps += 1
@@ -119,11 +140,12 @@ class Engine:
             self.release(rid)
         return logits
 
-    def _run(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        mgr, ps = self.manager, self.page_size
-        R = len(entries)
-        T = sum(len(e.tokens) for e in entries)
+    # ---- packing the step's integers ---------------------------------------------------------------------
+    def _pack(self, entries: list[StepEntry], max_pages: int) -> tuple[list, dict]:
+        """The step's integer arrays as python lists, in the fixed order of the device buffer."""
+        mgr = self.manager
         rids = [e.rid for e in entries]
+        R = len(entries)
         token_ids, tok_pos, tok_req, want_rows = [], [], [], []
         req_start, req_len_after, req_slot = [0], [], []
         for r, e in enumerate(entries):
@@ -137,8 +159,6 @@ class Engine:
             req_start.append(row0 + n)
             req_len_after.append(base + n)
             req_slot.append(mgr.slot(e.rid))
-        max_len_after = max(req_len_after)
-        max_pages = -(-max_len_after // ps)
         tables = []
         for g in range(len(mgr.groups)):
             flat = []
@@ -152,30 +172,96 @@ class Engine:
                  if req_start[r + 1] - req_start[r] > 1]
         pieces = [token_ids, tok_pos, tok_req, positions, req_start, req_len_after, req_slot, want_rows, dec_rows,
                   *tables]
-        total = sum(len(p) for p in pieces)
-        host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=True)
-        flat_all = [x for p in pieces for x in p]
-        host[:total] = torch.tensor(flat_all, dtype=torch.int32)
-        dev = host.to(self.device, non_blocking=True)
-        self.last_h2d_bytes = total * 4
+        info = {"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot, "spans": spans,
+                "n_dec": len(dec_rows), "n_want": len(want_rows)}
+        return pieces, info
+
+    def _context(self, dev: torch.Tensor, sizes: list[int], R: int, T: int, max_pages: int, info: dict,
+                 max_len_after: int, max_new: int, with_host: bool):
         out, off = [], 0
-        for p in pieces:
-            out.append(dev[off: off + len(p)])
-            off += len(p)
+        for n in sizes:
+            out.append(dev[off: off + n])
+            off += n
         d_ids, d_pos, d_req, d_positions, d_start, d_len, d_slot, d_want, d_dec = out[:9]
         d_tables = [t.view(R, max_pages) for t in out[9:]]
         ctx = StepContext(
             n_tokens=T, positions=d_positions.view(T, self.n_axes), tok_pos=d_pos, tok_req=d_req, req_slot=d_slot,
             req_start=d_start, req_len_after=d_len, status=self.status, dtype=self.model.dtype,
-            max_new_tokens_per_req=max(len(e.tokens) for e in entries), max_len_after=max_len_after,
-            host={"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot},
-            dec_tok=d_dec if dec_rows else None, n_dec=len(dec_rows), spans=spans)
+            max_new_tokens_per_req=max_new, max_len_after=max_len_after,
+            host={k: info[k] for k in ("req_start", "req_len_after", "req_slot")} if with_host else {},
+            dec_tok=d_dec if info["n_dec"] else None, n_dec=info["n_dec"], spans=info["spans"])
         caches = []
         for pos, entry in enumerate(self.model.schedule):
             src = pos if entry.read_cache_of is None else entry.read_cache_of
             if src in self.kv:
                 k, v = self.kv[src]
-                caches.append(LayerCache(k, v, ps, d_tables[mgr.group_of[src]], write=entry.read_cache_of is None))
+                caches.append(LayerCache(k, v, self.page_size, d_tables[self.manager.group_of[src]],
+                                         write=entry.read_cache_of is None))
             else:
                 caches.append(None)
-        return self.model.forward(d_ids, ctx, caches, self.state, d_want if want_rows else None)
+        return d_ids, d_want, ctx, caches
+
+    # ---- eager ---------------------------------------------------------------------------------------------
+    def _run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        mgr, ps = self.manager, self.page_size
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        max_len_after = max(mgr.length(e.rid) + len(e.tokens) for e in entries)
+        max_pages = -(-max_len_after // ps)
+        pieces, info = self._pack(entries, max_pages)
+        sizes = [len(p) for p in pieces]
+        total = sum(sizes)
+        host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=True)
+        host[:total] = torch.tensor([x for p in pieces for x in p], dtype=torch.int32)
+        dev = host.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = total * 4
+        d_ids, d_want, ctx, caches = self._context(dev, sizes, R, T, max_pages, info, max_len_after,
+                                                   max(len(e.tokens) for e in entries), with_host=True)
+        return self.model.forward(d_ids, ctx, caches, self.state, d_want if info["n_want"] else None)
+
+    # ---- decoding through a captured graph ----------------------------------------------------------------------
+    def _run_decode(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        mgr, ps = self.manager, self.page_size
+        B = len(entries)
+        max_len_after = max(mgr.length(e.rid) + 1 for e in entries)
+        bucket = 512
+        while bucket < max_len_after:
+            bucket *= 2
+        key = (B, bucket)
+        g = self._graphs.setdefault(key, _DecodeGraph())
+        if g.graph is None and g.seen < 1:
+            g.seen += 1
+            return self._run(entries)            # first time at this shape: eager (also warms the libraries up)
+        max_pages = -(-bucket // ps)
+        # every row's logits are computed inside the graph; the wanted ones are picked afterwards
+        full = [StepEntry(e.rid, e.tokens, (0,)) for e in entries]
+        pieces, info = self._pack(full, max_pages)
+        sizes = [len(p) for p in pieces]
+        total = sum(sizes)
+        if g.graph is None:
+            g.dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        # a fresh pinned buffer every step: the host may run ahead of the device, and the pinned
+        # allocator does not hand a block out again before the copy that reads it is done
+        host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        host.copy_(torch.tensor([x for p in pieces for x in p], dtype=torch.int32))
+        g.dev.copy_(host, non_blocking=True)
+        self.last_h2d_bytes = total * 4
+        if g.graph is None:
+            d_ids, d_want, ctx, caches = self._context(g.dev, sizes, B, B, max_pages, info, bucket, 1, with_host=False)
+            torch.cuda.synchronize()
+            before = kernels.LAUNCHES
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g.logits = self.model.forward(d_ids, ctx, caches, self.state, d_want)
+            g.launches = kernels.LAUNCHES - before
+            g.graph = graph
+        else:
+            kernels.LAUNCHES += g.launches
+        g.graph.replay()
+        self.graph_replays += 1
+        want = [r for r, e in enumerate(entries) for _ in e.want]
+        if not want:
+            return None
+        if want == list(range(B)):
+            return g.logits
+        return g.logits[torch.tensor(want, device=self.device)]

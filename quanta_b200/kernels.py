@@ -213,23 +213,28 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec: int, 
                                 _p(status), _stream()), "attn_decode", 2)
 
 
-def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[M,N] = a[M,K] @ b[N,K].T`` in float32 on the CUDA cores, fixed summation order."""
+def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, k_chunk: int = 0) -> None:
+    """``out[M,N] = a[M,K] @ b[N,K].T`` in float32 on the CUDA cores, fixed summation order.  With
+    ``k_chunk`` (a multiple of 16) ``out`` is ``[ceil(K/k_chunk), M, N]``: partial products of the
+    chunks of the inner dimension, to be added in index order by the consumer."""
     M, K = a.shape
     N = b.shape[0]
-    if b.shape[1] != K or out.shape != (M, N):
+    want = (M, N) if not k_chunk else (-(-K // k_chunk), M, N)
+    if b.shape[1] != K or tuple(out.shape) != want:
         raise ValueError("gemm_nt_simt: shape mismatch")
     _check(lib().qb_gemm_nt_simt(_p(a), _code(a), _p(b), _code(b), _p(out), _code(out), M, N, K, K, K, N,
-                                 _stream()), "gemm_nt_simt")
+                                 int(k_chunk), _stream()), "gemm_nt_simt")
 
 
 def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> None:
+    """``logits`` [T, E], or [P, T, E] partial sums that are added in index order first."""
     _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
-    T, E = logits.shape
+    n_partials = 1 if logits.dim() == 2 else logits.shape[0]
+    T, E = logits.shape[-2:]
     k = idx_out.shape[1]
     if bias is not None:
         _want(bias, torch.float32, "bias")
-    _check(lib().qb_router_topk(_p(logits), _p(bias), _p(idx_out), _p(w_out), T, E, k, int(renorm),
+    _check(lib().qb_router_topk(_p(logits), n_partials, _p(bias), _p(idx_out), _p(w_out), T, E, k, int(renorm),
                                 ctypes.c_float(scale), _stream()), "router_topk")
 
 

@@ -21,6 +21,8 @@ _NORM_KIND = {None: kernels.NORM_NONE, "per_layer": kernels.NORM_PER_LAYER, "per
 
 @register("mixer", "gqa_attention")
 class GQAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None):
         if n_q_heads % n_kv_heads:

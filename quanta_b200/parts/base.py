@@ -108,6 +108,10 @@ class StepContext:
 class Part:
     """Base of every part."""
 
+    # True when ``forward`` reads nothing from the host (no ``ctx.host``, no ``.item()``, no shapes that
+    # depend on data): a decode step of such parts can be captured in a CUDA graph and replayed.
+    graph_safe = False
+
     def tensor_specs(self) -> list[TensorSpec]:
         return []
 

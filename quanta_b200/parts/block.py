@@ -16,6 +16,8 @@ from .base import Block, Part, TensorSpec, make, register
 
 @register("block", "pre_norm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, mixer, feed_forward, mixer_norm, feed_forward_norm):
         self.hidden = int(hidden_size)
         self.mixer = make("mixer", mixer)
@@ -38,6 +40,8 @@ class PreNormBlock(Block):
 class Embedding(Part):
     """``h = table[ids]`` into the float32 residual stream (src/quanta/minimax/model.py:91)."""
 
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, weight_name: str):
         self.V, self.H, self.weight_name = int(vocab_size), int(hidden_size), weight_name
         self.table = None
@@ -57,6 +61,8 @@ class Embedding(Part):
 class OutputHead(Part):
     """Final norm on the wanted rows, then ``logits = x @ head.T`` in float32
     (src/quanta/minimax/runtime.py:95-98).  ``tied_to`` names the embedding table to reuse."""
+
+    graph_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, norm, weight_name: str | None, tied_to: str | None):
         self.V, self.H = int(vocab_size), int(hidden_size)

@@ -18,6 +18,8 @@ from .base import FeedForward, TensorSpec, register
 
 @register("feed_forward", "sigmoid_topk_experts")
 class SigmoidTopKExperts(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, use_bias: bool,
                  renormalize: bool, scaling: float, names: dict):
         if top_k > n_experts:
@@ -59,8 +61,11 @@ class SigmoidTopKExperts(FeedForward):
     def route(self, x):
         """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
         T = x.shape[0]
-        logits = torch.empty((T, self.E), dtype=torch.float32, device=x.device)
-        kernels.gemm_nt_simt(x, self.gate_w, logits)
+        # the inner dimension is cut at fixed multiples of 256, whatever T: few rows still fill the GPU,
+        # and a token's logits are bit-identical however the step is cut
+        chunk = 256
+        logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
+        kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
         idx = torch.empty((T, self.k), dtype=torch.int32, device=x.device)
         w = torch.empty((T, self.k), dtype=torch.float32, device=x.device)
         kernels.router_topk(logits, self.bias, idx, w, self.renorm, self.scaling)
@@ -96,6 +101,8 @@ class SigmoidTopKExperts(FeedForward):
 @register("feed_forward", "swiglu_dense")
 class SwiGLUDense(FeedForward):
     """``down(silu(gate x) * up x)`` with library products and a fused activation kernel."""
+
+    graph_safe = True
 
     def __init__(self, hidden_size: int, inner_size: int, names: dict):
         self.H, self.I, self.names = int(hidden_size), int(inner_size), dict(names)

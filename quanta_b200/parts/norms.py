@@ -10,6 +10,8 @@ from .base import Norm, TensorSpec, register
 
 @register("norm", "rms_norm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     """``weight * x * rsqrt(mean(x^2) + eps)`` with float32 statistics; plain weight (no ``1 + w``)."""
 
     def __init__(self, width: int, eps: float, weight_name: str):

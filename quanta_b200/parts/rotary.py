@@ -16,6 +16,8 @@ from .base import PositionEncoding, register
 
 @register("position", "partial_rotary")
 class PartialRotary(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, sections=None):
         if rotary_dim % 2 or not 0 <= rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
