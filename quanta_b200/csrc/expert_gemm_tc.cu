@@ -1,0 +1,357 @@
+// Routed experts on the 5th-generation tensor cores: TMA-fed tcgen05.mma with accumulators in TMEM.
+//
+// One block = one tile of up to NT token rows of ONE expert x 128 of its output features.  The
+// expert's WEIGHTS are the 128-row operand (M = 128) and the token rows are the N operand ("swap
+// A/B"), so an expert with few rows still uses the full height of the MMA and its weights stream
+// through shared memory exactly once per token tile:
+//
+//   warp 0   : TMA producer.  Per 64-wide k block: weight tile(s) [128 x 64] and token tile [NT x 64],
+//              bfloat16, 128-byte swizzle, into a ring of shared-memory stages (mbarrier expect_tx).
+//   warp 1   : MMA issuer.  4 x tcgen05.mma (K = 16 each) per stage and matrix, D[128 x NT] float32 in
+//              TMEM; tcgen05.commit frees the stage and, at the end, signals the epilogue.
+//   warps 2-5: epilogue.  tcgen05.ld (one TMEM lane = one output feature per thread), then
+//              MODE 1: act[p, j] = silu(gate) * up  (bfloat16),  gate/up = two accumulators;
+//              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32).
+//   (src/quanta/minimax/moe.py:59-88; rows p sorted by expert, see the plan kernels.)
+//
+// The token rows must be contiguous in p order: MODE 1 reads a gathered copy of x (gather kernel
+// below), MODE 2 reads the act rows MODE 1 wrote.  Rows past the expert's last row compute garbage
+// that the epilogue drops; TMA zero-fills past the end of a tensor, so K need not be a multiple of 64
+// (it must be a multiple of 8: 16-byte rows).  No multicast, no clusters: every tile comes from this
+// GPU's memory through a plain per-block TMA load.
+//
+// Every wait on an mbarrier is bounded; when one runs out the block records it in the status words,
+// lets its copies in flight land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int EG_M = 128;            // output features per block (UMMA M)
+constexpr int EG_BK = 64;            // k elements per stage: 128 bytes, one swizzle row
+constexpr int EG_THREADS = 192;
+constexpr uint32_t EG_SPIN_LIMIT = 4u * 1000u * 1000u;
+constexpr uint64_t EG_WAIT_NS = 200ull * 1000ull * 1000ull;   // no wait is longer than 0.2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when another role gave up or the limit is reached (and then raises the flag).
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t it = 0; it < EG_SPIN_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((it & 63u) == 63u && global_ns() - t0 > EG_WAIT_NS) break;      // both an iteration and a time limit
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address
+  // leading byte offset (bits 16-29): 0, the tile is one swizzle atom wide along k
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: 8 rows x 128 B
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // 128-byte swizzle
+  return d;
+}
+// kind::f16, bfloat16 x bfloat16 -> float32, both operands K-major
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+
+struct EgShared {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(EG_THREADS, 1)
+expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                      void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
+                      const int* __restrict__ plan, const int* __restrict__ tile_expert,
+                      const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
+                      int tmem_cols, int* status) {
+  constexpr int NM = MODE == 1 ? 2 : 1;
+  extern __shared__ unsigned char smem_dyn[];
+  // stage buffers need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  __shared__ EgShared sh;
+  __shared__ int s_pair[256];
+  __shared__ float s_w[256];
+
+  const int num_tiles = plan[3 * E + 1];
+  const int tile = blockIdx.y;
+  if (tile >= num_tiles) return;
+  const int e = tile_expert[tile], row0 = tile_row0[tile];
+  const int rows = min(NT, plan[2 * E + e + 1] - row0);          // valid token rows of this tile
+  const int j0 = blockIdx.x * EG_M;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t a_bytes = EG_M * EG_BK * 2, b_bytes = (uint32_t)NT * EG_BK * 2;
+  const uint32_t stage_bytes = NM * a_bytes + b_bytes;
+  const int k_blocks = (K + EG_BK - 1) / EG_BK;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&sh.full[s]), 1);
+      mbar_init(smem_u32(&sh.empty[s]), 1);
+    }
+    mbar_init(smem_u32(&sh.tmem_full), 1);
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {      // one warp allocates the accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&sh.tmem_base)), "r"((uint32_t)tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (MODE == 2) {
+    for (int i = threadIdx.x; i < NT; i += blockDim.x) {
+      const int pr = i < rows ? sorted_pair[row0 + i] : 0;
+      s_pair[i] = pr;
+      s_w[i] = i < rows ? pair_w[pr] : 0.f;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int w_row = MODE == 1 ? e * 2 * N_out + j0 : e * N_out + j0;
+      int armed = 0;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % stages;
+        const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+        if (!mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag)) break;
+        const uint32_t full = smem_u32(&sh.full[s]);
+        unsigned char* st = tiles + (size_t)s * stage_bytes;
+        mbar_expect_tx(full, stage_bytes);
+        tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full);
+        if (MODE == 1) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + N_out, full);
+        tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full);
+        armed = kb + 1;
+      }
+      if (*abort_flag) {
+        // let the copies that were issued land before this block's shared memory is given away
+        for (int kb = max(0, armed - stages); kb < armed; ++kb) {
+          const int s = kb % stages;
+          const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+          const uint64_t t0 = global_ns();
+          for (uint32_t it = 0; it < EG_SPIN_LIMIT && !mbar_try_wait(smem_u32(&sh.full[s]), ph); ++it)
+            if ((it & 63u) == 63u && global_ns() - t0 > EG_WAIT_NS) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(EG_M, NT);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % stages;
+        const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+        ok = mbar_wait(smem_u32(&sh.full[s]), ph, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t st = smem_u32(tiles + (size_t)s * stage_bytes);
+        const uint64_t b_desc = umma_desc_sw128(st + NM * a_bytes);
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+          const uint64_t a_desc = umma_desc_sw128(st + m * a_bytes);
+#pragma unroll
+          for (int k16 = 0; k16 < EG_BK / 16; ++k16) {
+            // 16 k elements = 32 bytes further along the swizzled row: +2 in the 16-byte address field
+            umma_bf16(tmem_base + (uint32_t)(m * NT), a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc,
+                      (kb | k16) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&sh.empty[s]));      // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(&sh.tmem_full));
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, one TMEM lane quadrant each ----------------
+    const int quad = warp & 3;
+    const int feat = j0 + quad * 32 + lane;
+    if (mbar_wait(smem_u32(&sh.tmem_full), 0u, abort_flag)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      for (int c0 = 0; c0 < NT; c0 += 16) {
+        if (c0 >= rows) break;
+        uint32_t v0[16], v1[16];
+        tmem_ld16(lane_addr + (uint32_t)c0, v0);
+        if (MODE == 1) tmem_ld16(lane_addr + (uint32_t)(NT + c0), v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (feat < N_out) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int col = c0 + i;
+            if (col >= rows) break;
+            if (MODE == 1) {
+              const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
+              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(row0 + col) * N_out + feat] =
+                  __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+            } else {
+              reinterpret_cast<float*>(out)[(size_t)s_pair[col] * N_out + feat] = s_w[col] * __uint_as_float(v0[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
+  }
+  if (threadIdx.x == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, tile, 5);
+}
+
+// out[p, :] = x[sorted_pair[p] / top_k, :]   (rows of 16-byte chunks)
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
+                                   const int* __restrict__ sorted_pair, int n_pairs, int top_k, int chunks) {
+  const size_t total = (size_t)n_pairs * chunks;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int p = (int)(i / chunks), c = (int)(i % chunks);
+    out[i] = x[(size_t)(sorted_pair[p] / top_k) * chunks + c];
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bfloat16 tensor [rows, K] row-major, boxes of [box_rows, 64] with the 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return QB_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {K, rows};
+  const cuuint64_t strides[1] = {K * 2};
+  const cuuint32_t box[2] = {EG_BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : QB_ERR_BAD_ARG;
+}
+
+}  // namespace
+
+extern "C" int qb_gather_rows(const void* x, void* out, const int* sorted_pair, int n_pairs, int top_k, int K,
+                              cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (K % 8) return QB_ERR_UNSUPPORTED;
+  const size_t total = (size_t)n_pairs * (K / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  gather_rows_kernel<<<blocks, 256, 0, stream>>>((const uint4*)x, (uint4*)out, sorted_pair, n_pairs, top_k, K / 8);
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// x_rows: bf16 [n_pairs, K] in sorted order (mode 1: the gathered activations; mode 2: the act rows).
+// weights: bf16 [E, (mode 1 ? 2 : 1) * N_out, K].  NT: token tile (16..256, a multiple of 16); the plan's
+// tile list must have been made with the same NT.
+extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weights, void* out, const int* sorted_pair,
+                                 const float* pair_w, const int* plan, const int* tile_expert, const int* tile_row0,
+                                 int max_tiles, int n_pairs, int E, int K, int N_out, int NT, int* status,
+                                 cudaStream_t stream) {
+  if (max_tiles <= 0 || n_pairs <= 0) return 0;
+  if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
+  if (mode != 1 && mode != 2) return QB_ERR_BAD_ARG;
+  const int nm = mode == 1 ? 2 : 1;
+  if (((uintptr_t)x_rows | (uintptr_t)weights) & 15) return QB_ERR_BAD_ARG;
+  CUtensorMap tm_w, tm_x;
+  int rc = make_map(&tm_w, weights, (uint64_t)E * nm * N_out, (uint64_t)K, EG_M);
+  if (rc) return rc;
+  rc = make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)NT);
+  if (rc) return rc;
+  const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)NT * EG_BK * 2;
+  int stages = (int)((200 * 1024) / stage_bytes);
+  if (stages > 8) stages = 8;
+  const int k_blocks = (K + EG_BK - 1) / EG_BK;
+  if (stages > k_blocks) stages = k_blocks;
+  if (stages < 2 && k_blocks >= 2) return QB_ERR_UNSUPPORTED;
+  const size_t smem = stage_bytes * stages + 1024;
+  int tmem_cols = 32;
+  while (tmem_cols < nm * NT) tmem_cols *= 2;
+  dim3 grid((N_out + EG_M - 1) / EG_M, max_tiles);
+  cudaError_t err;
+  if (mode == 1) {
+    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    expert_gemm_tc_kernel<1><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
+                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, status);
+  } else {
+    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+    expert_gemm_tc_kernel<2><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
+                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, status);
+  }
+  QB_LAUNCH_CHECK();
+  return 0;
+}

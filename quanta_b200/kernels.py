@@ -289,6 +289,41 @@ def moe_stream(mode: int, x, weights, out, sorted_pair, pair_w, plan, n_experts:
                                top_k, K, N, min(n_experts, n_pairs), int(max_rows), _stream()), "moe_stream")
 
 
+def expert_tile_rows(n_tokens: int) -> int:
+    """Token tile (the MMA's N) of the tcgen05 expert kernel for a step of ``n_tokens`` tokens: an expert
+    never receives more rows than there are tokens."""
+    for nt in (16, 32, 64):
+        if n_tokens <= nt:
+            return nt
+    return 128
+
+
+def gather_rows(x, out, sorted_pair, top_k: int) -> None:
+    """``out[p] = x[sorted_pair[p] // top_k]``: the token rows in expert order, contiguous for TMA."""
+    n_pairs, K = out.shape
+    _want(x, torch.bfloat16, "x"); _want(out, torch.bfloat16, "out")
+    if x.shape[1] != K or sorted_pair.numel() != n_pairs:
+        raise ValueError("gather_rows: shape mismatch")
+    _check(lib().qb_gather_rows(_p(x), _p(out), _p(sorted_pair), n_pairs, top_k, K, _stream()), "gather_rows")
+
+
+def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
+                   n_experts: int, tile_rows: int, status) -> None:
+    """Expert products on tcgen05/TMEM fed by TMA.  ``x_rows`` bf16 [pairs, K] in expert order; mode 1:
+    ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32).  The plan's
+    tile list must have been made with ``bm = tile_rows``."""
+    n_pairs, K = x_rows.shape
+    N = out.shape[1]
+    want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
+    if tuple(weights.shape) != want:
+        raise ValueError(f"expert_gemm_tc: weights {tuple(weights.shape)} != {want}")
+    _want(x_rows, torch.bfloat16, "x_rows"); _want(weights, torch.bfloat16, "weights")
+    _want(out, torch.bfloat16 if mode == 1 else torch.float32, "out")
+    _check(lib().qb_expert_gemm_tc(mode, _p(x_rows), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan),
+                                   _p(tile_expert), _p(tile_row0), tile_expert.numel(), n_pairs, n_experts, K, N,
+                                   int(tile_rows), _p(status), _stream()), "expert_gemm_tc")
+
+
 def sample_rows(logits, fparams, iparams, out) -> None:
     """``fparams``/``iparams`` None: every row is greedy (first maximum)."""
     _want(logits, torch.float32, "logits"); _want(out, torch.int32, "out")

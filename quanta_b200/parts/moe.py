@@ -9,6 +9,8 @@ index); weights are the bias-free scores, renormalised (``+ 1e-20``) and scaled;
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import kernels
@@ -58,6 +60,22 @@ class SigmoidTopKExperts(FeedForward):
             self.w2[e].copy_(fetch(n["w2"].format(e=e)))
         del first
 
+    # Which kernels run the expert products: "tc" (tcgen05 + TMA), "stream" (mma.sync, weights from
+    # registers), "simt" (float32 CUDA cores).  "auto": float32 and odd sizes -> simt; bfloat16 -> stream
+    # for steps of at most ``stream_max_tokens`` tokens, tc above.  Set per part, or for the whole process with
+    # QUANTA_B200_EXPERT_KERNELS (a tuning knob, for measurements).
+    expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
+    stream_max_tokens = 2
+
+    def path_for(self, x) -> str:
+        ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
+        choice = self.expert_kernels
+        if not ok16 or choice == "simt":
+            return "simt"
+        if choice in ("tc", "stream"):
+            return choice
+        return "stream" if x.shape[0] <= self.stream_max_tokens else "tc"
+
     def route(self, x):
         """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
         T = x.shape[0]
@@ -75,7 +93,8 @@ class SigmoidTopKExperts(FeedForward):
         T, dev = x.shape[0], x.device
         idx, w = self.route(x)
         n_pairs = T * self.k
-        bm = kernels.MOE_SIMT_BM
+        path = self.path_for(x)
+        bm = kernels.expert_tile_rows(T) if path == "tc" else kernels.MOE_SIMT_BM
         plan_words, max_tiles = kernels.moe_plan_sizes(n_pairs, self.E, bm)
         ints = torch.empty(plan_words + n_pairs + 2 * max_tiles, dtype=torch.int32, device=dev)
         plan = ints[:plan_words]
@@ -86,8 +105,16 @@ class SigmoidTopKExperts(FeedForward):
         self.last_counts = plan[: self.E]
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
-        if kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16:
-            # bfloat16: expert weights streamed once through the tensor cores
+        if path == "tc":
+            # bfloat16: TMA-fed tcgen05 products, weights as the 128-row operand, accumulators in TMEM
+            xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
+            kernels.gather_rows(x, xg, sorted_pair, self.k)
+            kernels.expert_gemm_tc(1, xg, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert, tile_row0,
+                                   self.E, bm, ctx.status)
+            kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
+                                   tile_expert, tile_row0, self.E, bm, ctx.status)
+        elif path == "stream":
+            # bfloat16, very few rows: expert weights streamed once through mma.sync from registers
             kernels.moe_stream(1, x, self.w13, act, sorted_pair, w.view(-1), plan, self.E, self.k, T)
             kernels.moe_stream(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan, self.E,
                                self.k, T)

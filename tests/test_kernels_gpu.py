@@ -255,12 +255,14 @@ def test_router_topk(E, k, bias, renorm, scale):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("path", ["simt", "stream"])
-@pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2)])
+@pytest.mark.parametrize("path", ["simt", "stream", "tc"])
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2),
+                                       (300, 256, 136, 7, 2)])
 def test_expert_products(dtype, T, H, I, E, k, path):
     kern = K()
-    if path == "stream" and dtype != torch.bfloat16:
-        pytest.skip("the streaming kernel is the bfloat16 path")
+    if path != "simt" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernels are the bfloat16 path")
+    bm = kern.expert_tile_rows(T) if path == "tc" else kern.MOE_SIMT_BM
     torch.manual_seed(3)
     x = torch.randn(T, H, device=DEV).to(dtype)
     # scaled so that outputs stay of order one at every size (the tolerance is absolute)
@@ -273,13 +275,13 @@ def test_expert_products(dtype, T, H, I, E, k, path):
         idx[:30, 1] = torch.where(idx[:30, 1] == idx[:30, 0], 6, idx[:30, 1])
     pw = torch.rand(T, k, device=DEV)
     n_pairs = T * k
-    words, max_tiles = kern.moe_plan_sizes(n_pairs, E, kern.MOE_SIMT_BM)
+    words, max_tiles = kern.moe_plan_sizes(n_pairs, E, bm)
     plan = torch.empty(words, device=DEV, dtype=torch.int32)
     sorted_pair = torch.empty(n_pairs, device=DEV, dtype=torch.int32)
     te = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
     tr = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
     st = kern.new_status(DEV)
-    kern.moe_plan(idx, E, kern.MOE_SIMT_BM, plan, sorted_pair, te, tr, st)
+    kern.moe_plan(idx, E, bm, plan, sorted_pair, te, tr, st)
     counts = torch.bincount(idx.flatten().long(), minlength=E)
     assert plan[:E].tolist() == counts.tolist()
     assert sorted(sorted_pair.tolist()) == list(range(n_pairs))
@@ -290,6 +292,14 @@ def test_expert_products(dtype, T, H, I, E, k, path):
     if path == "simt":
         kern.moe_grouped_simt(1, x, w13, act, sorted_pair, pw, plan, te, tr, E, k)
         kern.moe_grouped_simt(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, k)
+    elif path == "tc":
+        xg = torch.empty(n_pairs, H, device=DEV, dtype=dtype)
+        kern.gather_rows(x, xg, sorted_pair, k)
+        assert torch.equal(xg, x[(sorted_pair // k).long()])
+        kern.expert_gemm_tc(1, xg, w13, act, sorted_pair, pw.view(-1), plan, te, tr, E, bm, st)
+        kern.expert_gemm_tc(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, bm, st)
+        torch.cuda.synchronize()
+        assert st.tolist()[0] == 0, f"device status {st.tolist()}"
     else:
         assert kern.moe_stream_supported(x, H, I)
         kern.moe_stream(1, x, w13, act, sorted_pair, pw.view(-1), plan, E, k, T)
