@@ -455,3 +455,54 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
   QB_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: the scratch is a static device array.
+// (No counterpart in the reference; contract and reasons in no_alloc.h.)
+// ------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Partial results of the split-key kernel for one call at a time.  Host code must not hand this
+// name to a kernel: on the host it is only a stand-in for the symbol; the device address is looked
+// up once per device below.
+static __device__ __align__(256) float qb_noalloc_scratch[QB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+extern "C" long long qb_attn_decode_noalloc_floats(int n_dec, int nq, int hd, int n_splits_max) {
+  if (n_dec <= 0 || nq <= 0 || hd <= 0 || n_splits_max <= 0) return 0;
+  return (long long)n_dec * nq * n_splits_max * (hd + 2);
+}
+
+extern "C" long long qb_attn_decode_noalloc_capacity(void) { return (long long)QB_NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" int qb_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* dec_tok, int n_dec, const int* tok_pos, const int* tok_req,
+                                      const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
+                                      int num_pages, float scale, int window, int n_splits_max, int* status,
+                                      cudaStream_t stream) {
+  if (n_dec <= 0) return 0;
+  if (nq <= 0 || hd <= 0 || n_splits_max <= 0) return QB_ERR_BAD_ARG;
+  const long long need = qb_attn_decode_noalloc_floats(n_dec, nq, hd, n_splits_max);
+  if (need > (long long)QB_NOALLOC_SCRATCH_FLOATS) return QB_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return (int)err;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return QB_ERR_UNSUPPORTED;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // first call on this device (which is current): the array's address in this device's memory
+    float* p = nullptr;
+    err = cudaGetSymbolAddress((void**)&p, qb_noalloc_scratch);
+    if (err != cudaSuccess) return (int)err;
+    if (p == nullptr) return QB_ERR_UNSUPPORTED;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_o = g_noalloc_ptr[dev];
+  // the (max, sum) pairs follow the partial outputs; the offset keeps them 8-byte aligned
+  float* part_ml = part_o + (size_t)n_dec * nq * n_splits_max * hd;
+  return qb_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec, tok_pos, tok_req, block_table,
+                        bt_stride, nq, nkv, hd, page_size, num_pages, scale, window, n_splits_max, status, stream);
+}
