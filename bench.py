@@ -221,6 +221,7 @@ def run_ours(args) -> dict:
 
     # ---- end to end through the Python entry point ----
     n_new = args.warmup + args.steps + 1
+    llm.sched_opts["max_step_tokens"] = B * prompt_len       # all prompts in the first step, then pure decode steps
     reqs = [Request(rid=("e", i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new)) for i in range(B)]
     llm.run(reqs)
     log = llm.step_log

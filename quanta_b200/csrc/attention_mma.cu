@@ -8,9 +8,9 @@
 //    masked by its own token's position, so prompt portions of any length run, from the cache that
 //    earlier steps and this step's rope kernel wrote.  K/V blocks of 64 keys are gathered page by
 //    page into shared memory with cp.async, double buffered.
-//  * decode kernel: one query token, one kv head and one fixed split of 256 keys per block, 64 keys
+//  * decode kernel: one query token, one kv head and one fixed split of 128 keys per block, 64 keys
 //    per warp; the partial (max, sum, O) of each split goes to scratch and a merge kernel adds the
-//    splits in index order.  Split boundaries are multiples of 256 in absolute position, so a token's
+//    splits in index order.  Split boundaries are multiples of 128 in absolute position, so a token's
 //    result does not depend on the batch.
 //
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
@@ -23,7 +23,7 @@ namespace {
 constexpr int AT_BN = 64;            // keys per block (span kernel) and per warp (decode kernel)
 constexpr int AT_WARPS = 4;
 constexpr int AT_BM = 16 * AT_WARPS; // query rows per span tile
-constexpr int AT_SPLIT = AT_BN * AT_WARPS;   // keys per decode split
+constexpr int AT_DEC_WARPS = 2;      // warps of a decode block: 128 keys per split, two or more blocks per SM
 constexpr int AT_PAD = 8;            // +16 bytes a row: ldmatrix rows fall on distinct banks
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -60,20 +60,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HDP>
 __device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ cache,
                                               const int* __restrict__ bt, int key0, int n_keys, int key_end,
-                                              int kvh, int nkv, int hd, int page_size, int num_pages, int* status) {
+                                              int kvh, int nkv, int hd, int page_size, int num_pages, int* status,
+                                              int pi0 = 0) {
   constexpr int CH = HDP / 8;        // 16-byte chunks per row
+  // pages of a power-of-two size (the usual case) are found with a shift instead of a division
+  const int shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   for (int c = threadIdx.x; c < n_keys * CH; c += blockDim.x) {
     const int r = c / CH, d = (c % CH) * 8;
     const int key = key0 + r;
     bool ok = key >= 0 && key <= key_end && d < hd;
     const __nv_bfloat16* src = cache;
     if (ok) {
-      const int page = bt[key / page_size];
+      const int pi = shift >= 0 ? key >> shift : key / page_size;
+      const int slot = shift >= 0 ? key & (page_size - 1) : key % page_size;
+      const int page = bt[pi - pi0];       // bt may be a copy of the table's entries from pi0 on
       if (page < 0 || page >= num_pages) {
         qb_set_status(status, QB_STATUS_BAD_PAGE, page, 7);
         ok = false;
       } else {
-        src = cache + (((size_t)page * nkv + kvh) * page_size + key % page_size) * hd + d;
+        src = cache + (((size_t)page * nkv + kvh) * page_size + slot) * hd + d;
       }
     }
     cp_async16(dst + (size_t)r * (HDP + AT_PAD) + d, src, ok);
@@ -214,17 +219,31 @@ attn_span_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
 #pragma unroll
   for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  load_kv_block<HDP>(kbuf, k_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status);
-  load_kv_block<HDP>(vbuf, v_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status);
+  // the page ids of the keys this tile reads are copied to shared memory once (when they fit), so the
+  // per-block copies do not each wait for a table entry
+  constexpr int MAX_SPAN_PAGES = 2048;
+  __shared__ int s_page[MAX_SPAN_PAGES];
+  int pi0 = key_begin / page_size;
+  const int n_pi = key_end / page_size - pi0 + 1;
+  if (n_pi <= MAX_SPAN_PAGES) {
+    for (int i = tid; i < n_pi; i += blockDim.x) s_page[i] = bt[pi0 + i];
+    bt = s_page;
+    __syncthreads();
+  } else {
+    pi0 = 0;
+  }
+
+  load_kv_block<HDP>(kbuf, k_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status, pi0);
+  load_kv_block<HDP>(vbuf, v_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status, pi0);
   cp_async_commit();
   for (int b = 0; b < n_blocks; ++b) {
     const int cur = b & 1;
     if (b + 1 < n_blocks) {
       const int k0n = key_begin + (b + 1) * AT_BN;
       load_kv_block<HDP>(kbuf + (cur ^ 1) * AT_BN * LD, k_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
-                         num_pages, status);
+                         num_pages, status, pi0);
       load_kv_block<HDP>(vbuf + (cur ^ 1) * AT_BN * LD, v_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
-                         num_pages, status);
+                         num_pages, status, pi0);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -264,7 +283,7 @@ attn_span_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
 
 // ------------------------------------------------------------------------------------------------
 // decode kernel: grid (n_splits_max, n_kv, n_decode_tokens); dec_tok[z] = token row.  The block has
-// W warps (4, or 2 for head_dim > 128) and owns the W*64 keys [split*W*64, (split+1)*W*64).
+// W = 2 warps and owns the W*64 keys [split*W*64, (split+1)*W*64).
 // scratch: part_o float [n_dec][nq][n_splits_max][hd], part_ml float [n_dec][nq][n_splits_max][2]
 // ------------------------------------------------------------------------------------------------
 template <int HDP>
@@ -292,8 +311,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int n_keys = min(split_keys, pos - key0 + 1);
   const int keys_pad = (n_keys + AT_BN - 1) / AT_BN * AT_BN;
 
-  load_kv_block<HDP>(kbuf, k_cache, bt, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status);
-  load_kv_block<HDP>(vbuf, v_cache, bt, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status);
+  // the split's page ids, fetched once with independent loads, so that the copies below do not each
+  // wait for a table entry
+  __shared__ int s_page[AT_DEC_WARPS * AT_BN];
+  const int pi0 = key0 / page_size, n_pi = (key0 + n_keys - 1) / page_size - pi0 + 1;
+  for (int i = tid; i < n_pi; i += blockDim.x) s_page[i] = bt[pi0 + i];
+  __syncthreads();
+  load_kv_block<HDP>(kbuf, k_cache, s_page, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status, pi0);
+  load_kv_block<HDP>(vbuf, v_cache, s_page, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status, pi0);
   cp_async_commit();
 
   for (int rb = 0; rb < G; rb += 16) {                        // 16 heads of the group at a time
@@ -421,7 +446,7 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
 }
 
 // Keys per decode split for a head size (the Python side sizes the scratch with it).
-extern "C" int qb_attn_decode_split_keys(int hd) { return (hd <= 128 ? AT_WARPS : 2) * AT_BN; }
+extern "C" int qb_attn_decode_split_keys(int hd) { (void)hd; return AT_DEC_WARPS * AT_BN; }
 
 // Scratch, in floats: part_o n_dec*nq*n_splits_max*hd, part_ml n_dec*nq*n_splits_max*2, where
 // n_splits_max >= ceil(longest context / split keys).
@@ -434,7 +459,7 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535 || n_dec > 65535 || n_splits_max <= 0)
     return QB_ERR_UNSUPPORTED;
   const float scale_log2 = scale * 1.4426950408889634f;
-  const int warps = hd <= 128 ? AT_WARPS : 2, split_keys = warps * AT_BN;
+  const int warps = AT_DEC_WARPS, split_keys = warps * AT_BN;
   dim3 grid(n_splits_max, nkv, n_dec);
 #define QB_DEC(HDP)                                                                                        \
   do {                                                                                                     \

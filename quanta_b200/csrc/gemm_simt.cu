@@ -28,17 +28,29 @@ __global__ void gemm_nt_simt_kernel(const TA* __restrict__ A, const TB* __restri
   const int k_begin = k_chunk > 0 ? blockIdx.z * k_chunk : 0;
   const int k_stop = k_chunk > 0 ? min(K, k_begin + k_chunk) : K;
   C += (size_t)blockIdx.z * M * ldc;
-  for (int k0 = k_begin; k0 < k_stop; k0 += GS_BK) {
-    // 64 rows x 16 k = 1024 elements per operand, 4 per thread
+  // 64 rows x 16 k = 1024 elements per operand and slice, 4 per thread; the next slice is fetched into
+  // registers while the current one is multiplied
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int idx = tid + e * 256;
       const int r = idx / GS_BK, kk = idx % GS_BK;
       const int gm = m0 + r, gn = n0 + r, gk = k0 + kk;
-      As[kk][r] = (gm < M && gk < k_stop) ? qb_to_float<TA>(A[(size_t)gm * lda + gk]) : 0.f;
-      Bs[kk][r] = (gn < N && gk < k_stop) ? qb_to_float<TB>(B[(size_t)gn * ldb + gk]) : 0.f;
+      ra[e] = (gm < M && gk < k_stop) ? qb_to_float<TA>(A[(size_t)gm * lda + gk]) : 0.f;
+      rb[e] = (gn < N && gk < k_stop) ? qb_to_float<TB>(B[(size_t)gn * ldb + gk]) : 0.f;
+    }
+  };
+  fetch(k_begin);
+  for (int k0 = k_begin; k0 < k_stop; k0 += GS_BK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = tid + e * 256;
+      As[idx % GS_BK][idx / GS_BK] = ra[e];
+      Bs[idx % GS_BK][idx / GS_BK] = rb[e];
     }
     __syncthreads();
+    if (k0 + GS_BK < k_stop) fetch(k0 + GS_BK);
 #pragma unroll
     for (int kk = 0; kk < GS_BK; ++kk) {
       float a[4], b[4];

@@ -22,15 +22,25 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_parti
   if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
   const size_t pstride = (size_t)T * E;
-  float choice[NPL], score[NPL];
+  float choice[NPL], score[NPL], logit[NPL];
   unsigned taken = 0u;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) logit[i] = 0.f;
+  // partial sums in index order; the loads of one partial are independent and issued together
+#pragma unroll 4
+  for (int p = 0; p < n_partials; ++p) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E) logit[i] += lg[p * pstride + e];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
     score[i] = 0.f;
     if (e < E) {
-      float x = lg[e];
-      for (int p = 1; p < n_partials; ++p) x += lg[p * pstride + e];
+      const float x = logit[i];
       const float s = 1.f / (1.f + expf(-x));
       score[i] = s;
       choice[i] = bias ? s + bias[e] : s;

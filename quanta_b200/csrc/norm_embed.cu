@@ -22,7 +22,15 @@ __global__ void embedding_kernel(float* __restrict__ h, const W* __restrict__ ta
     return;
   }
   const W* row = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = qb_to_float<W>(row[i]);
+  if (H % 8 == 0) {
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float v[8];
+      QbVec8<W>::load(row + i, v);
+      QbVec8<float>::store(out + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = qb_to_float<W>(row[i]);
+  }
 }
 
 extern "C" int qb_embedding(float* h, const void* table, int table_dtype, const int* ids, int T, int H,
@@ -54,21 +62,53 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const D* __restrict__ 
   float* hrow = h + (size_t)tok * H;
   const D* drow = delta ? delta + (size_t)tok * S * H : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float x = hrow[i];
-    if (drow) {
-      for (int s = 0; s < S; ++s) x += qb_to_float<D>(drow[(size_t)s * H + i]);
+  if (H % 8 == 0) {
+    // 8 elements a thread and step, vector loads; the slots of the delta are still added in index order
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float x[8];
+      QbVec8<float>::load(hrow + i, x);
+      if (drow) {
+#pragma unroll 4
+        for (int s = 0; s < S; ++s) {
+          float dv[8];
+          QbVec8<D>::load(drow + (size_t)s * H + i, dv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x[e] += dv[e];
+        }
+        if (store_h) QbVec8<float>::store(hrow + i, x);
+      }
+      QbVec8<float>::store(row_buf + i, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
     }
-    row_buf[i] = x;
-    if (store_h && drow) hrow[i] = x;
-    ss += x * x;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float x = hrow[i];
+      if (drow) {
+        for (int s = 0; s < S; ++s) x += qb_to_float<D>(drow[(size_t)s * H + i]);
+      }
+      row_buf[i] = x;
+      if (store_h && drow) hrow[i] = x;
+      ss += x * x;
+    }
   }
   const float total = qb_block_sum(ss, scratch);
   if (out == nullptr) return;
   const float r_inv = rsqrtf(total / (float)H + eps);
   O* orow = out + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    orow[i] = qb_from_float<O>(w[i] * (row_buf[i] * r_inv));
+  if (H % 8 == 0) {
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float x[8], wv[8];
+      QbVec8<float>::load(row_buf + i, x);
+      QbVec8<float>::load(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = wv[e] * (x[e] * r_inv);
+      QbVec8<O>::store(orow + i, x);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      orow[i] = qb_from_float<O>(w[i] * (row_buf[i] * r_inv));
+  }
 }
 
 extern "C" int qb_add_rmsnorm(float* h, const void* delta, int delta_dtype, int S, const float* w,

@@ -32,7 +32,14 @@ __global__ void qknorm_rope_write_kernel(
   const A* row = qkv + (size_t)t * (qn + 2 * kn);
   const int half = rd / 2;
 
-  for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) buf[i] = qb_to_float<A>(row[i]);
+  // 16-byte loads, all of a thread's loads issued before their first use
+  const int n_chunks = (qn + kn) / 8;
+#pragma unroll 4
+  for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+    float v[8];
+    QbVec8<A>::load(row + c * 8, v);
+    QbVec8<float>::store(buf + c * 8, v);
+  }
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const int ax = pair_axis ? pair_axis[j] : 0;
     const float ang = (float)positions[(size_t)t * n_axes + ax] * inv_freq[j];
@@ -50,8 +57,17 @@ __global__ void qknorm_rope_write_kernel(
     const float tq = qb_block_sum(sq, scratch);
     const float tk = qb_block_sum(sk, scratch);
     const float rq = rsqrtf(tq / (float)qn + eps), rk = rsqrtf(tk / (float)kn + eps);
-    for (int i = threadIdx.x; i < qn; i += blockDim.x) buf[i] = q_norm_w[i] * (buf[i] * rq);
-    for (int i = threadIdx.x; i < kn; i += blockDim.x) buf[qn + i] = k_norm_w[i] * (buf[qn + i] * rk);
+#pragma unroll 4
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+      const int i = c * 8;
+      float w[8], v[8];
+      QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w);
+      QbVec8<float>::load(buf + i, v);
+      const float r = i < qn ? rq : rk;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = w[e] * (v[e] * r);
+      QbVec8<float>::store(buf + i, v);
+    }
     __syncthreads();
   } else if (norm_kind == NORM_PER_HEAD) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -81,7 +97,11 @@ __global__ void qknorm_rope_write_kernel(
   __syncthreads();
 
   A* qo = q_out + (size_t)t * qn;
-  for (int i = threadIdx.x; i < qn; i += blockDim.x) qo[i] = qb_from_float<A>(buf[i]);
+  for (int c = threadIdx.x; c < qn / 8; c += blockDim.x) {
+    float v[8];
+    QbVec8<float>::load(buf + c * 8, v);
+    QbVec8<A>::store(qo + c * 8, v);
+  }
 
   if (k_cache == nullptr) return;
   const int pos = tok_pos[t];
@@ -92,11 +112,14 @@ __global__ void qknorm_rope_write_kernel(
   }
   const int slot = pos % page_size;
   const A* vrow = row + qn + kn;
-  for (int i = threadIdx.x; i < kn; i += blockDim.x) {
-    const int h = i / hd, d = i % hd;
+  for (int c = threadIdx.x; c < kn / 8; c += blockDim.x) {
+    const int i = c * 8, h = i / hd, d = i % hd;
     const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
-    k_cache[dst] = qb_from_float<A>(buf[qn + i]);
-    v_cache[dst] = vrow[i];
+    float kv[8], vv[8];
+    QbVec8<float>::load(buf + qn + i, kv);
+    QbVec8<A>::load(vrow + i, vv);
+    QbVec8<A>::store(k_cache + dst, kv);
+    QbVec8<A>::store(v_cache + dst, vv);        // V passes through unchanged (the float round trip is exact)
   }
 }
 
@@ -109,6 +132,7 @@ extern "C" int qb_qknorm_rope_write(
   if (T <= 0) return 0;
   if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0) return QB_ERR_BAD_ARG;
   if (norm_kind != NORM_NONE && (q_norm_w == nullptr || k_norm_w == nullptr)) return QB_ERR_BAD_ARG;
+  if (hd % 8) return QB_ERR_UNSUPPORTED;        // rows are moved in 16-byte pieces
   const size_t smem = (size_t)((nq + nkv) * hd + rd + 32 + nq + nkv) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
   QB_DISPATCH_DTYPE(dtype, A, {

@@ -163,6 +163,48 @@ extern "C" int qb_sample_rows(const float* logits, int n, int V, const float* fp
   return 0;
 }
 
+// Greedy over many blocks: a row of a large vocabulary is cut into `parts` chunks, each block leaves the
+// first maximum of its chunk, and a second kernel takes the first maximum of those (chunks in index order,
+// so the result is the first maximum of the row, whatever `parts`).
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, int parts, float* __restrict__ pv,
+                                      int* __restrict__ pi) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int r = blockIdx.y, part = blockIdx.x;
+  const int chunk = (V + parts - 1) / parts;
+  const int lo = part * chunk, hi = min(V, lo + chunk);
+  const float* row = logits + (size_t)r * V;
+  float bv = -INFINITY; int bi = -1;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
+    if (bi < 0 || row[i] > bv) { bv = row[i]; bi = i; }
+  const ArgBest b = block_argmax(bv, bi, sv, si);
+  if (threadIdx.x == 0) { pv[r * parts + part] = b.v; pi[r * parts + part] = b.i; }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int parts,
+                                    int* __restrict__ out) {
+  const int r = blockIdx.x;
+  if (threadIdx.x != 0) return;
+  float bv = -INFINITY; int bi = -1;
+  for (int p = 0; p < parts; ++p) {
+    const int i = pi[r * parts + p];
+    const float v = pv[r * parts + p];
+    if (i >= 0 && (bi < 0 || v > bv)) { bv = v; bi = i; }
+  }
+  out[r] = bi;
+}
+
+// scratch: parts floats and parts ints per row
+extern "C" int qb_argmax_rows(const float* logits, int n, int V, int parts, float* scratch_v, int* scratch_i,
+                              int* out, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (parts <= 0 || n > 65535) return QB_ERR_BAD_ARG;
+  argmax_partial_kernel<<<dim3(parts, n), 256, 0, stream>>>(logits, V, parts, scratch_v, scratch_i);
+  argmax_final_kernel<<<n, 32, 0, stream>>>(scratch_v, scratch_i, parts, out);
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
 // Penalties, in place on a float32 logits row.  prev[prev_off[r] .. prev_off[r+1]) are the tokens the
 // request has generated.  The first occurrence of a token applies the penalty with its full count.
 // pparams [n,3]: repetition, frequency, presence.

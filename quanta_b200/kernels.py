@@ -330,6 +330,13 @@ def sample_rows(logits, fparams, iparams, out) -> None:
     if fparams is not None:
         _want(fparams, torch.float32, "fparams"); _want(iparams, torch.int32, "iparams")
     n, V = logits.shape
+    if fparams is None and V >= 4096:
+        # all greedy: a row is cut over many blocks, then the first maximum of the chunks is taken
+        parts = 32
+        sv = torch.empty(n * parts, dtype=torch.float32, device=logits.device)
+        si = torch.empty(n * parts, dtype=torch.int32, device=logits.device)
+        _check(lib().qb_argmax_rows(_p(logits), n, V, parts, _p(sv), _p(si), _p(out), _stream()), "argmax_rows", 2)
+        return
     _check(lib().qb_sample_rows(_p(logits), n, V, _p(fparams), _p(iparams), _p(out), _stream()), "sample_rows")
 
 

@@ -79,9 +79,9 @@ class SigmoidTopKExperts(FeedForward):
     def route(self, x):
         """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
         T = x.shape[0]
-        # the inner dimension is cut at fixed multiples of 256, whatever T: few rows still fill the GPU,
+        # the inner dimension is cut at fixed multiples of 128, whatever T: few rows still fill the GPU,
         # and a token's logits are bit-identical however the step is cut
-        chunk = 256
+        chunk = 128
         logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
         kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
         idx = torch.empty((T, self.k), dtype=torch.int32, device=x.device)

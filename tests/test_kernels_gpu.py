@@ -372,3 +372,19 @@ def test_sampling_distribution_and_penalties():
     kern.apply_penalties(lg, prev, off, pp)
     w0 = P.apply_penalties(np.array([2.0, -2.0, 1.0, 0.5], dtype=np.float32), [0, 1, 1], 2.0, 0.5, 0.25)
     assert np.allclose(lg[0].cpu().numpy(), w0) and lg[1].tolist() == [1.0] * 4
+
+
+def test_greedy_over_a_large_vocabulary():
+    """Rows cut over many blocks still give the first maximum."""
+    kern = K()
+    V, n = 200064, 5
+    torch.manual_seed(6)
+    logits = torch.randn(n, V, device=DEV)
+    logits[1, 150000] = logits[1, 7] = logits[1, 199999] = 9.0         # a tie across chunks: the lowest index wins
+    logits[2, V - 1] = 11.0
+    logits[3, 0] = 12.0
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    kern.sample_rows(logits, None, None, out)
+    assert out.tolist()[1:4] == [7, V - 1, 0]
+    for r in (0, 4):
+        assert int(out[r]) == int(logits[r].argmax())          # no ties in a random row
