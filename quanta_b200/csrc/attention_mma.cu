@@ -410,7 +410,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 template <typename Kern>
 int set_smem(Kern kern, size_t smem) {
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {      // the kernels also have static shared memory; the default limit counts both
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

@@ -69,10 +69,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+// L2 policies: weights are read once per step (evict first), token tiles by every row block (evict last)
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar,
+                                            uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar), "l"(policy) : "memory");
 }
 
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -115,7 +128,7 @@ struct EgShared {
 };
 
 template <int MODE>
-__global__ void __launch_bounds__(EG_THREADS, 1)
+__global__ void __launch_bounds__(EG_THREADS, 2)
 expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                       void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
                       const int* __restrict__ plan, const int* __restrict__ tile_expert,
@@ -171,6 +184,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int w_row = MODE == 1 ? e * 2 * N_out + j0 : e * N_out + j0;
+      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
       int armed = 0;
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % stages;
@@ -179,9 +193,9 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const uint32_t full = smem_u32(&sh.full[s]);
         unsigned char* st = tiles + (size_t)s * stage_bytes;
         mbar_expect_tx(full, stage_bytes);
-        tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full);
-        if (MODE == 1) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + N_out, full);
-        tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full);
+        tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full, pol_w);
+        if (MODE == 1) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + N_out, full, pol_w);
+        tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full, pol_x);
         armed = kb + 1;
       }
       if (*abort_flag) {
@@ -331,7 +345,9 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   rc = make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)NT);
   if (rc) return rc;
   const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)NT * EG_BK * 2;
-  int stages = (int)((200 * 1024) / stage_bytes);
+  // Two blocks share an SM (shared memory is the limit), so that one block's prologue and epilogue run
+  // under the other's main loop; each gets a ring of about 105 KB.
+  int stages = (int)((105 * 1024) / stage_bytes);
   if (stages > 8) stages = 8;
   const int k_blocks = (K + EG_BK - 1) / EG_BK;
   if (stages > k_blocks) stages = k_blocks;
