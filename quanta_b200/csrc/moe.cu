@@ -166,11 +166,73 @@ __global__ void moe_scatter_kernel(const int* __restrict__ idx, int n_pairs, int
   }
 }
 
+// The whole plan in one block, for steps with few pairs (decoding): counts in shared memory, the same
+// scans as above, then the scatter.  One launch instead of a memset and three kernels.
+__global__ void moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
+                                      int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                                      int* __restrict__ tile_row0, int max_tiles, int* status) {
+  __shared__ int s_cnt[1024];
+  __shared__ int s_til[1024];
+  __shared__ int s_act[1024];
+  __shared__ int s_cur[1024];
+  const int e = threadIdx.x;
+  s_cur[e] = 0;
+  __syncthreads();
+  for (int i = e; i < n_pairs; i += 1024) {
+    const int x = idx[i];
+    if (x < 0 || x >= E) { qb_set_status(status, QB_STATUS_BAD_EXPERT, x, 4); continue; }
+    atomicAdd(&s_cur[x], 1);
+  }
+  __syncthreads();
+  const int c = e < E ? s_cur[e] : 0;
+  const int nt = (c + BM - 1) / BM;
+  s_cnt[e] = c;
+  s_til[e] = nt;
+  s_act[e] = c > 0;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    int a = 0, b = 0, d = 0;
+    if (e >= o) { a = s_cnt[e - o]; b = s_til[e - o]; d = s_act[e - o]; }
+    __syncthreads();
+    s_cnt[e] += a;
+    s_til[e] += b;
+    s_act[e] += d;
+    __syncthreads();
+  }
+  const int off = s_cnt[e] - c, toff = s_til[e] - nt;
+  int* counts = plan;
+  int* offsets = plan + 2 * E;
+  int* num_tiles = plan + 3 * E + 1;
+  int* active = plan + 3 * E + 4;
+  if (e < E) { counts[e] = c; offsets[e] = off; }
+  if (c > 0) active[s_act[e] - 1] = e;
+  if (e == E - 1) { offsets[E] = s_cnt[e]; num_tiles[0] = min(s_til[e], max_tiles); num_tiles[1] = s_act[e]; }
+  for (int i = 0; i < nt; ++i) {
+    if (toff + i < max_tiles) {
+      tile_expert[toff + i] = e;
+      tile_row0[toff + i] = off + i * BM;
+    }
+  }
+  s_cur[e] = off;                     // running write position of each expert
+  __syncthreads();
+  for (int i = e; i < n_pairs; i += 1024) {
+    const int x = idx[i];
+    if (x < 0 || x >= E) continue;
+    sorted_pair[atomicAdd(&s_cur[x], 1)] = i;
+  }
+}
+
 extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan, int* sorted_pair,
                            int* tile_expert, int* tile_row0, int max_tiles, int* status,
                            cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
+  if (n_pairs <= 4096) {
+    moe_plan_small_kernel<<<1, 1024, 0, stream>>>(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0,
+                                                  max_tiles, status);
+    QB_LAUNCH_CHECK();
+    return 0;
+  }
   int* counts = plan;
   int* cursor = plan + E;
   int* offsets = plan + 2 * E;

@@ -257,7 +257,7 @@ def test_router_topk(E, k, bias, renorm, scale):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("path", ["simt", "stream", "tc"])
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2),
-                                       (300, 256, 136, 7, 2)])
+                                       (300, 256, 136, 7, 2), (700, 64, 40, 9, 8)])
 def test_expert_products(dtype, T, H, I, E, k, path):
     kern = K()
     if path != "simt" and dtype != torch.bfloat16:
