@@ -8,10 +8,10 @@
 //    masked by its own token's position, so prompt portions of any length run, from the cache that
 //    earlier steps and this step's rope kernel wrote.  K/V blocks of 64 keys are gathered page by
 //    page into shared memory with cp.async, double buffered.
-//  * decode kernel: one query token, one kv head and one fixed split of 128 keys per block, 64 keys
-//    per warp; the partial (max, sum, O) of each split goes to scratch and a merge kernel adds the
-//    splits in index order.  Split boundaries are multiples of 128 in absolute position, so a token's
-//    result does not depend on the batch.
+//  * decode kernel: persistent blocks, a producer warp that issues bulk asynchronous copies of 64-key
+//    tiles into a ring in shared memory and four consumer warps; the partial (max, sum, O) of each
+//    tile goes to scratch and a merge kernel adds a token's tiles in index order.  Tile boundaries are
+//    multiples of 64 in absolute position, so a token's result does not depend on the batch.
 //
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
 // probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
@@ -23,7 +23,6 @@ namespace {
 constexpr int AT_BN = 64;            // keys per block (span kernel) and per warp (decode kernel)
 constexpr int AT_WARPS = 4;
 constexpr int AT_BM = 16 * AT_WARPS; // query rows per span tile
-constexpr int AT_DEC_WARPS = 2;      // warps of a decode block: 128 keys per split, two or more blocks per SM
 constexpr int AT_PAD = 8;            // +16 bytes a row: ldmatrix rows fall on distinct banks
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -282,106 +281,239 @@ attn_span_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
 }
 
 // ------------------------------------------------------------------------------------------------
-// decode kernel: grid (n_splits_max, n_kv, n_decode_tokens); dec_tok[z] = token row.  The block has
-// W = 2 warps and owns the W*64 keys [split*W*64, (split+1)*W*64).
+// decode kernel: single query tokens against the cache, bound by reading K and V once.
+//
+// Persistent blocks (one per SM) of one PRODUCER warp and four CONSUMER warps around a ring of tiles
+// in shared memory.  A tile is 64 keys of one (token, kv head): its K rows, V rows and the group's Q
+// rows.  The producer resolves a batch of 32 candidate tiles at a time (token -> position -> page
+// ids, all lanes in parallel, so the dependent loads are paid once per batch), then issues one bulk
+// asynchronous copy per row (cp.async.bulk, completion counted on the tile's mbarrier).  Each
+// consumer warp takes every fourth tile: S = Q K^T, softmax, P V on the tensor cores as in the span
+// kernel, and leaves the tile's (max, sum, O) in the scratch; a merge kernel adds a token's tiles in
+// index order.  Tile boundaries are multiples of 64 in absolute position, so a token's result does
+// not depend on the batch.  The ring keeps several tiles in flight per SM whatever a single warp waits
+// for.  Every wait is bounded.
 // scratch: part_o float [n_dec][nq][n_splits_max][hd], part_ml float [n_dec][nq][n_splits_max][2]
 // ------------------------------------------------------------------------------------------------
+constexpr int AD_CONSUMERS = 4;
+constexpr int AD_THREADS = (AD_CONSUMERS + 1) * 32;
+constexpr int AD_MAX_STAGES = 8;
+constexpr uint32_t AD_SPIN_LIMIT = 4u * 1000u * 1000u;
+constexpr uint64_t AD_WAIT_NS = 200ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when another warp gave up or the limit (iterations and 0.2 s) is reached.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t it = 0; it < AD_SPIN_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((it & 63u) == 63u && global_ns() - t0 > AD_WAIT_NS) break;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// one row, global -> shared, completion counted in bytes on the mbarrier; 16-byte aligned, size % 16 == 0
+__device__ __forceinline__ void bulk_copy_row(void* dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+struct AdDesc { int valid, z, kvh, split, pos, lo; };
+
 template <int HDP>
-__global__ void __launch_bounds__(AT_WARPS * 32)
+__global__ void __launch_bounds__(AD_THREADS, 1)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                    const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   const int* __restrict__ dec_tok, const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
-                   const int* __restrict__ block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
-                   int num_pages, float scale_log2, int window, int n_splits_max, int* status) {
+                   const int* __restrict__ dec_tok, int n_dec, const int* __restrict__ tok_pos,
+                   const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int nq, int nkv,
+                   int hd, int page_size, int num_pages, float scale_log2, int window, int n_splits_max, int stages,
+                   int q_rows, int* status) {
   constexpr int LD = HDP + AT_PAD;
-  const int n_warps = blockDim.x >> 5, split_keys = n_warps * AT_BN;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [16][LD]
-  __nv_bfloat16* kbuf = qs + 16 * LD;                                           // [split_keys][LD]
-  __nv_bfloat16* vbuf = kbuf + (size_t)split_keys * LD;                         // [split_keys][LD]
-  float* red = reinterpret_cast<float*>(vbuf + (size_t)split_keys * LD);        // [n_warps][16][HDP + 2]
-  const int z = blockIdx.z, t = dec_tok[z];
-  const int kvh = blockIdx.y, split = blockIdx.x, G = nq / nkv;
-  const int pos = tok_pos[t];
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int key0 = split * split_keys;
-  if (key0 > pos || key0 + split_keys <= lo) return;          // this split holds no visible key
-  const int* bt = block_table + (size_t)tok_req[t] * bt_stride;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
-  const int n_keys = min(split_keys, pos - key0 + 1);
-  const int keys_pad = (n_keys + AT_BN - 1) / AT_BN * AT_BN;
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [stages][q_rows + 128][LD]
+  const size_t stage_elems = (size_t)(q_rows + 2 * AT_BN) * LD;
+  __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES];
+  __shared__ AdDesc desc[AD_MAX_STAGES];
+  __shared__ int s_pages[32][AT_BN + 1];        // page ids of the producer's batch, one row per lane
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = nq / nkv;
 
-  // the split's page ids, fetched once with independent loads, so that the copies below do not each
-  // wait for a table entry
-  __shared__ int s_page[AT_DEC_WARPS * AT_BN];
-  const int pi0 = key0 / page_size, n_pi = (key0 + n_keys - 1) / page_size - pi0 + 1;
-  for (int i = tid; i < n_pi; i += blockDim.x) s_page[i] = bt[pi0 + i];
+  // The ring starts as zeros: padding columns and Q rows past the group are never copied into, and a
+  // tile's unused key rows only ever hold older (finite) keys.
+  for (size_t i = tid; i < stage_elems * stages / 8; i += blockDim.x) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeros above before any bulk copy lands
   __syncthreads();
-  load_kv_block<HDP>(kbuf, k_cache, s_page, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status, pi0);
-  load_kv_block<HDP>(vbuf, v_cache, s_page, key0, keys_pad, pos, kvh, nkv, hd, page_size, num_pages, status, pi0);
-  cp_async_commit();
 
-  for (int rb = 0; rb < G; rb += 16) {                        // 16 heads of the group at a time
-    __syncthreads();
-    for (int c = tid; c < 16 * (HDP / 8); c += blockDim.x) {
-      const int r = c / (HDP / 8), d = (c % (HDP / 8)) * 8;
-      const bool ok = rb + r < G && d < hd;
-      const __nv_bfloat16* src = ok ? q + ((size_t)t * nq + kvh * G + rb + r) * hd + d : q;
-      cp_async16(qs + (size_t)r * LD + d, src, ok);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[HDP / 8][4];
-#pragma unroll
-    for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    int row_lo[2], row_hi[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const bool ok = rb + g + 8 * r < G;
-      row_hi[r] = ok ? pos : -1;
-      row_lo[r] = lo;
-    }
-    if (warp * AT_BN < n_keys)
-      attend_block<HDP>(qs, kbuf + (size_t)warp * AT_BN * LD, vbuf + (size_t)warp * AT_BN * LD, key0 + warp * AT_BN,
-                        row_lo, row_hi, scale_log2, m, l, o);
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-    // every warp leaves (m, l, O) of its 64 keys; rows are merged in warp order
-    float* mine = red + (size_t)warp * 16 * (HDP + 2);
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float* row = mine + (size_t)(g + 8 * r) * (HDP + 2);
-      if (qd == 0) { row[HDP] = m[r]; row[HDP + 1] = l[r]; }
-#pragma unroll
-      for (int i = 0; i < HDP / 8; ++i) {
-        row[i * 8 + qd * 2] = o[i][2 * r];
-        row[i * 8 + qd * 2 + 1] = o[i][2 * r + 1];
+  const uint32_t row_bytes = (uint32_t)hd * 2u;
+  if (warp == AD_CONSUMERS) {
+    // ---------------- producer ----------------
+    const long pairs = (long)n_dec * nkv, total = pairs * n_splits_max;
+    long seq = 0;
+    bool ok = true;
+    for (long batch = blockIdx.x; batch * 32 < total && ok; batch += gridDim.x) {
+      const long item = batch * 32 + lane;
+      int valid = item < total, z = 0, kvh = 0, split = 0, pos = 0, lo = 0, t = 0, pi0 = 0;
+      if (valid) {
+        split = (int)(item / pairs);                       // tiles of one split index are neighbours: the
+        const int rem = (int)(item % pairs);               // work of a batch is alike, batches are dealt round robin
+        z = rem / nkv;
+        kvh = rem % nkv;
+        t = dec_tok[z];
+        pos = tok_pos[t];
+        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int key0 = split * AT_BN;
+        valid = key0 <= pos && key0 + AT_BN > lo;
+        if (valid) {
+          const int* bt = block_table + (size_t)tok_req[t] * bt_stride;
+          const int last = min(pos, key0 + AT_BN - 1);
+          pi0 = key0 / page_size;
+          const int n_pi = last / page_size - pi0 + 1;
+          for (int i = 0; i < n_pi; ++i) {
+            const int pg = bt[pi0 + i];
+            if (pg < 0 || pg >= num_pages) {
+              qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 6);
+              valid = 0;
+            }
+            s_pages[lane][i] = pg;
+          }
+        }
       }
-    }
-    __syncthreads();
-    for (int c = tid; c < 16 * hd; c += blockDim.x) {
-      const int r = c / hd, d = c % hd;
-      if (rb + r >= G) continue;
-      float M = -INFINITY;
-      for (int w = 0; w < n_warps; ++w) M = fmaxf(M, red[((size_t)w * 16 + r) * (HDP + 2) + HDP]);
-      float acc = 0.f, L = 0.f;
-      for (int w = 0; w < n_warps; ++w) {
-        const float* row = red + ((size_t)w * 16 + r) * (HDP + 2);
-        const float f = row[HDP] == -INFINITY ? 0.f : exp2f(row[HDP] - M);
-        acc += f * row[d];
-        L += f * row[HDP + 1];
+      __syncwarp();
+      for (int src = 0; src < 32 && ok; ++src) {
+        if (!__shfl_sync(0xffffffffu, valid, src)) continue;
+        const int b_z = __shfl_sync(0xffffffffu, z, src), b_kvh = __shfl_sync(0xffffffffu, kvh, src);
+        const int b_split = __shfl_sync(0xffffffffu, split, src), b_pos = __shfl_sync(0xffffffffu, pos, src);
+        const int b_lo = __shfl_sync(0xffffffffu, lo, src), b_t = __shfl_sync(0xffffffffu, t, src);
+        const int b_pi0 = __shfl_sync(0xffffffffu, pi0, src);
+        const int slot = (int)(seq % stages);
+        const uint32_t ph = (uint32_t)(seq / stages) & 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);   // one answer per warp
+        if (!ok) break;
+        const int key0 = b_split * AT_BN;
+        const int n_keys = min(AT_BN, b_pos - key0 + 1);
+        const uint32_t bar = smem_u32(&full[slot]);
+        if (lane == 0) {
+          desc[slot] = AdDesc{1, b_z, b_kvh, b_split, b_pos, b_lo};
+          mbar_expect_tx(bar, (uint32_t)(G + 2 * n_keys) * row_bytes);
+        }
+        __syncwarp();
+        __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
+        __nv_bfloat16* ks = qs + (size_t)q_rows * LD;
+        __nv_bfloat16* vs = ks + (size_t)AT_BN * LD;
+        for (int r = lane; r < G; r += 32)
+          bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)b_t * nq + b_kvh * G + r) * hd, row_bytes, bar);
+        for (int r = lane; r < n_keys; r += 32) {
+          const int key = key0 + r;
+          const int pg = s_pages[src][key / page_size - b_pi0];
+          const size_t off = (((size_t)pg * nkv + b_kvh) * page_size + key % page_size) * hd;
+          bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
+          bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+        }
+        ++seq;
       }
-      const int head = kvh * G + rb + r;
-      const size_t slot = ((size_t)z * nq + head) * n_splits_max + split;
-      part_o[slot * hd + d] = acc;
-      if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+      __syncwarp();
+    }
+    // one terminator for each consumer (consecutive sequence numbers reach all four)
+    for (int c = 0; c < AD_CONSUMERS && ok; ++c, ++seq) {
+      const int slot = (int)(seq % stages);
+      const uint32_t ph = (uint32_t)(seq / stages) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      if (lane == 0) {
+        desc[slot] = AdDesc{0, 0, 0, 0, 0, 0};
+        mbar_arrive(smem_u32(&full[slot]));
+      }
+      __syncwarp();
+    }
+    if (!ok) {
+      // gave up: let the copies already issued land before the block's shared memory is given away
+      const uint64_t t0 = global_ns();
+      while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+  } else {
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, qd = lane & 3;
+    for (long seq = warp;; seq += AD_CONSUMERS) {
+      const int slot = (int)(seq % stages);
+      const uint32_t ph = (uint32_t)(seq / stages) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), ph, abort_flag) ? 1 : 0)) break;
+      const AdDesc d = desc[slot];
+      if (!d.valid) {          // the terminator: give the slot back (the producer may still need it) and stop
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
+        break;
+      }
+      const __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
+      const __nv_bfloat16* ks = qs + (size_t)q_rows * LD;
+      const __nv_bfloat16* vs = ks + (size_t)AT_BN * LD;
+      const int key0 = d.split * AT_BN;
+      for (int rb = 0; rb < G; rb += 16) {
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[HDP / 8][4];
+#pragma unroll
+        for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        int row_lo[2], row_hi[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          row_hi[r] = (rb + g + 8 * r < G) ? d.pos : -1;
+          row_lo[r] = d.lo;
+        }
+        attend_block<HDP>(qs + (size_t)rb * LD, ks, vs, key0, row_lo, row_hi, scale_log2, m, l, o);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+          l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+          const int row = rb + g + 8 * r;
+          if (row >= G) continue;
+          const size_t at = ((size_t)d.z * nq + d.kvh * G + row) * n_splits_max + d.split;
+          if (qd == 0) { part_ml[at * 2] = m[r]; part_ml[at * 2 + 1] = l[r]; }
+#pragma unroll
+          for (int i = 0; i < HDP / 8; ++i) {
+            const int dd = i * 8 + qd * 2;
+            if (dd < hd) *reinterpret_cast<float2*>(part_o + at * hd + dd) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));      // the tile's rows have been read: the slot is free
     }
   }
+  __syncthreads();
+  if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 6);
 }
 
 // out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits that hold visible keys
@@ -446,7 +578,7 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
 }
 
 // Keys per decode split for a head size (the Python side sizes the scratch with it).
-extern "C" int qb_attn_decode_split_keys(int hd) { (void)hd; return AT_DEC_WARPS * AT_BN; }
+extern "C" int qb_attn_decode_split_keys(int hd) { (void)hd; return AT_BN; }
 
 // Scratch, in floats: part_o n_dec*nq*n_splits_max*hd, part_ml n_dec*nq*n_splits_max*2, where
 // n_splits_max >= ceil(longest context / split keys).
@@ -459,17 +591,28 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535 || n_dec > 65535 || n_splits_max <= 0)
     return QB_ERR_UNSUPPORTED;
   const float scale_log2 = scale * 1.4426950408889634f;
-  const int warps = AT_DEC_WARPS, split_keys = warps * AT_BN;
-  dim3 grid(n_splits_max, nkv, n_dec);
+  const int split_keys = AT_BN;
+  const int G = nq / nkv, q_rows = (G + 15) / 16 * 16;
+  int dev = 0, sms = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (err != cudaSuccess) return (int)err;
+  const long total = (long)n_dec * nkv * n_splits_max;
+  const long batches = (total + 31) / 32;
+  const int blocks = (int)(batches < sms ? batches : sms);
 #define QB_DEC(HDP)                                                                                        \
   do {                                                                                                     \
-    const size_t smem = (size_t)(16 + 2 * split_keys) * (HDP + AT_PAD) * 2 + (size_t)warps * 16 * (HDP + 2) * 4; \
+    const size_t stage_bytes = (size_t)(q_rows + 2 * AT_BN) * (HDP + AT_PAD) * 2;                          \
+    int stages = (int)((size_t)(196 * 1024) / stage_bytes);                                                \
+    if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;                                                    \
+    if (stages < 2) return QB_ERR_UNSUPPORTED;                                                             \
+    const size_t smem = stage_bytes * stages;                                                              \
     int rc = set_smem(attn_decode_kernel<HDP>, smem);                                                      \
     if (rc) return rc;                                                                                     \
-    attn_decode_kernel<HDP><<<grid, warps * 32, smem, stream>>>(                                           \
+    attn_decode_kernel<HDP><<<blocks, AD_THREADS, smem, stream>>>(                                         \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_o, part_ml, \
-        dec_tok, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, num_pages, scale_log2,   \
-        window, n_splits_max, status);                                                                     \
+        dec_tok, n_dec, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, num_pages, scale_log2, \
+        window, n_splits_max, stages, q_rows, status);                                                     \
   } while (0)
   if (hd <= 64) QB_DEC(64);
   else if (hd <= 128) QB_DEC(128);
