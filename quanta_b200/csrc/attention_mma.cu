@@ -384,12 +384,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const long pairs = (long)n_dec * nkv, total = pairs * n_splits_max;
     long seq = 0;
     bool ok = true;
-    for (long batch = blockIdx.x; batch * 32 < total && ok; batch += gridDim.x) {
-      const long item = batch * 32 + lane;
+    // Candidate tiles are numbered split-major and dealt to the blocks round robin, so every block gets
+    // the same mix of early and late tiles; a lane resolves one candidate, 32 at a time.
+    for (long round = 0; blockIdx.x + round * 32 * (long)gridDim.x < total && ok; ++round) {
+      const long item = blockIdx.x + (round * 32 + lane) * (long)gridDim.x;
       int valid = item < total, z = 0, kvh = 0, split = 0, pos = 0, lo = 0, t = 0, pi0 = 0;
       if (valid) {
-        split = (int)(item / pairs);                       // tiles of one split index are neighbours: the
-        const int rem = (int)(item % pairs);               // work of a batch is alike, batches are dealt round robin
+        split = (int)(item / pairs);
+        const int rem = (int)(item % pairs);
         z = rem / nkv;
         kvh = rem % nkv;
         t = dec_tok[z];
@@ -447,8 +449,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       }
       __syncwarp();
     }
-    // one terminator for each consumer (consecutive sequence numbers reach all four)
-    for (int c = 0; c < AD_CONSUMERS && ok; ++c, ++seq) {
+    // a terminator in every slot: each consumer meets one on a slot of its own
+    for (int c = 0; c < stages && ok; ++c, ++seq) {
       const int slot = (int)(seq % stages);
       const uint32_t ph = (uint32_t)(seq / stages) & 1u;
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
@@ -467,8 +469,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   } else {
     // ---------------- consumers ----------------
     const int g = lane >> 2, qd = lane & 3;
-    for (long seq = warp;; seq += AD_CONSUMERS) {
+    // A consumer owns the slots s with s % 4 == warp and sees every phase of them, in order: the
+    // parity it waits for is then never more than one phase ahead of the barrier.
+    for (long seq = 0; warp < stages; ++seq) {
       const int slot = (int)(seq % stages);
+      if (slot % AD_CONSUMERS != warp) continue;
       const uint32_t ph = (uint32_t)(seq / stages) & 1u;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), ph, abort_flag) ? 1 : 0)) break;
       const AdDesc d = desc[slot];
@@ -598,13 +603,12 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (err != cudaSuccess) return (int)err;
   const long total = (long)n_dec * nkv * n_splits_max;
-  const long batches = (total + 31) / 32;
-  const int blocks = (int)(batches < sms ? batches : sms);
+  const int blocks = (int)(total < sms ? total : sms);
 #define QB_DEC(HDP)                                                                                        \
   do {                                                                                                     \
     const size_t stage_bytes = (size_t)(q_rows + 2 * AT_BN) * (HDP + AT_PAD) * 2;                          \
     int stages = (int)((size_t)(196 * 1024) / stage_bytes);                                                \
-    if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;                                                    \
+    stages = stages >= 8 ? 8 : (stages >= 4 ? 4 : stages);   /* a multiple of the consumers: equal shares */ \
     if (stages < 2) return QB_ERR_UNSUPPORTED;                                                             \
     const size_t smem = stage_bytes * stages;                                                              \
     int rc = set_smem(attn_decode_kernel<HDP>, smem);                                                      \
