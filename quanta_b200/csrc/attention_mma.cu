@@ -16,11 +16,16 @@
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
 // probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
 // head_dim: any multiple of 16 up to 256 (template padding 64 / 128 / 256, dims past head_dim are zero).
+#include <cuda.h>
+
+#include <cstring>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
 
-constexpr int AT_BN = 64;            // keys per block (span kernel) and per warp (decode kernel)
+constexpr int AT_BN = 64;           // keys per block (span kernel) and per warp (decode kernel)
 constexpr int AT_WARPS = 4;
 constexpr int AT_BM = 16 * AT_WARPS; // query rows per span tile
 constexpr int AT_PAD = 8;            // +16 bytes a row: ldmatrix rows fall on distinct banks
@@ -88,7 +93,25 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfl
 //   qs: the warp's 16 rows [16][HDP+PAD]; ks, vs: [AT_BN][HDP+PAD]
 //   row_hi[2], row_lo[2]: last / first visible key of the thread's two rows (g and g+8), absolute
 //   key0: absolute position of ks row 0.   m, l, o: running max (log2 domain), partial sum, output.
+// How a K or V tile of 64 keys lies in shared memory.
+//  PaddedKV:   rows of HDP + 8 elements (what cp.async / per-row bulk copies write).
+//  SwizzledKV: what TMA tensor loads with the 128-byte swizzle write: head_dim in slabs of 64 dims, each
+//              slab [64 keys][64 dims] with rows of 128 bytes whose 16-byte chunks are XORed with (row & 7);
+//              the tile is 1024-byte aligned.  Both are free of bank conflicts for ldmatrix.
 template <int HDP>
+struct PaddedKV {
+  static __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) {
+    return base + (size_t)row * (HDP + AT_PAD) + dim;
+  }
+};
+struct SwizzledKV {
+  static __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) {
+    const int chunk = (dim & 63) >> 3;
+    return base + (dim >> 6) * (AT_BN * 64) + row * 64 + ((chunk ^ (row & 7)) << 3) + (dim & 7);
+  }
+};
+
+template <int HDP, typename KV = PaddedKV<HDP>>
 __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv_bfloat16* ks, const __nv_bfloat16* vs,
                                              int key0, const int (&row_lo)[2], const int (&row_hi)[2],
                                              float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HDP / 8][4]) {
@@ -104,7 +127,7 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 #pragma unroll
     for (int nt = 0; nt < AT_BN / 16; ++nt) {
       uint32_t b[4];
-      ldmatrix_x4(b, ks + (size_t)(nt * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+      ldmatrix_x4(b, KV::at(ks, nt * 16 + (lane & 7) + 8 * (lane >> 4), kk * 16 + 8 * ((lane >> 3) & 1)));
       mma16816(s[2 * nt], a, b[0], b[1]);
       mma16816(s[2 * nt + 1], a, b[2], b[3]);
     }
@@ -154,7 +177,7 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 #pragma unroll
     for (int dt = 0; dt < HDP / 16; ++dt) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, vs + (size_t)(j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dt * 16 + 8 * (lane >> 4));
+      ldmatrix_x4_trans(b, KV::at(vs, j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt * 16 + 8 * (lane >> 4)));
       mma16816(o[2 * dt], a, b[0], b[1]);
       mma16816(o[2 * dt + 1], a, b[2], b[3]);
     }
@@ -342,20 +365,43 @@ __device__ __forceinline__ void bulk_copy_row(void* dst, const void* src, uint32
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// one [box rows x 64 dims] box of a cache seen as a 2-D tensor [rows, head_dim]; no multicast
+__device__ __forceinline__ void tma_load_tile(void* dst, const CUtensorMap* map, int dim0, int row, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(dim0), "r"(row), "r"(bar) : "memory");
+}
+
 struct AdDesc { int valid, z, kvh, split, pos, lo; };
 
-template <int HDP>
+// Elements of one ring stage: the Q rows (padded rows), then the K tile and the V tile.  With TMA the
+// tiles are swizzled slabs and every part starts on a 1024-byte boundary.
+__host__ __device__ constexpr size_t ad_q_elems(int hdp, int q_rows, bool tma) {
+  return tma ? ((size_t)q_rows * (hdp + AT_PAD) + 511) / 512 * 512 : (size_t)q_rows * (hdp + AT_PAD);
+}
+__host__ __device__ constexpr size_t ad_tile_elems(int hdp, bool tma) {
+  return tma ? (size_t)(hdp / 64) * AT_BN * 64 : (size_t)AT_BN * (hdp + AT_PAD);
+}
+
+// TMA: K and V tiles come as tensor loads of [rows of one page x 64 dims] boxes with the 128-byte swizzle
+// (a page's keys of one kv head are contiguous rows of the cache seen as [pages*kv_heads*page_size, hd]):
+// 16 requests per tile instead of 128 row copies.  Needs hd % 64 == 0 and a power-of-two page size.
+template <int HDP, bool TMA>
 __global__ void __launch_bounds__(AD_THREADS, 1)
-attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                    const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const int* __restrict__ dec_tok, int n_dec, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int nq, int nkv,
                    int hd, int page_size, int num_pages, float scale_log2, int window, int n_splits_max, int stages,
                    int q_rows, int* status) {
   constexpr int LD = HDP + AT_PAD;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [stages][q_rows + 128][LD]
-  const size_t stage_elems = (size_t)(q_rows + 2 * AT_BN) * LD;
+  using KV = typename std::conditional<TMA, SwizzledKV, PaddedKV<HDP>>::type;
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [stages][Q | K tile | V tile]
+  const size_t q_elems = ad_q_elems(HDP, q_rows, TMA), tile_elems = ad_tile_elems(HDP, TMA);
+  const size_t stage_elems = q_elems + 2 * tile_elems;
   __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES];
   __shared__ AdDesc desc[AD_MAX_STAGES];
   __shared__ int s_pages[32][AT_BN + 1];        // page ids of the producer's batch, one row per lane
@@ -428,22 +474,38 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         const int key0 = b_split * AT_BN;
         const int n_keys = min(AT_BN, b_pos - key0 + 1);
         const uint32_t bar = smem_u32(&full[slot]);
+        __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
+        __nv_bfloat16* ks = qs + q_elems;
+        __nv_bfloat16* vs = ks + tile_elems;
+        // boxes of the TMA path: rows of one page (or 64 rows of a larger page) x 64 dims
+        const int box_rows = min(page_size, AT_BN), n_slabs = hd / 64;
+        const int n_boxes = (n_keys + box_rows - 1) / box_rows;          // pages of the tile that hold visible keys
         if (lane == 0) {
           desc[slot] = AdDesc{1, b_z, b_kvh, b_split, b_pos, b_lo};
-          mbar_expect_tx(bar, (uint32_t)(G + 2 * n_keys) * row_bytes);
+          const uint32_t kv_bytes = TMA ? (uint32_t)(2 * n_boxes * n_slabs * box_rows) * 128u
+                                        : (uint32_t)(2 * n_keys) * row_bytes;
+          mbar_expect_tx(bar, (uint32_t)G * row_bytes + kv_bytes);
         }
         __syncwarp();
-        __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
-        __nv_bfloat16* ks = qs + (size_t)q_rows * LD;
-        __nv_bfloat16* vs = ks + (size_t)AT_BN * LD;
         for (int r = lane; r < G; r += 32)
           bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)b_t * nq + b_kvh * G + r) * hd, row_bytes, bar);
-        for (int r = lane; r < n_keys; r += 32) {
-          const int key = key0 + r;
-          const int pg = s_pages[src][key / page_size - b_pi0];
-          const size_t off = (((size_t)pg * nkv + b_kvh) * page_size + key % page_size) * hd;
-          bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
-          bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+        if (TMA) {
+          for (int i = lane; i < 2 * n_boxes * n_slabs; i += 32) {
+            const int which = i & 1, slab = (i >> 1) % n_slabs, box = (i >> 1) / n_slabs;
+            const int key = key0 + box * box_rows;
+            const int pg = s_pages[src][key / page_size - b_pi0];
+            const int row = (pg * nkv + b_kvh) * page_size + key % page_size;       // row of the cache seen as 2-D
+            __nv_bfloat16* dst = (which ? vs : ks) + (size_t)slab * (AT_BN * 64) + (size_t)box * box_rows * 64;
+            tma_load_tile(dst, which ? &tm_v : &tm_k, slab * 64, row, bar);
+          }
+        } else {
+          for (int r = lane; r < n_keys; r += 32) {
+            const int key = key0 + r;
+            const int pg = s_pages[src][key / page_size - b_pi0];
+            const size_t off = (((size_t)pg * nkv + b_kvh) * page_size + key % page_size) * hd;
+            bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
+            bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+          }
         }
         ++seq;
       }
@@ -483,8 +545,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         break;
       }
       const __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
-      const __nv_bfloat16* ks = qs + (size_t)q_rows * LD;
-      const __nv_bfloat16* vs = ks + (size_t)AT_BN * LD;
+      const __nv_bfloat16* ks = qs + q_elems;
+      const __nv_bfloat16* vs = ks + tile_elems;
       const int key0 = d.split * AT_BN;
       for (int rb = 0; rb < G; rb += 16) {
         float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -497,7 +559,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
           row_hi[r] = (rb + g + 8 * r < G) ? d.pos : -1;
           row_lo[r] = d.lo;
         }
-        attend_block<HDP>(qs + (size_t)rb * LD, ks, vs, key0, row_lo, row_hi, scale_log2, m, l, o);
+        attend_block<HDP, KV>(qs + (size_t)rb * LD, ks, vs, key0, row_lo, row_hi, scale_log2, m, l, o);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -543,6 +605,38 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     }
     out[((size_t)t * nq + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A cache [rows, hd] bfloat16 row-major, boxes of [box_rows, 64 dims], 128-byte swizzle
+int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t hd, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return QB_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {hd, rows};
+  const cuuint64_t strides[1] = {hd * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : QB_ERR_BAD_ARG;
 }
 
 template <typename Kern>
@@ -604,23 +698,43 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (err != cudaSuccess) return (int)err;
   const long total = (long)n_dec * nkv * n_splits_max;
   const int blocks = (int)(total < sms ? total : sms);
-#define QB_DEC(HDP)                                                                                        \
+  // TMA tensor loads when the shapes allow (whole 64-dim slabs, pages that tile 64 keys), else row copies
+  const bool pow2 = (page_size & (page_size - 1)) == 0;
+  const bool tma = hd % 64 == 0 && pow2 && (page_size <= AT_BN || page_size % AT_BN == 0) && encode_fn() != nullptr &&
+                   (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+  CUtensorMap tm_k, tm_v;
+  memset(&tm_k, 0, sizeof(tm_k));
+  memset(&tm_v, 0, sizeof(tm_v));
+  if (tma) {
+    const uint64_t rows = (uint64_t)num_pages * nkv * page_size;
+    const uint32_t box_rows = (uint32_t)(page_size < AT_BN ? page_size : AT_BN);
+    int rc = make_kv_map(&tm_k, k_cache, rows, (uint64_t)hd, box_rows);
+    if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, (uint64_t)hd, box_rows);
+    if (rc) return rc;
+  }
+#define QB_DEC(HDP, TMA_)                                                                                  \
   do {                                                                                                     \
-    const size_t stage_bytes = (size_t)(q_rows + 2 * AT_BN) * (HDP + AT_PAD) * 2;                          \
-    int stages = (int)((size_t)(196 * 1024) / stage_bytes);                                                \
+    const size_t stage_bytes = (ad_q_elems(HDP, q_rows, TMA_) + 2 * ad_tile_elems(HDP, TMA_)) * 2;         \
+    int stages = (int)((size_t)(194 * 1024) / stage_bytes);                                                \
     stages = stages >= 8 ? 8 : (stages >= 4 ? 4 : stages);   /* a multiple of the consumers: equal shares */ \
     if (stages < 2) return QB_ERR_UNSUPPORTED;                                                             \
-    const size_t smem = stage_bytes * stages;                                                              \
-    int rc = set_smem(attn_decode_kernel<HDP>, smem);                                                      \
+    const size_t smem = stage_bytes * stages + 1024;         /* room to align the ring to 1024 bytes */    \
+    int rc = set_smem(attn_decode_kernel<HDP, TMA_>, smem);                                                \
     if (rc) return rc;                                                                                     \
-    attn_decode_kernel<HDP><<<blocks, AD_THREADS, smem, stream>>>(                                         \
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part_o, part_ml, \
-        dec_tok, n_dec, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, num_pages, scale_log2, \
-        window, n_splits_max, stages, q_rows, status);                                                     \
+    attn_decode_kernel<HDP, TMA_><<<blocks, AD_THREADS, smem, stream>>>(                                   \
+        tm_k, tm_v, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+        part_o, part_ml, dec_tok, n_dec, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, \
+        num_pages, scale_log2, window, n_splits_max, stages, q_rows, status);                              \
   } while (0)
-  if (hd <= 64) QB_DEC(64);
-  else if (hd <= 128) QB_DEC(128);
-  else QB_DEC(256);
+  if (tma) {
+    if (hd <= 64) QB_DEC(64, true);
+    else if (hd <= 128) QB_DEC(128, true);
+    else QB_DEC(256, true);
+  } else {
+    if (hd <= 64) QB_DEC(64, false);
+    else if (hd <= 128) QB_DEC(128, false);
+    else QB_DEC(256, false);
+  }
 #undef QB_DEC
   attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, tok_pos, nq,
                                                          hd, window, n_splits_max, split_keys);

@@ -16,24 +16,29 @@ template <int NPL>   // experts per lane, E <= 32*NPL
 __global__ void router_topk_kernel(const float* __restrict__ logits, int n_partials,
                                    const float* __restrict__ bias, int* __restrict__ idx_out,
                                    float* __restrict__ w_out, int T, int E, int k, int renorm, float scale) {
-  // logits: [n_partials][T][E]; the partial products of the inner dimension are added in index order
+  // logits: [n_partials][T][E]; the partial products of the inner dimension are added in index order.
+  // One block per token: all threads add the partials (many independent loads in flight), then the
+  // first warp selects.
+  __shared__ float s_logit[1024];
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t = blockIdx.x;
   if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
   const size_t pstride = (size_t)T * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float x = 0.f;
+#pragma unroll 8
+    for (int p = 0; p < n_partials; ++p) x += lg[p * pstride + e];
+    s_logit[e] = x;
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
   float choice[NPL], score[NPL], logit[NPL];
   unsigned taken = 0u;
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) logit[i] = 0.f;
-  // partial sums in index order; the loads of one partial are independent and issued together
-#pragma unroll 4
-  for (int p = 0; p < n_partials; ++p) {
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int e = lane + 32 * i;
-      if (e < E) logit[i] += lg[p * pstride + e];
-    }
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    logit[i] = e < E ? s_logit[e] : 0.f;
   }
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
@@ -92,7 +97,7 @@ extern "C" int qb_router_topk(const float* logits, int n_partials, const float* 
   if (T <= 0) return 0;
   if (k <= 0 || k > E || n_partials <= 0) return QB_ERR_BAD_ARG;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
-  const int warps = 4, blocks = (T + warps - 1) / warps;
+  const int warps = 4, blocks = T;
 #define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale)
   if (E <= 32) QB_ROUTE(1);
   else if (E <= 64) QB_ROUTE(2);
