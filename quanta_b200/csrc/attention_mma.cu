@@ -3,11 +3,12 @@
 // Two kernels share one inner loop (flash style: S = Q K^T by mma.m16n8k16, online softmax in
 // float32 with exp2, O += P V with P rounded to bfloat16):
 //
-//  * span kernel: a tile of 64 query rows of ONE request and ONE kv head, where a row is a
-//    (token, q head of the group) pair, so grouped heads fill the 16-row MMA operand.  Each row is
-//    masked by its own token's position, so prompt portions of any length run, from the cache that
-//    earlier steps and this step's rope kernel wrote.  K/V blocks of 64 keys are gathered page by
-//    page into shared memory with cp.async, double buffered.
+//  * span kernel: a tile of 128 (64 for head sizes above 128) query rows of ONE request and ONE kv
+//    head, where a row is a (token, q head of the group) pair, so grouped heads fill the 16-row MMA
+//    operand.  Each row is masked by its own token's position, so prompt portions of any length run,
+//    from the cache that earlier steps and this step's rope kernel wrote.  A producer warp streams
+//    K/V blocks of 64 keys through a ring in shared memory (TMA, one box per page); consumer warps
+//    own 16 rows each.
 //  * decode kernel: persistent blocks, a producer warp that issues bulk asynchronous copies of 64-key
 //    tiles into a ring in shared memory and four consumer warps; the partial (max, sum, O) of each
 //    tile goes to scratch and a merge kernel adds a token's tiles in index order.  Tile boundaries are
@@ -180,125 +181,6 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
       ldmatrix_x4_trans(b, KV::at(vs, j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt * 16 + 8 * (lane >> 4)));
       mma16816(o[2 * dt], a, b[0], b[1]);
       mma16816(o[2 * dt + 1], a, b[2], b[3]);
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// span kernel.  tiles[t] = {request row, first token row of the span, tokens in the span, first
-// flattened row (token*G + head) of this tile}.  grid (n_tiles, n_kv).
-// ------------------------------------------------------------------------------------------------
-template <int HDP>
-__global__ void __launch_bounds__(AT_WARPS * 32)
-attn_span_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                 const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
-                 const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
-                 const int* __restrict__ tiles, int nq, int nkv, int hd, int page_size, int num_pages,
-                 float scale_log2, int window, int* status) {
-  constexpr int LD = HDP + AT_PAD;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [AT_BM][LD]
-  __nv_bfloat16* kbuf = qs + AT_BM * LD;                                        // [2][AT_BN][LD]
-  __nv_bfloat16* vbuf = kbuf + 2 * AT_BN * LD;                                  // [2][AT_BN][LD]
-  const int* tile = tiles + 4 * blockIdx.x;
-  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
-  const int kvh = blockIdx.y, G = nq / nkv;
-  const int n_rows = min(AT_BM, n_tok * G - row0);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
-  const int* bt = block_table + (size_t)req * bt_stride;
-
-  // Q rows -> shared memory (zero past head_dim and past the last row)
-  for (int c = tid; c < AT_BM * (HDP / 8); c += blockDim.x) {
-    const int r = c / (HDP / 8), d = (c % (HDP / 8)) * 8;
-    const int R = row0 + r;
-    const bool ok = r < n_rows && d < hd;
-    const __nv_bfloat16* src = q;
-    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd + d;
-    cp_async16(qs + (size_t)r * LD + d, src, ok);
-  }
-  // visible key range of this thread's two rows, and of the whole tile
-  int row_lo[2], row_hi[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int lr = warp * 16 + g + 8 * r;
-    if (lr < n_rows) {
-      const int p = tok_pos[tok0 + (row0 + lr) / G];
-      row_hi[r] = p;
-      row_lo[r] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    } else {
-      row_hi[r] = -1;
-      row_lo[r] = 0;
-    }
-  }
-  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
-  const int key_end = tok_pos[last_tok];
-  const int p_first = tok_pos[first_tok];
-  const int key_begin = (window > 0 && p_first - window + 1 > 0) ? (p_first - window + 1) / AT_BN * AT_BN : 0;
-  const int n_blocks = (key_end - key_begin) / AT_BN + 1;
-
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[HDP / 8][4];
-#pragma unroll
-  for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
-  // the page ids of the keys this tile reads are copied to shared memory once (when they fit), so the
-  // per-block copies do not each wait for a table entry
-  constexpr int MAX_SPAN_PAGES = 2048;
-  __shared__ int s_page[MAX_SPAN_PAGES];
-  int pi0 = key_begin / page_size;
-  const int n_pi = key_end / page_size - pi0 + 1;
-  if (n_pi <= MAX_SPAN_PAGES) {
-    for (int i = tid; i < n_pi; i += blockDim.x) s_page[i] = bt[pi0 + i];
-    bt = s_page;
-    __syncthreads();
-  } else {
-    pi0 = 0;
-  }
-
-  load_kv_block<HDP>(kbuf, k_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status, pi0);
-  load_kv_block<HDP>(vbuf, v_cache, bt, key_begin, AT_BN, key_end, kvh, nkv, hd, page_size, num_pages, status, pi0);
-  cp_async_commit();
-  for (int b = 0; b < n_blocks; ++b) {
-    const int cur = b & 1;
-    if (b + 1 < n_blocks) {
-      const int k0n = key_begin + (b + 1) * AT_BN;
-      load_kv_block<HDP>(kbuf + (cur ^ 1) * AT_BN * LD, k_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
-                         num_pages, status, pi0);
-      load_kv_block<HDP>(vbuf + (cur ^ 1) * AT_BN * LD, v_cache, bt, k0n, AT_BN, key_end, kvh, nkv, hd, page_size,
-                         num_pages, status, pi0);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const int key0 = key_begin + b * AT_BN;
-    // a warp whose rows all end before this block (or start after it) has nothing to add
-    int any_hi = max(row_hi[0], row_hi[1]);
-    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 4));
-    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 8));
-    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 16));
-    if (any_hi >= key0)
-      attend_block<HDP>(qs + (size_t)warp * 16 * LD, kbuf + cur * AT_BN * LD, vbuf + cur * AT_BN * LD, key0, row_lo,
-                        row_hi, scale_log2, m, l, o);
-    __syncthreads();
-  }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-  }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int lr = warp * 16 + g + 8 * r;
-    if (lr >= n_rows) continue;
-    const int R = row0 + lr;
-    __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd;
-    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
-#pragma unroll
-    for (int i = 0; i < HDP / 8; ++i) {
-      const int d = i * 8 + qd * 2;
-      if (d < hd) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
     }
   }
 }
@@ -583,6 +465,195 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 6);
 }
 
+// ------------------------------------------------------------------------------------------------
+// span kernel: prompt portions.  tiles[t] = {request row, first token row of the span, tokens in the
+// span, first flattened row (token*G + head) of this tile}; grid (n_tiles, n_kv).
+//
+// One block = NC*16 query rows (a row is a (token, q head of the group) pair) of ONE request and ONE kv
+// head, NC consumer warps of 16 rows each and one producer warp.  The producer streams the request's
+// keys in blocks of 64 through a ring of K/V tiles in shared memory (TMA tensor loads, one box per
+// page, or per-row bulk copies when the shapes do not allow TMA); consumers wait on a tile's mbarrier,
+// run S = Q K^T, the online softmax and P V for their rows, and release the tile.  No block-wide
+// barrier in the loop.  Each row is masked by its own token's position.
+// ------------------------------------------------------------------------------------------------
+constexpr int SP_MAX_PAGES = 2048;
+
+template <int HDP, bool TMA, int NC>
+__global__ void __launch_bounds__((NC + 1) * 32, 1)
+attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                 const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                 const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
+                 const int* __restrict__ tiles, int nq, int nkv, int hd, int page_size, int num_pages,
+                 float scale_log2, int window, int stages, int* status) {
+  constexpr int LD = HDP + AT_PAD, BM = NC * 16;
+  using KV = typename std::conditional<TMA, SwizzledKV, PaddedKV<HDP>>::type;
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const size_t q_elems = ad_q_elems(HDP, BM, TMA), tile_elems = ad_tile_elems(HDP, TMA);
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);         // [BM][LD]
+  __nv_bfloat16* ring = qs + q_elems;                                      // [stages][K tile | V tile]
+  __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES];
+  __shared__ int s_page[SP_MAX_PAGES];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
+  const int kvh = blockIdx.y, G = nq / nkv;
+  const int n_rows = min(BM, n_tok * G - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
+  const int* bt = block_table + (size_t)req * bt_stride;
+
+  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
+  const int key_end = tok_pos[last_tok];
+  const int p_first = tok_pos[first_tok];
+  const int key_begin = (window > 0 && p_first - window + 1 > 0) ? (p_first - window + 1) / AT_BN * AT_BN : 0;
+  const int n_blocks = (key_end - key_begin) / AT_BN + 1;
+
+  // Q rows (zero past head_dim and past the last row), the ring as zeros, the page ids of the keys read
+  for (int c = tid; c < BM * (HDP / 8); c += blockDim.x) {
+    const int r = c / (HDP / 8), d = (c % (HDP / 8)) * 8;
+    const int R = row0 + r;
+    const bool ok = r < n_rows && d < hd;
+    const __nv_bfloat16* src = q;
+    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd + d;
+    cp_async16(qs + (size_t)r * LD + d, src, ok);
+  }
+  cp_async_commit();
+  for (size_t i = tid; i < 2 * tile_elems * stages / 8; i += blockDim.x) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+  int pi0 = key_begin / page_size;
+  const int n_pi = key_end / page_size - pi0 + 1;
+  const bool pages_in_smem = n_pi <= SP_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = tid; i < n_pi; i += blockDim.x) s_page[i] = bt[pi0 + i];
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), NC);
+    }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  cp_async_wait<0>();
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+
+  if (warp == NC) {
+    // ---------------- producer ----------------
+    const uint32_t row_bytes = (uint32_t)hd * 2u;
+    const int box_rows = min(page_size, AT_BN), n_slabs = hd / 64;
+    bool ok = true;
+    for (int b = 0; b < n_blocks && ok; ++b) {
+      const int slot = b % stages;
+      const uint32_t ph = (uint32_t)(b / stages) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      const int key0 = key_begin + b * AT_BN;
+      const int n_keys = min(AT_BN, key_end - key0 + 1);
+      const int n_boxes = (n_keys + box_rows - 1) / box_rows;
+      const uint32_t bar = smem_u32(&full[slot]);
+      __nv_bfloat16* ks = ring + (size_t)slot * 2 * tile_elems;
+      __nv_bfloat16* vs = ks + tile_elems;
+      // a page id outside the pool is recorded and its rows are not copied (the byte count must match)
+      int bad = 0;
+      const int n_req = TMA ? 2 * n_boxes * n_slabs : n_keys;
+      for (int i = lane; i < n_req; i += 32) {
+        const int key = TMA ? key0 + ((i >> 1) / n_slabs) * box_rows : key0 + i;
+        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+        if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++bad; }
+      }
+      bad = __reduce_add_sync(0xffffffffu, bad);
+      if (lane == 0) {
+        const uint32_t per = TMA ? (uint32_t)box_rows * 128u : 2u * row_bytes;
+        mbar_expect_tx(bar, (uint32_t)(n_req - bad) * per);
+      }
+      __syncwarp();
+      for (int i = lane; i < n_req; i += 32) {
+        if (TMA) {
+          const int which = i & 1, slab = (i >> 1) % n_slabs, box = (i >> 1) / n_slabs;
+          const int key = key0 + box * box_rows;
+          const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+          if (pg < 0 || pg >= num_pages) continue;
+          const int row = (pg * nkv + kvh) * page_size + key % page_size;
+          __nv_bfloat16* dst = (which ? vs : ks) + (size_t)slab * (AT_BN * 64) + (size_t)box * box_rows * 64;
+          tma_load_tile(dst, which ? &tm_v : &tm_k, slab * 64, row, bar);
+        } else {
+          const int key = key0 + i;
+          const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+          if (pg < 0 || pg >= num_pages) continue;
+          const size_t off = (((size_t)pg * nkv + kvh) * page_size + key % page_size) * hd;
+          bulk_copy_row(ks + (size_t)i * LD, k_cache + off, row_bytes, bar);
+          bulk_copy_row(vs + (size_t)i * LD, v_cache + off, row_bytes, bar);
+        }
+      }
+    }
+    if (!ok) {
+      const uint64_t t0 = global_ns();
+      while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+  } else {
+    // ---------------- consumers: 16 rows each ----------------
+    int row_lo[2], row_hi[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int lr = warp * 16 + g + 8 * r;
+      if (lr < n_rows) {
+        const int p = tok_pos[tok0 + (row0 + lr) / G];
+        row_hi[r] = p;
+        row_lo[r] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+      } else {
+        row_hi[r] = -1;
+        row_lo[r] = 0;
+      }
+    }
+    int any_hi = max(row_hi[0], row_hi[1]);
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 4));
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 8));
+    any_hi = max(any_hi, __shfl_xor_sync(0xffffffffu, any_hi, 16));
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HDP / 8][4];
+#pragma unroll
+    for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    bool ok = true;
+    for (int b = 0; b < n_blocks; ++b) {
+      const int slot = b % stages;
+      const uint32_t ph = (uint32_t)(b / stages) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), ph, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      const int key0 = key_begin + b * AT_BN;
+      const __nv_bfloat16* ks = ring + (size_t)slot * 2 * tile_elems;
+      // a warp whose rows all end before this block has nothing to add
+      if (any_hi >= key0)
+        attend_block<HDP, KV>(qs + (size_t)warp * 16 * LD, ks, ks + tile_elems, key0, row_lo, row_hi, scale_log2, m, l, o);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
+    }
+    if (ok) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int lr = warp * 16 + g + 8 * r;
+        if (lr >= n_rows) continue;
+        const int R = row0 + lr;
+        __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * hd;
+        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+#pragma unroll
+        for (int i = 0; i < HDP / 8; ++i) {
+          const int d = i * 8 + qd * 2;
+          if (d < hd) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
+}
+
 // out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits that hold visible keys
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, const int* __restrict__ dec_tok,
@@ -650,6 +721,9 @@ int set_smem(Kern kern, size_t smem) {
 
 }  // namespace
 
+// Query rows (token x head of the group) per tile of the span kernel, for a head size.
+extern "C" int qb_attn_span_rows(int hd) { return hd <= 128 ? 128 : 64; }
+
 extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
                             const int* block_table, int bt_stride, const int* tiles, int n_tiles, int nq, int nkv,
                             int hd, int page_size, int num_pages, float scale, int window, int* status,
@@ -658,19 +732,42 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
   if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535) return QB_ERR_UNSUPPORTED;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_tiles, nkv);
-#define QB_SPAN(HDP)                                                                                       \
+  const bool pow2 = (page_size & (page_size - 1)) == 0;
+  const bool tma = hd % 64 == 0 && pow2 && (page_size <= AT_BN || page_size % AT_BN == 0) && encode_fn() != nullptr &&
+                   (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+  CUtensorMap tm_k, tm_v;
+  memset(&tm_k, 0, sizeof(tm_k));
+  memset(&tm_v, 0, sizeof(tm_v));
+  if (tma) {
+    const uint64_t rows = (uint64_t)num_pages * nkv * page_size;
+    const uint32_t box_rows = (uint32_t)(page_size < AT_BN ? page_size : AT_BN);
+    int rc = make_kv_map(&tm_k, k_cache, rows, (uint64_t)hd, box_rows);
+    if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, (uint64_t)hd, box_rows);
+    if (rc) return rc;
+  }
+#define QB_SPAN(HDP, TMA_, NC_)                                                                            \
   do {                                                                                                     \
-    const size_t smem = (size_t)(AT_BM + 4 * AT_BN) * (HDP + AT_PAD) * 2;                                   \
-    int rc = set_smem(attn_span_kernel<HDP>, smem);                                                        \
+    const size_t q_bytes = ad_q_elems(HDP, NC_ * 16, TMA_) * 2, stage_bytes = 2 * ad_tile_elems(HDP, TMA_) * 2; \
+    int stages = (int)(((size_t)(192 * 1024) - q_bytes) / stage_bytes);                                    \
+    if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;                                                    \
+    if (stages < 2) return QB_ERR_UNSUPPORTED;                                                             \
+    const size_t smem = q_bytes + stage_bytes * stages + 1024;                                             \
+    int rc = set_smem(attn_span_kernel<HDP, TMA_, NC_>, smem);                                             \
     if (rc) return rc;                                                                                     \
-    attn_span_kernel<HDP><<<grid, AT_WARPS * 32, smem, stream>>>(                                          \
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,              \
+    attn_span_kernel<HDP, TMA_, NC_><<<grid, (NC_ + 1) * 32, smem, stream>>>(                              \
+        tm_k, tm_v, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,  \
         (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv, hd, page_size, num_pages,     \
-        scale_log2, window, status);                                                                       \
+        scale_log2, window, stages, status);                                                               \
   } while (0)
-  if (hd <= 64) QB_SPAN(64);
-  else if (hd <= 128) QB_SPAN(128);
-  else QB_SPAN(256);
+  if (tma) {
+    if (hd <= 64) QB_SPAN(64, true, 8);
+    else if (hd <= 128) QB_SPAN(128, true, 8);
+    else QB_SPAN(256, true, 4);
+  } else {
+    if (hd <= 64) QB_SPAN(64, false, 8);
+    else if (hd <= 128) QB_SPAN(128, false, 8);
+    else QB_SPAN(256, false, 4);
+  }
 #undef QB_SPAN
   QB_LAUNCH_CHECK();
   return 0;

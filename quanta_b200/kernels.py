@@ -175,7 +175,9 @@ def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table
         _p(status), _stream()), "paged_attention_simt")
 
 
-ATTN_SPAN_ROWS = 64          # query rows (token x head-of-group) per tile of the span kernel
+def attn_span_rows(hd: int) -> int:
+    """Query rows (token x head-of-group) per tile of the span kernel for a head size."""
+    return int(lib().qb_attn_span_rows(int(hd)))
 
 
 def attn_decode_split_keys(hd: int) -> int:

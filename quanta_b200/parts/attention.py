@@ -107,9 +107,9 @@ class GQAttention(Mixer):
                                 cache.block_table, self.scale, window, n_splits, ctx.status)
         if spans:
             G = self.nq // self.nkv
-            key = ("span_tiles", G)
+            key = ("span_tiles", G, self.hd)
             if key not in ctx.work:
-                rows = kernels.ATTN_SPAN_ROWS
+                rows = kernels.attn_span_rows(self.hd)
                 tiles = [[r, t0, n, r0] for (r, t0, n) in spans for r0 in range(0, n * G, rows)]
                 ctx.work[key] = torch.tensor(tiles, dtype=torch.int32).to(q.device, non_blocking=True)
             kernels.attn_span(q, cache.k, cache.v, out, ctx.tok_pos, cache.block_table, ctx.work[key], self.scale,

@@ -190,7 +190,7 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
             if n == 1:
                 dec.append(row0)
             else:
-                tiles += [[r, row0, n, x] for x in range(0, n * G, k.ATTN_SPAN_ROWS)]
+                tiles += [[r, row0, n, x] for x in range(0, n * G, k.attn_span_rows(hd))]
             row0 += n
         split = k.attn_decode_split_keys(hd)
         n_splits = -(-(max(a + n for a, n in spans)) // split)
