@@ -38,6 +38,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 FULL_LAYERS = 62
+PREFILL_TOKENS = 2048
 SIZES = dict(vocab_size=200064, hidden_size=3072, intermediate_size=1536, num_attention_heads=48,
              num_key_value_heads=8, head_dim=128, rotary_dim=64, rope_theta=5e6, use_qk_norm=True,
              qk_norm_type="per_layer", num_local_experts=256, num_experts_per_tok=8, use_routing_bias=True,
@@ -166,19 +167,20 @@ def run_ours(args) -> dict:
         return [a.elapsed_time(b) for a, b in evs[n_warm:]]
 
     # ---- prefill: one 2,048-token prompt as one step ----
+    pf_tokens = min(PREFILL_TOKENS, prompt_len)
     pre_ms = []
     for i in range(3 + 3):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        p = toks(prompt_len)
+        p = toks(pf_tokens)
         torch.cuda.synchronize()
         a.record()
-        eng.step([StepEntry(("pf", i), p, (prompt_len - 1,))], end=[("pf", i)])
+        eng.step([StepEntry(("pf", i), p, (pf_tokens - 1,))], end=[("pf", i)])
         b.record()
         torch.cuda.synchronize()
         pre_ms.append(a.elapsed_time(b))
     pre = statistics.median(pre_ms[3:])
-    pf = prefill_flops(raw, layers, prompt_len)
-    prefill = {"value": round(prompt_len / pre * 1e3, 1), "tokens": prompt_len, "ms": round(pre, 3),
+    pf = prefill_flops(raw, layers, pf_tokens)
+    prefill = {"value": round(pf_tokens / pre * 1e3, 1), "tokens": pf_tokens, "ms": round(pre, 3),
                "frac": round(pf / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
@@ -186,7 +188,9 @@ def run_ours(args) -> dict:
     def decode_run(batch, n_warm, n_timed):
         rids = [("d", batch, i) for i in range(batch)]
         for rid in rids:
-            eng.step([StepEntry(rid, toks(prompt_len), ())])
+            prompt = toks(prompt_len)
+            for lo in range(0, prompt_len, args.prefill_chunk or prompt_len):      # whole, or in portions
+                eng.step([StepEntry(rid, prompt[lo: lo + (args.prefill_chunk or prompt_len)], ())])
         kernels.LAUNCHES = 0
         ms = timed_steps(lambda i: [StepEntry(rid, [rng.randrange(V)], (0,)) for rid in rids], n_warm, n_timed, True)
         launches = kernels.LAUNCHES * n_timed // (n_warm + n_timed)
@@ -221,10 +225,14 @@ def run_ours(args) -> dict:
 
     # ---- end to end through the Python entry point ----
     n_new = args.warmup + args.steps + 1
-    llm.sched_opts["max_step_tokens"] = B * prompt_len       # all prompts in the first step, then pure decode steps
-    reqs = [Request(rid=("e", i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new)) for i in range(B)]
-    llm.run(reqs)
-    log = llm.step_log
+    chunk = args.prefill_chunk or prompt_len
+    llm.sched_opts["max_step_tokens"] = B * chunk            # all prompts advance together, then pure decode steps
+    llm.sched_opts["prefill_chunk"] = chunk
+    log = []
+    if args.e2e:
+        reqs = [Request(rid=("e", i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new)) for i in range(B)]
+        llm.run(reqs)
+        log = llm.step_log
     dec = [s for s in log if s["tokens"] == s["sampled"] == B][args.warmup:]
     e2e_val = None
     if len(dec) >= 2:
@@ -256,6 +264,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--prefill-chunk", type=int, default=0,
+                    help="feed the prompts of the decode runs in portions of this many tokens (0: whole)")
+    ap.add_argument("--no-e2e", dest="e2e", action="store_false", help="skip the run through the Python entry point")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
     args = ap.parse_args()
     if args.impl == "reference":

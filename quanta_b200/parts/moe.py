@@ -62,10 +62,11 @@ class SigmoidTopKExperts(FeedForward):
 
     # Which kernels run the expert products: "tc" (tcgen05 + TMA), "stream" (mma.sync, weights from
     # registers), "simt" (float32 CUDA cores).  "auto": float32 and odd sizes -> simt; bfloat16 -> stream
-    # for steps of at most ``stream_max_tokens`` tokens, tc above.  Set per part, or for the whole process with
+    # for steps of at most ``stream_max_tokens`` tokens, tc above (measured on a B200: tc is at least as
+    # fast from one token on, so the bound is 0).  Set per part, or for the whole process with
     # QUANTA_B200_EXPERT_KERNELS (a tuning knob, for measurements).
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
-    stream_max_tokens = 2
+    stream_max_tokens = 0
 
     def path_for(self, x) -> str:
         ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
