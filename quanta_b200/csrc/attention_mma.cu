@@ -334,7 +334,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           const int n_pi = last / page_size - pi0 + 1;
           for (int i = 0; i < n_pi; ++i) {
             const int pg = bt[pi0 + i];
-            if (pg < 0 || pg >= num_pages) {
+            // a page wholly before the window may have been given back already: it is not read
+            const bool needed = (pi0 + i + 1) * page_size > lo;
+            if (needed && (pg < 0 || pg >= num_pages)) {
               qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 6);
               valid = 0;
             }
@@ -362,18 +364,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         // boxes of the TMA path: rows of one page (or 64 rows of a larger page) x 64 dims
         const int box_rows = min(page_size, AT_BN), n_slabs = hd / 64;
         const int n_boxes = (n_keys + box_rows - 1) / box_rows;          // pages of the tile that hold visible keys
+        // keys before the window are not fetched (their rows keep older, finite values and are masked)
+        const int key_skip = b_lo > key0 ? b_lo - key0 : 0;
+        const int box_first = key_skip / box_rows;
         if (lane == 0) {
           desc[slot] = AdDesc{1, b_z, b_kvh, b_split, b_pos, b_lo};
-          const uint32_t kv_bytes = TMA ? (uint32_t)(2 * n_boxes * n_slabs * box_rows) * 128u
-                                        : (uint32_t)(2 * n_keys) * row_bytes;
+          const uint32_t kv_bytes = TMA ? (uint32_t)(2 * (n_boxes - box_first) * n_slabs * box_rows) * 128u
+                                        : (uint32_t)(2 * (n_keys - key_skip)) * row_bytes;
           mbar_expect_tx(bar, (uint32_t)G * row_bytes + kv_bytes);
         }
         __syncwarp();
         for (int r = lane; r < G; r += 32)
           bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)b_t * nq + b_kvh * G + r) * hd, row_bytes, bar);
         if (TMA) {
-          for (int i = lane; i < 2 * n_boxes * n_slabs; i += 32) {
-            const int which = i & 1, slab = (i >> 1) % n_slabs, box = (i >> 1) / n_slabs;
+          for (int i = lane; i < 2 * (n_boxes - box_first) * n_slabs; i += 32) {
+            const int which = i & 1, slab = (i >> 1) % n_slabs, box = box_first + (i >> 1) / n_slabs;
             const int key = key0 + box * box_rows;
             const int pg = s_pages[src][key / page_size - b_pi0];
             const int row = (pg * nkv + b_kvh) * page_size + key % page_size;       // row of the cache seen as 2-D
@@ -381,7 +386,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             tma_load_tile(dst, which ? &tm_v : &tm_k, slab * 64, row, bar);
           }
         } else {
-          for (int r = lane; r < n_keys; r += 32) {
+          for (int r = key_skip + lane; r < n_keys; r += 32) {
             const int key = key0 + r;
             const int pg = s_pages[src][key / page_size - b_pi0];
             const size_t off = (((size_t)pg * nkv + b_kvh) * page_size + key % page_size) * hd;
@@ -510,6 +515,7 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   const int p_first = tok_pos[first_tok];
   const int key_begin = (window > 0 && p_first - window + 1 > 0) ? (p_first - window + 1) / AT_BN * AT_BN : 0;
   const int n_blocks = (key_end - key_begin) / AT_BN + 1;
+  const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;   // the lowest key any row reads
 
   // Q rows (zero past head_dim and past the last row), the ring as zeros, the page ids of the keys read
   for (int c = tid; c < BM * (HDP / 8); c += blockDim.x) {
@@ -555,11 +561,13 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       const uint32_t bar = smem_u32(&full[slot]);
       __nv_bfloat16* ks = ring + (size_t)slot * 2 * tile_elems;
       __nv_bfloat16* vs = ks + tile_elems;
-      // a page id outside the pool is recorded and its rows are not copied (the byte count must match)
+      // a page id outside the pool is recorded and its rows are not copied (the byte count must match);
+      // keys before every row's window are not fetched: their pages may have been given back already
       int bad = 0;
       const int n_req = TMA ? 2 * n_boxes * n_slabs : n_keys;
       for (int i = lane; i < n_req; i += 32) {
         const int key = TMA ? key0 + ((i >> 1) / n_slabs) * box_rows : key0 + i;
+        if ((TMA ? key + box_rows - 1 : key) < lo_min) { ++bad; continue; }
         const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
         if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++bad; }
       }
@@ -573,6 +581,7 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         if (TMA) {
           const int which = i & 1, slab = (i >> 1) % n_slabs, box = (i >> 1) / n_slabs;
           const int key = key0 + box * box_rows;
+          if (key + box_rows - 1 < lo_min) continue;
           const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
           if (pg < 0 || pg >= num_pages) continue;
           const int row = (pg * nkv + kvh) * page_size + key % page_size;
@@ -580,6 +589,7 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           tma_load_tile(dst, which ? &tm_v : &tm_k, slab * 64, row, bar);
         } else {
           const int key = key0 + i;
+          if (key < lo_min) continue;
           const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
           if (pg < 0 || pg >= num_pages) continue;
           const size_t off = (((size_t)pg * nkv + kvh) * page_size + key % page_size) * hd;

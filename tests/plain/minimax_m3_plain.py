@@ -110,17 +110,21 @@ def partial_rope(x: torch.Tensor, pos: torch.Tensor, rd: int, theta: float) -> t
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin, x[..., rd:]], dim=-1)
 
 
-def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, act, compute) -> torch.Tensor:
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, act, compute, window=None) -> torch.Tensor:
     """Causal softmax attention of one whole sequence with grouped heads
     (src/quanta/minimax/attention.py:194-203, mask :105-110).  ``q`` ``[T,nq,hd]``, ``k``/``v``
     ``[T,nkv,hd]``; q head ``h`` reads kv head ``h // (nq/nkv)``; scale ``hd**-0.5``; the softmax is
-    taken in ``compute`` and the probabilities are rounded to ``act`` before ``P @ V``."""
+    taken in ``compute`` and the probabilities are rounded to ``act`` before ``P @ V``.
+    ``window`` (not in the reference, whose layers all read every key; used by the tests of cache groups):
+    a query at position p reads the keys p-window+1 .. p only."""
     T, nq, hd = q.shape
     rep = nq // k.shape[1]
     kr = k.repeat_interleave(rep, dim=1).transpose(0, 1)          # [nq,T,hd]
     vr = v.repeat_interleave(rep, dim=1).transpose(0, 1)
     s = (q.transpose(0, 1) @ kr.transpose(1, 2)) * (hd ** -0.5)   # [nq,T,T]
     mask = torch.ones(T, T, dtype=torch.bool).tril()
+    if window:
+        mask &= ~torch.ones(T, T, dtype=torch.bool).tril(-int(window))
     s = s.masked_fill(~mask, float("-inf"))
     p = _round(torch.softmax(s, dim=-1), act, compute)
     out = (p @ vr).transpose(0, 1).reshape(T, nq * hd)
@@ -173,7 +177,7 @@ def _w(weights: dict, name: str) -> torch.Tensor:
     return weights["language_model." + name]
 
 
-def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | None = None):
+def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | None = None, window=None):
     """``h + attn(norm(h))`` then ``h + moe(norm(h))`` (src/quanta/minimax/model.py:70-73)."""
     c = cfg
     wl = layer if weight_layer is None else weight_layer
@@ -189,7 +193,7 @@ def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | No
         k = qk_norm(k, W("self_attn.k_norm.weight"), c["nkv"], c["hd"], c["qk_norm_type"], c["eps"])
     q = _round(partial_rope(q, pos, c["rd"], c["theta"]), act, compute)
     k = _round(partial_rope(k, pos, c["rd"], c["theta"]), act, compute)
-    a = causal_attention(q, k, v, act, compute)
+    a = causal_attention(q, k, v, act, compute, window)
     h = h + linear(a, W("self_attn.o_proj.weight"), act, compute)
     x2 = _round(rms_norm(h, W("post_attention_layernorm.weight"), c["eps"]), act, compute)
     m = p + "block_sparse_moe."
@@ -202,16 +206,17 @@ def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | No
 
 
 def forward_logits(weights: dict, cfg: dict, ids, *, act=None, compute=torch.float32,
-                   schedule=None) -> torch.Tensor:
+                   schedule=None, windows=None) -> torch.Tensor:
     """Logits ``[T, V]`` of one whole sequence: embed -> blocks -> final norm -> head
     (src/quanta/minimax/model.py:86-96; head in float32, src/quanta/minimax/runtime.py:95-98).
-    ``schedule`` lists the layers in the order they run (a layer may appear twice)."""
+    ``schedule`` lists the layers in the order they run (a layer may appear twice); ``windows`` maps a
+    place in that order to the window of its attention (absent: every key)."""
     ids = torch.as_tensor(ids, dtype=torch.long)
     h = embedding(ids, _w(weights, "model.embed_tokens.weight"), compute)
     pos = torch.arange(ids.shape[0])
     order = list(range(cfg["L"])) if schedule is None else list(schedule)
     for i, wl in enumerate(order):
-        h = block(h, pos, weights, cfg, i, act, compute, weight_layer=wl)
+        h = block(h, pos, weights, cfg, i, act, compute, weight_layer=wl, window=(windows or {}).get(i))
     hf = _round(rms_norm(h, _w(weights, "model.norm.weight").to(compute), cfg["eps"]), act, compute)
     head = _w(weights, "model.embed_tokens.weight" if cfg["tied"] else "lm_head.weight")
     return hf @ head.to(compute).T

@@ -149,7 +149,7 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 3, 48, 4, 0), (4, 4, 16, 16, 0), (12, 2, 128, 8, 0),
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
-                                                   (48, 8, 128, 16, 0)])
+                                                   (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37)])
 @pytest.mark.parametrize("impl", ["simt", "mma"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
     k = K()
@@ -213,6 +213,14 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
         kc[pg2, :, sl2, 0] = 60.0
         run()
         assert torch.allclose(out[T - 1].float().cpu(), want[T - 1], **tol(dtype))
+        # pages that lie wholly before the window of a request's first token have been given back: the
+        # table holds -1 there, and the kernels must neither read them nor report them
+        for r, (a, n) in enumerate(spans):
+            table[r, : max(0, a - window + 1) // page] = -1
+        assert int((table < 0).sum()) > 0
+        run()
+        assert int(st[0]) == 0
+        assert torch.allclose(out.float().cpu(), want, **tol(dtype))
 
 
 @pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])

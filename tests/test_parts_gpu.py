@@ -155,6 +155,49 @@ def test_a_layer_reads_another_layers_cache(model_dirs):
         _spec_with_schedule("A", [ScheduleEntry(0, read_cache_of=1), ScheduleEntry(1)])
 
 
+@pytest.mark.parametrize("name,dtype,windows,page_size", [("A", "float32", {1: 9}, 4), ("B", "float32", {0: 21, 2: 6}, 8),
+                                                          ("B", "bfloat16", {0: 21, 2: 6}, 8)])
+def test_windowed_layers_have_pages_of_their_own(model_dirs, plain_models, name, dtype, windows, page_size):
+    """Some layers read a window of keys only: they form cache groups of their own, whose pages go back
+    to the pool as the window passes them, while the other layers keep every key."""
+    from quanta_b200.config import MiniMaxM3Config, resolve
+    from quanta_b200.engine.model import Model
+    from quanta_b200.engine.step import Engine
+    from quanta_b200.weights import FolderSource
+    raw = TINY[name]
+    spec = resolve(raw).build_spec(MiniMaxM3Config.from_dict(raw))
+    for layer, w in windows.items():
+        spec.layers[layer][1]["mixer"][1]["window"] = w
+    model = Model(spec, dtype=dtype).load(FolderSource(model_dirs[name]))
+    vocab = raw["vocab_size"]
+    reqs = {"a": H.random_tokens(90, vocab, 11), "b": H.random_tokens(57, vocab, 12), "c": H.random_tokens(75, vocab, 13)}
+    act = None if dtype == "float32" else torch.bfloat16
+    want = H.plain_logits(plain_models[name], reqs, act=act, windows=windows)
+    if dtype == "float32":
+        tol = 2e-5
+    else:
+        exact = H.plain_logits(plain_models[name], reqs, windows=windows)
+        tol = 2.0 * max(float((want[k] - exact[k]).abs().max()) for k in want)
+    # the windows matter: without them the logits differ
+    full = H.plain_logits(plain_models[name], {"a": reqs["a"]})
+    assert float((full[("a", 89)] - want[("a", 89)]).abs().max()) > 100 * tol or dtype != "float32"
+    cuts = {"whole": H.cut_whole(reqs), "tail": H.cut_tail_decode(reqs, 32), "portions": H.cut_portions(reqs),
+            "mixed": H.cut_mixed(reqs, 3, seed=5)}
+    for what, cut in cuts.items():
+        eng = Engine(model, num_pages=H.tokens_in_flight(cut, page_size) // page_size, page_size=page_size, max_requests=4)
+        groups = eng.manager.stats()["groups"]
+        assert sorted(str(g["window"]) for g in groups) == sorted(["None"] + [str(w) for w in set(windows.values())])
+        got = H.replay(eng, cut)
+        eng.manager.check_invariants()
+        bad = H.first_wrong(got, want, tol)
+        assert bad is None, (what, bad, H.worst_error(got, want), tol)
+        groups = eng.manager.stats()["groups"]
+        everything = max(g["high_water"] for g in groups if g["window"] is None)
+        for g in groups:
+            if g["window"] is not None and what != "whole":
+                assert g["high_water"] < everything, "the windowed group gave no page back while it ran"
+
+
 # ---- toy parts, defined here, registered, built and stepped --------------------------------------------
 def _register_toys():
     from quanta_b200.parts.base import FeedForward, Mixer, PositionEncoding, TensorSpec, register
