@@ -9,16 +9,18 @@
 //    from the cache that earlier steps and this step's rope kernel wrote.  A producer warp streams
 //    K/V blocks of 64 keys through a ring in shared memory (TMA, one box per page); consumer warps
 //    own 16 rows each.
-//  * decode kernel: persistent blocks, a producer warp that issues bulk asynchronous copies of 64-key
-//    tiles into a ring in shared memory and four consumer warps; the partial (max, sum, O) of each
-//    tile goes to scratch and a merge kernel adds a token's tiles in index order.  Tile boundaries are
-//    multiples of 64 in absolute position, so a token's result does not depend on the batch.
+//  * decode kernel: the 64-key tiles of all single tokens form one list that persistent blocks cut
+//    into equal ranges; in a block a producer warp streams the tiles through a ring in shared memory
+//    (TMA, one box per page) and four consumer warps share each tile, keeping their running softmax
+//    state in registers along a (token, kv head) pair; pairs that a range boundary cuts leave partial
+//    results that a small merge kernel adds.
 //
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
 // probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
 // head_dim: any multiple of 16 up to 256 (template padding 64 / 128 / 256, dims past head_dim are zero).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -90,60 +92,114 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* dst, const __nv_bfl
   }
 }
 
-// One warp: 16 query rows against AT_BN keys held in shared memory.
-//   qs: the warp's 16 rows [16][HDP+PAD]; ks, vs: [AT_BN][HDP+PAD]
+// One warp: 16 query rows against NK keys (rows koff .. koff+NK-1 of a tile) held in shared memory.
+//   qs: the warp's 16 rows [16][HDP+PAD]; ks, vs: a tile of AT_BN keys
 //   row_hi[2], row_lo[2]: last / first visible key of the thread's two rows (g and g+8), absolute
-//   key0: absolute position of ks row 0.   m, l, o: running max (log2 domain), partial sum, output.
+//   key0: absolute position of tile row koff.   m, l, o: running max (log2 domain), partial sum, output.
 // How a K or V tile of 64 keys lies in shared memory.
 //  PaddedKV:   rows of HDP + 8 elements (what cp.async / per-row bulk copies write).
-//  SwizzledKV: what TMA tensor loads with the 128-byte swizzle write: head_dim in slabs of 64 dims, each
+//  SwizzledKV: what 2-D TMA tensor loads with the 128-byte swizzle write: head_dim in slabs of 64 dims, each
 //              slab [64 keys][64 dims] with rows of 128 bytes whose 16-byte chunks are XORed with (row & 7);
-//              the tile is 1024-byte aligned.  Both are free of bank conflicts for ldmatrix.
+//              the tile is 1024-byte aligned.  Free of bank conflicts for ldmatrix, like PaddedKV.
+//  BoxedKV:    what 3-D TMA tensor loads write when ONE box is a whole page of a kv head (all slabs), so that
+//              a tile needs few requests.  A tile is its boxes one after the other.  Inside a box either the
+//              slabs follow one another, each [box rows][64 dims] (slab-major: conflict-free from 8 rows a
+//              box on), or a key's slabs lie side by side (interleaved: two-way conflicts for ldmatrix when
+//              the number of slabs is even).  Lines of 128 bytes, chunks XORed with (line & 7).
 template <int HDP>
 struct PaddedKV {
-  static __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) {
+  __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) const {
     return base + (size_t)row * (HDP + AT_PAD) + dim;
   }
 };
 struct SwizzledKV {
-  static __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) {
+  __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) const {
     const int chunk = (dim & 63) >> 3;
     return base + (dim >> 6) * (AT_BN * 64) + row * 64 + ((chunk ^ (row & 7)) << 3) + (dim & 7);
   }
 };
+template <int NS>
+struct BoxedKV {
+  int box_shift;       // log2 of the rows of a box
+  int slab_major;
+  __device__ __forceinline__ const __nv_bfloat16* at(const __nv_bfloat16* base, int row, int dim) const {
+    const int slab = dim >> 6;
+    const int line = slab_major ? ((((row >> box_shift) * NS + slab) << box_shift) + (row & ((1 << box_shift) - 1)))
+                                : row * NS + slab;
+    return base + line * 64 + ((((dim & 63) >> 3) ^ (line & 7)) << 3) + (dim & 7);
+  }
+};
 
-template <int HDP, typename KV = PaddedKV<HDP>>
+// QREG: the Q rows are already MMA fragments in registers (qf[k step][4]) and qs is not read.
+template <int HDP, typename KV = PaddedKV<HDP>, int NK = AT_BN, bool QREG = false>
 __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv_bfloat16* ks, const __nv_bfloat16* vs,
                                              int key0, const int (&row_lo)[2], const int (&row_hi)[2],
-                                             float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HDP / 8][4]) {
+                                             float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HDP / 8][4],
+                                             int koff = 0, const uint32_t (*qf)[4] = nullptr, const KV kv = KV()) {
   constexpr int LD = HDP + AT_PAD;
   const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  float s[AT_BN / 8][4];
+  float s[NK / 8][4];
 #pragma unroll
-  for (int i = 0; i < AT_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  for (int i = 0; i < NK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  if (NK == 16) {
+    // two keys' worth of accumulators only: sum the even and the odd 16-dim steps apart, so that two
+    // chains of dependent MMAs run at a time instead of one
+    float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-  for (int kk = 0; kk < HDP / 16; ++kk) {
-    uint32_t a[4];
-    ldmatrix_x4(a, qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+    for (int kk = 0; kk < HDP / 16; ++kk) {
+      uint32_t a[4], b[4];
+      if (QREG) { a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3]; }
+      else ldmatrix_x4(a, qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+      ldmatrix_x4(b, kv.at(ks, koff + (lane & 7) + 8 * (lane >> 4), kk * 16 + 8 * ((lane >> 3) & 1)));
+      if (kk & 1) {
+        mma16816(s2[0], a, b[0], b[1]);
+        mma16816(s2[1], a, b[2], b[3]);
+      } else {
+        mma16816(s[0], a, b[0], b[1]);
+        mma16816(s[1], a, b[2], b[3]);
+      }
+    }
 #pragma unroll
-    for (int nt = 0; nt < AT_BN / 16; ++nt) {
-      uint32_t b[4];
-      ldmatrix_x4(b, KV::at(ks, nt * 16 + (lane & 7) + 8 * (lane >> 4), kk * 16 + 8 * ((lane >> 3) & 1)));
-      mma16816(s[2 * nt], a, b[0], b[1]);
-      mma16816(s[2 * nt + 1], a, b[2], b[3]);
+    for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
+  } else {
+#pragma unroll
+    for (int kk = 0; kk < HDP / 16; ++kk) {
+      uint32_t a[4];
+      if (QREG) { a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3]; }
+      else ldmatrix_x4(a, qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+      for (int nt = 0; nt < NK / 16; ++nt) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kv.at(ks, koff + nt * 16 + (lane & 7) + 8 * (lane >> 4), kk * 16 + 8 * ((lane >> 3) & 1)));
+        mma16816(s[2 * nt], a, b[0], b[1]);
+        mma16816(s[2 * nt + 1], a, b[2], b[3]);
+      }
     }
   }
   // scale, mask, running max
   float mx[2] = {-INFINITY, -INFINITY};
+  // far from the ends of a request every key of the block is visible to every row: no compares then
+  const bool all_visible = __all_sync(0xffffffffu, key0 >= max(row_lo[0], row_lo[1]) &&
+                                                   key0 + NK - 1 <= min(row_hi[0], row_hi[1]));
+  if (all_visible) {
 #pragma unroll
-  for (int i = 0; i < AT_BN / 8; ++i)
+    for (int i = 0; i < NK / 8; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int key = key0 + i * 8 + q * 2 + (e & 1), r = e >> 1;
-      const float v = (key >= row_lo[r] && key <= row_hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
-      s[i][e] = v;
-      mx[r] = fmaxf(mx[r], v);
-    }
+      for (int e = 0; e < 4; ++e) {
+        s[i][e] *= scale_log2;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
+      }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NK / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + i * 8 + q * 2 + (e & 1), r = e >> 1;
+        const float v = (key >= row_lo[r] && key <= row_hi[r]) ? s[i][e] * scale_log2 : -INFINITY;
+        s[i][e] = v;
+        mx[r] = fmaxf(mx[r], v);
+      }
+  }
   float corr[2], msafe[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -155,12 +211,15 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
     m[r] = mn;
     l[r] *= corr[r];
   }
+  // most blocks leave the running maximum where it was: nothing to rescale then
+  if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-  for (int i = 0; i < HDP / 8; ++i) {
-    o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    for (int i = 0; i < HDP / 8; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
   }
 #pragma unroll
-  for (int i = 0; i < AT_BN / 8; ++i)
+  for (int i = 0; i < NK / 8; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float p = exp2f(s[i][e] - msafe[e >> 1]);
@@ -169,7 +228,7 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
     }
   // O += P V
 #pragma unroll
-  for (int j = 0; j < AT_BN / 16; ++j) {
+  for (int j = 0; j < NK / 16; ++j) {
     uint32_t a[4];
     a[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
     a[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
@@ -178,7 +237,7 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 #pragma unroll
     for (int dt = 0; dt < HDP / 16; ++dt) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, KV::at(vs, j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt * 16 + 8 * (lane >> 4)));
+      ldmatrix_x4_trans(b, kv.at(vs, koff + j * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dt * 16 + 8 * (lane >> 4)));
       mma16816(o[2 * dt], a, b[0], b[1]);
       mma16816(o[2 * dt + 1], a, b[2], b[3]);
     }
@@ -188,17 +247,26 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 // ------------------------------------------------------------------------------------------------
 // decode kernel: single query tokens against the cache, bound by reading K and V once.
 //
-// Persistent blocks (one per SM) of one PRODUCER warp and four CONSUMER warps around a ring of tiles
-// in shared memory.  A tile is 64 keys of one (token, kv head): its K rows, V rows and the group's Q
-// rows.  The producer resolves a batch of 32 candidate tiles at a time (token -> position -> page
-// ids, all lanes in parallel, so the dependent loads are paid once per batch), then issues one bulk
-// asynchronous copy per row (cp.async.bulk, completion counted on the tile's mbarrier).  Each
-// consumer warp takes every fourth tile: S = Q K^T, softmax, P V on the tensor cores as in the span
-// kernel, and leaves the tile's (max, sum, O) in the scratch; a merge kernel adds a token's tiles in
-// index order.  Tile boundaries are multiples of 64 in absolute position, so a token's result does
-// not depend on the batch.  The ring keeps several tiles in flight per SM whatever a single warp waits
-// for.  Every wait is bounded.
-// scratch: part_o float [n_dec][nq][n_splits_max][hd], part_ml float [n_dec][nq][n_splits_max][2]
+// The work is the list of all 64-key tiles of all (token, kv head) pairs, token-major.  Persistent
+// blocks (one per SM) cut that list into equal contiguous ranges (a block's range may begin and end
+// inside a pair), so every SM reads the same number of bytes whatever the mix of context lengths.
+// A block is one PRODUCER warp and four CONSUMER warps around a ring of tiles in shared memory.  A tile
+// is 64 keys of one pair: its K rows, V rows and the group's Q rows.  The producer resolves 32 tiles at
+// a time (pair by binary search in a prefix sum of the tokens' tile counts held in shared memory, then
+// the page ids, all lanes in parallel) and issues TMA tensor loads (one box per page) or, where the
+// shapes do not allow them, one bulk copy per row; completion is counted on the tile's mbarrier.
+// The four consumers work on the SAME tile: with up to 16 q heads per kv head each takes 16 of its 64
+// keys (17..32 heads: two row blocks x two key halves; 33..64: a row block each), so a tile is consumed
+// in a fraction of the time it takes to arrive, and they keep their running (max, sum, O) in registers
+// over the consecutive tiles of a pair.  Where the block's range leaves a pair the consumers merge
+// their parts through the tile's shared memory and write ONE partial result for the segment, or the
+// final output if the segment is the whole pair; a small merge kernel adds the segments of the pairs that
+// were cut.  At most (pairs + blocks) partials are written whatever the context length.  A token's result
+// depends on the batch only through the order of these float32 additions.  Every wait is bounded.
+//
+// scratch: part_o float [n_dec][nq][n_parts][hd], part_ml float [n_dec][nq][n_parts][2]; the last of
+// the n_parts entries of a row holds, as an integer, how many segments the merge kernel has to add
+// (0: the output is already final).
 // ------------------------------------------------------------------------------------------------
 constexpr int AD_CONSUMERS = 4;
 constexpr int AD_THREADS = (AD_CONSUMERS + 1) * 32;
@@ -229,14 +297,20 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false when another warp gave up or the limit (iterations and 0.2 s) is reached.
+// Bounded wait: false when another warp gave up or the limit (iterations and 0.2 s) is reached.  The
+// clock and the abort flag are read only now and then: a read of the global timer costs more than
+// most waits last.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
+  uint64_t t0 = 0;
   for (uint32_t it = 0; it < AD_SPIN_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if ((it & 63u) == 63u && global_ns() - t0 > AD_WAIT_NS) break;
+    if ((it & 127u) == 127u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > AD_WAIT_NS) break;
+    }
   }
   *abort_flag = 1;
   return false;
@@ -253,160 +327,260 @@ __device__ __forceinline__ void tma_load_tile(void* dst, const CUtensorMap* map,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(dim0), "r"(row), "r"(bar) : "memory");
 }
+// one box of whole rows (all slabs of 64 dims) of a cache seen as a 3-D tensor whose middle and outer
+// dimensions are (rows, slabs) when slab-major, (slabs, rows) when interleaved; no multicast
+__device__ __forceinline__ void tma_load_rows(void* dst, const CUtensorMap* map, int row, int slab_major, uint32_t bar) {
+  const int c1 = slab_major ? row : 0, c2 = slab_major ? 0 : row;
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+template <int H> __device__ __forceinline__ PaddedKV<H> make_kv(PaddedKV<H>*, int, int) { return PaddedKV<H>(); }
+template <int NS> __device__ __forceinline__ BoxedKV<NS> make_kv(BoxedKV<NS>*, int box_shift, int slab_major) {
+  return BoxedKV<NS>{box_shift, slab_major};
+}
 
-struct AdDesc { int valid, z, kvh, split, pos, lo; };
+constexpr int AD_MAX_DEC = 256;      // tokens per launch: their positions and tile counts live in shared memory
+constexpr int AD_FIRST = 1, AD_LAST = 2, AD_WHOLE = 4, AD_PAIR_END = 8;
 
-// Elements of one ring stage: the Q rows (padded rows), then the K tile and the V tile.  With TMA the
-// tiles are swizzled slabs and every part starts on a 1024-byte boundary.
+// One tile of the block's range.  valid: 1 a tile, 2 a tile that is passed over (a page id outside the
+// pool; the status word says so).  flags: the first / last tile of a segment (the part of a pair inside
+// this block's range), whether that segment is the whole pair, whether the tile ends its pair.
+// qslot: where in the ring of Q rows the pair's queries lie.  48 bytes, read as three 16-byte words.
+struct __align__(16) AdDesc { int valid, z, tok, kvh, key0, pos, lo, flags, seg, pi0, qslot, pad; };
+
+// Elements of the Q rows of one tile (span kernel: of the block), and of a K or V tile.  With TMA the
+// tiles are swizzled slabs and start on 1024-byte boundaries.
 __host__ __device__ constexpr size_t ad_q_elems(int hdp, int q_rows, bool tma) {
   return tma ? ((size_t)q_rows * (hdp + AT_PAD) + 511) / 512 * 512 : (size_t)q_rows * (hdp + AT_PAD);
 }
 __host__ __device__ constexpr size_t ad_tile_elems(int hdp, bool tma) {
   return tma ? (size_t)(hdp / 64) * AT_BN * 64 : (size_t)AT_BN * (hdp + AT_PAD);
 }
+// Q rows kept per pair: a multiple of 8 up to 16 heads (the MMA reads 16 rows; the rows past them
+// belong to the next entry of the ring, or to 8 rows of zeros after the last, and are masked), else
+// whole row blocks of 16.
+__host__ __device__ constexpr int ad_q_rows(int group) { return group <= 16 ? (group + 7) / 8 * 8 : (group + 15) / 16 * 16; }
 
-// TMA: K and V tiles come as tensor loads of [rows of one page x 64 dims] boxes with the 128-byte swizzle
-// (a page's keys of one kv head are contiguous rows of the cache seen as [pages*kv_heads*page_size, hd]):
-// 16 requests per tile instead of 128 row copies.  Needs hd % 64 == 0 and a power-of-two page size.
+__device__ __forceinline__ int ad_tiles_of(int pos, int window) {
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  return pos / AT_BN - lo / AT_BN + 1;
+}
+
+// TMA: K and V tiles come as tensor loads of one box per page, [rows of the page][head_dim], with the
+// 128-byte swizzle (a page's keys of one kv head are contiguous rows of the cache seen as
+// [pages*kv_heads*page_size][hd / 64][64]): 8 requests per tile with pages of 16 keys, 2 with pages of 64,
+// instead of 128 row copies.  An instruction that starts a tensor load holds the issuing warp for some
+// tens of cycles, so their number per tile decides how fast a producer can go.  Needs a head size of 64,
+// 128 or 256 and a power-of-two page size.
 template <int HDP, bool TMA>
 __global__ void __launch_bounds__(AD_THREADS, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                   const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   const int* __restrict__ dec_tok, int n_dec, const int* __restrict__ tok_pos,
-                   const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int nq, int nkv,
-                   int hd, int page_size, int num_pages, float scale_log2, int window, int n_splits_max, int stages,
-                   int q_rows, int* status) {
+                   const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ dec_tok, int n_dec,
+                   const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
+                   const int* __restrict__ block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
+                   int num_pages, float scale_log2, int window, int n_parts, int stages, int pages_ld,
+                   int slab_major, int* status) {
   constexpr int LD = HDP + AT_PAD;
-  using KV = typename std::conditional<TMA, SwizzledKV, PaddedKV<HDP>>::type;
+  using KV = typename std::conditional<TMA, BoxedKV<HDP / 64>, PaddedKV<HDP>>::type;
   extern __shared__ __align__(16) unsigned char smem_dyn[];
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [stages][Q | K tile | V tile]
-  const size_t q_elems = ad_q_elems(HDP, q_rows, TMA), tile_elems = ad_tile_elems(HDP, TMA);
-  const size_t stage_elems = q_elems + 2 * tile_elems;
-  __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES];
-  __shared__ AdDesc desc[AD_MAX_STAGES];
-  __shared__ int s_pages[32][AT_BN + 1];        // page ids of the producer's batch, one row per lane
+  const int G = nq / nkv, q_rows = ad_q_rows(G), q_slots = stages + 1;
+  const size_t tile_elems = ad_tile_elems(HDP, TMA);
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [stages][K tile | V tile]
+  __nv_bfloat16* qring = ring + (size_t)stages * 2 * tile_elems;             // [q_slots][q_rows][LD], then 8 zero rows
+  int* s_pos = reinterpret_cast<int*>(qring + ((size_t)q_slots * q_rows + 8) * LD);   // [AD_MAX_DEC] position of token z
+  int* s_req = s_pos + AD_MAX_DEC;                                           // its block-table row
+  int* s_tok = s_req + AD_MAX_DEC;                                           // its row among the step's tokens
+  int* s_cum = s_tok + AD_MAX_DEC;                                           // [AD_MAX_DEC + 1] tiles of the tokens before z
+  int* s_pages = s_cum + AD_MAX_DEC + 1;                                     // [32][pages_ld] page ids of a batch
+  __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES], cbar;
+  __shared__ AdDesc s_desc[2][32];            // the tiles of a batch of 32, double-buffered
+  __shared__ float s_ml[AD_CONSUMERS][16][2];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = nq / nkv;
 
-  // The ring starts as zeros: padding columns and Q rows past the group are never copied into, and a
-  // tile's unused key rows only ever hold older (finite) keys.
-  for (size_t i = tid; i < stage_elems * stages / 8; i += blockDim.x) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+  for (int z = tid; z < n_dec; z += blockDim.x) {
+    const int t = dec_tok[z];
+    s_tok[z] = t;
+    s_pos[z] = tok_pos[t];
+    s_req[z] = tok_req[t];
+  }
+  // The rings start as zeros: padding columns and Q rows past the group are never copied into, and a
+  // tile's unused key rows only ever hold older (finite) keys or zeros.
+  {
+    const size_t n16 = ((size_t)stages * 2 * tile_elems + ((size_t)q_slots * q_rows + 8) * LD) / 8;
+    for (size_t i = tid; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(ring)[i] = make_uint4(0, 0, 0, 0);
+  }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&full[s]), 1);
-      mbar_init(smem_u32(&empty[s]), 1);
+      mbar_init(smem_u32(&empty[s]), AD_CONSUMERS);
     }
+    mbar_init(smem_u32(&cbar), AD_CONSUMERS);
     abort_word = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive prefix sum of the tokens' tile counts
+    const int per = (n_dec + 31) / 32, z0 = lane * per, z1 = min(n_dec, z0 + per);
+    int sum = 0;
+    for (int z = z0; z < z1; ++z) sum += ad_tiles_of(s_pos[z], window);
+    int incl = sum;
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    int run = incl - sum;
+    for (int z = z0; z < z1; ++z) {
+      s_cum[z] = run;
+      run += ad_tiles_of(s_pos[z], window);
+    }
+    if (lane == 31) s_cum[n_dec] = incl;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeros above before any bulk copy lands
   __syncthreads();
 
+  // this block's range of the tile list
+  const long T = (long)nkv * s_cum[n_dec];
+  const long A = T < (long)gridDim.x ? T : (long)gridDim.x;
+  const long b = blockIdx.x;
+  const long start = b < A ? b * T / A : 0, end = b < A ? (b + 1) * T / A : 0;
+  const int n_tiles = (int)(end - start);
+
   const uint32_t row_bytes = (uint32_t)hd * 2u;
   if (warp == AD_CONSUMERS) {
     // ---------------- producer ----------------
-    const long pairs = (long)n_dec * nkv, total = pairs * n_splits_max;
-    long seq = 0;
     bool ok = true;
-    // Candidate tiles are numbered split-major and dealt to the blocks round robin, so every block gets
-    // the same mix of early and late tiles; a lane resolves one candidate, 32 at a time.
-    for (long round = 0; blockIdx.x + round * 32 * (long)gridDim.x < total && ok; ++round) {
-      const long item = blockIdx.x + (round * 32 + lane) * (long)gridDim.x;
-      int valid = item < total, z = 0, kvh = 0, split = 0, pos = 0, lo = 0, t = 0, pi0 = 0;
-      if (valid) {
-        split = (int)(item / pairs);
-        const int rem = (int)(item % pairs);
-        z = rem / nkv;
-        kvh = rem % nkv;
-        t = dec_tok[z];
-        pos = tok_pos[t];
-        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        const int key0 = split * AT_BN;
-        valid = key0 <= pos && key0 + AT_BN > lo;
-        if (valid) {
-          const int* bt = block_table + (size_t)tok_req[t] * bt_stride;
-          const int last = min(pos, key0 + AT_BN - 1);
-          pi0 = key0 / page_size;
-          const int n_pi = last / page_size - pi0 + 1;
-          for (int i = 0; i < n_pi; ++i) {
-            const int pg = bt[pi0 + i];
-            // a page wholly before the window may have been given back already: it is not read
-            const bool needed = (pi0 + i + 1) * page_size > lo;
-            if (needed && (pg < 0 || pg >= num_pages)) {
-              qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 6);
-              valid = 0;
-            }
-            s_pages[lane][i] = pg;
-          }
+    int slot = 0, q_count = 0;
+    uint32_t phase = 0;
+    const int box_rows = min(page_size, AT_BN);
+    const int page_shift = 31 - __clz(page_size), box_shift = 31 - __clz(box_rows);     // TMA path: powers of two
+    // page ids of a tile fit four registers when pages are powers of two of at least 16 keys: then the
+    // next batch's ids are fetched while this batch is being issued
+    const bool few_pages = (page_size & (page_size - 1)) == 0 && page_size >= 16;
+    AdDesc nd;                       // this lane's tile of the batch being resolved
+    int npg[4] = {0, 0, 0, 0};
+    auto resolve = [&](int first_tile) {
+      const int n = first_tile + lane;
+      nd = AdDesc{0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      if (n < n_tiles) {
+        const long gt = start + n;
+        int a = 0, c = n_dec;                   // nkv * s_cum[a] <= gt < nkv * s_cum[c]
+        while (c - a > 1) {
+          const int mid = (a + c) >> 1;
+          if ((long)nkv * s_cum[mid] <= gt) a = mid; else c = mid;
+        }
+        nd.valid = 1;
+        nd.z = a;
+        nd.tok = s_tok[a];
+        nd.pos = s_pos[a];
+        nd.lo = (window > 0 && nd.pos - window + 1 > 0) ? nd.pos - window + 1 : 0;
+        const int cnt = s_cum[a + 1] - s_cum[a];
+        const long base = (long)nkv * s_cum[a];
+        const int rem = (int)(gt - base);
+        nd.kvh = rem / cnt;
+        const int i = rem - nd.kvh * cnt;
+        nd.key0 = (nd.lo / AT_BN + i) * AT_BN;
+        const long g0 = base + (long)nd.kvh * cnt, g1 = g0 + cnt - 1;      // the pair's first and last tile
+        nd.flags = ((n == 0 || i == 0) ? AD_FIRST : 0) | ((n == n_tiles - 1 || i == cnt - 1) ? AD_LAST : 0) |
+                   ((g0 >= start && g1 < end) ? AD_WHOLE : 0) | (i == cnt - 1 ? AD_PAIR_END : 0);
+        nd.seg = (int)(b - ((g0 + 1) * A - 1) / T);      // blocks since the one that holds the pair's first tile
+        nd.pi0 = nd.key0 / page_size;
+        if (few_pages) {
+          const int* bt = block_table + (size_t)s_req[a] * bt_stride + nd.pi0;
+          const int last = min(nd.pos, nd.key0 + AT_BN - 1);
+          const int n_pi = last / page_size - nd.pi0 + 1;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) npg[j] = j < n_pi ? bt[j] : 0;
         }
       }
-      __syncwarp();
-      for (int src = 0; src < 32 && ok; ++src) {
-        if (!__shfl_sync(0xffffffffu, valid, src)) continue;
-        const int b_z = __shfl_sync(0xffffffffu, z, src), b_kvh = __shfl_sync(0xffffffffu, kvh, src);
-        const int b_split = __shfl_sync(0xffffffffu, split, src), b_pos = __shfl_sync(0xffffffffu, pos, src);
-        const int b_lo = __shfl_sync(0xffffffffu, lo, src), b_t = __shfl_sync(0xffffffffu, t, src);
-        const int b_pi0 = __shfl_sync(0xffffffffu, pi0, src);
-        const int slot = (int)(seq % stages);
-        const uint32_t ph = (uint32_t)(seq / stages) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);   // one answer per warp
-        if (!ok) break;
-        const int key0 = b_split * AT_BN;
-        const int n_keys = min(AT_BN, b_pos - key0 + 1);
-        const uint32_t bar = smem_u32(&full[slot]);
-        __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
-        __nv_bfloat16* ks = qs + q_elems;
-        __nv_bfloat16* vs = ks + tile_elems;
-        // boxes of the TMA path: rows of one page (or 64 rows of a larger page) x 64 dims
-        const int box_rows = min(page_size, AT_BN), n_slabs = hd / 64;
-        const int n_boxes = (n_keys + box_rows - 1) / box_rows;          // pages of the tile that hold visible keys
-        // keys before the window are not fetched (their rows keep older, finite values and are masked)
-        const int key_skip = b_lo > key0 ? b_lo - key0 : 0;
-        const int box_first = key_skip / box_rows;
-        if (lane == 0) {
-          desc[slot] = AdDesc{1, b_z, b_kvh, b_split, b_pos, b_lo};
-          const uint32_t kv_bytes = TMA ? (uint32_t)(2 * (n_boxes - box_first) * n_slabs * box_rows) * 128u
-                                        : (uint32_t)(2 * (n_keys - key_skip)) * row_bytes;
-          mbar_expect_tx(bar, (uint32_t)G * row_bytes + kv_bytes);
-        }
-        __syncwarp();
-        for (int r = lane; r < G; r += 32)
-          bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)b_t * nq + b_kvh * G + r) * hd, row_bytes, bar);
-        if (TMA) {
-          for (int i = lane; i < 2 * (n_boxes - box_first) * n_slabs; i += 32) {
-            const int which = i & 1, slab = (i >> 1) % n_slabs, box = box_first + (i >> 1) / n_slabs;
-            const int key = key0 + box * box_rows;
-            const int pg = s_pages[src][key / page_size - b_pi0];
-            const int row = (pg * nkv + b_kvh) * page_size + key % page_size;       // row of the cache seen as 2-D
-            __nv_bfloat16* dst = (which ? vs : ks) + (size_t)slab * (AT_BN * 64) + (size_t)box * box_rows * 64;
-            tma_load_tile(dst, which ? &tm_v : &tm_k, slab * 64, row, bar);
+    };
+    resolve(0);
+    for (int first_tile = 0; first_tile < n_tiles && ok; first_tile += 32) {
+      const int buf = (first_tile >> 5) & 1;
+      // ---- finish resolving this batch: page ids checked and laid down, Q slots numbered ----
+      if (nd.valid) {
+        const int last = min(nd.pos, nd.key0 + AT_BN - 1);
+        const int n_pi = last / page_size - nd.pi0 + 1;
+        const int* bt = block_table + (size_t)s_req[nd.z] * bt_stride + nd.pi0;
+        auto lay_down = [&](int j, int pg) {
+          // a page wholly before the window may have been given back already: it is not read
+          const bool needed = (nd.pi0 + j + 1) * page_size > nd.lo;
+          if (needed && (pg < 0 || pg >= num_pages)) {
+            qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 6);
+            nd.valid = 2;
           }
+          s_pages[lane * pages_ld + j] = pg;
+        };
+        if (few_pages) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j < n_pi) lay_down(j, npg[j]);
         } else {
-          for (int r = key_skip + lane; r < n_keys; r += 32) {
-            const int key = key0 + r;
-            const int pg = s_pages[src][key / page_size - b_pi0];
-            const size_t off = (((size_t)pg * nkv + b_kvh) * page_size + key % page_size) * hd;
-            bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
-            bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+          for (int j = 0; j < n_pi; ++j) lay_down(j, bt[j]);
+        }
+      }
+      const uint32_t firsts = __ballot_sync(0xffffffffu, nd.valid && (nd.flags & AD_FIRST));
+      nd.qslot = (q_count + __popc(firsts & (0xffffffffu >> (31 - lane))) + q_slots - 1) % q_slots;
+      q_count = (q_count + __popc(firsts)) % q_slots;
+      s_desc[buf][lane] = nd;
+      __syncwarp();
+      const int in_batch = min(32, n_tiles - first_tile);
+      if (first_tile + 32 < n_tiles) resolve(first_tile + 32);     // its loads are in flight while this batch is issued
+      // ---- issue the batch ----
+      for (int src = 0; src < in_batch && ok; ++src) {
+        const AdDesc d = s_desc[buf][src];
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), phase ^ 1u, abort_flag) ? 1 : 0);   // one answer per warp
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&full[slot]);
+        if (d.valid != 1) {
+          if (lane == 0) mbar_arrive(bar);
+        } else {
+          const int n_keys = min(AT_BN, d.pos - d.key0 + 1);
+          __nv_bfloat16* ks = ring + (size_t)slot * 2 * tile_elems;
+          __nv_bfloat16* vs = ks + tile_elems;
+          // boxes of the TMA path: rows of one page (or 64 rows of a larger page) x 64 dims
+          const int n_boxes = (n_keys + box_rows - 1) >> box_shift;       // pages of the tile that hold visible keys
+          // keys before the window are not fetched (their rows keep older, finite values and are masked)
+          const int key_skip = d.lo > d.key0 ? d.lo - d.key0 : 0;
+          const int box_first = TMA ? key_skip >> box_shift : 0;
+          const bool new_q = (d.flags & AD_FIRST) != 0;
+          if (lane == 0) {
+            const uint32_t kv_bytes = TMA ? (uint32_t)(2 * (n_boxes - box_first) * box_rows) * row_bytes
+                                    : (uint32_t)(2 * (n_keys - key_skip)) * row_bytes;
+            mbar_expect_tx(bar, (new_q ? (uint32_t)G * row_bytes : 0u) + kv_bytes);
+          }
+          __syncwarp();
+          if (new_q) {
+            __nv_bfloat16* qs = qring + (size_t)d.qslot * q_rows * LD;
+            for (int r = lane; r < G; r += 32)
+              bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)d.tok * nq + d.kvh * G + r) * hd, row_bytes, bar);
+          }
+          if (TMA) {
+            for (int i = lane; i < 2 * (n_boxes - box_first); i += 32) {
+              const int which = i & 1, box = box_first + (i >> 1);
+              const int key = d.key0 + (box << box_shift);
+              const int pg = s_pages[src * pages_ld + (key >> page_shift) - d.pi0];
+              const int row = ((pg * nkv + d.kvh) << page_shift) + (key & (page_size - 1));   // row of the cache [rows][hd]
+              __nv_bfloat16* dst = (which ? vs : ks) + ((size_t)box << box_shift) * HDP;
+              tma_load_rows(dst, which ? &tm_v : &tm_k, row, slab_major, bar);
+            }
+          } else {
+            for (int r = key_skip + lane; r < n_keys; r += 32) {
+              const int key = d.key0 + r;
+              const int pg = s_pages[src * pages_ld + key / page_size - d.pi0];
+              const size_t off = (((size_t)pg * nkv + d.kvh) * page_size + key % page_size) * hd;
+              bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
+              bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+            }
           }
         }
-        ++seq;
-      }
-      __syncwarp();
-    }
-    // a terminator in every slot: each consumer meets one on a slot of its own
-    for (int c = 0; c < stages && ok; ++c, ++seq) {
-      const int slot = (int)(seq % stages);
-      const uint32_t ph = (uint32_t)(seq / stages) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
-      if (!ok) break;
-      if (lane == 0) {
-        desc[slot] = AdDesc{0, 0, 0, 0, 0, 0};
-        mbar_arrive(smem_u32(&full[slot]));
+        if (++slot == stages) { slot = 0; phase ^= 1u; }
       }
       __syncwarp();
     }
@@ -416,54 +590,168 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
   } else {
-    // ---------------- consumers ----------------
+    // ---------------- consumers: all four on the same tile ----------------
     const int g = lane >> 2, qd = lane & 3;
-    // A consumer owns the slots s with s % 4 == warp and sees every phase of them, in order: the
-    // parity it waits for is then never more than one phase ahead of the barrier.
-    for (long seq = 0; warp < stages; ++seq) {
-      const int slot = (int)(seq % stages);
-      if (slot % AD_CONSUMERS != warp) continue;
-      const uint32_t ph = (uint32_t)(seq / stages) & 1u;
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[slot]), ph, abort_flag) ? 1 : 0)) break;
-      const AdDesc d = desc[slot];
-      if (!d.valid) {          // the terminator: give the slot back (the producer may still need it) and stop
+    const int kv_box_rows = min(page_size, AT_BN);
+    const KV kv = make_kv((KV*)nullptr, 31 - __clz(kv_box_rows), slab_major);
+    const int RB = (G + 15) / 16;                        // row blocks of 16 q heads (1..4)
+    const int KS = RB == 1 ? 4 : (RB == 2 ? 2 : 1);      // key slices of a tile
+    const int my_rb = RB == 1 ? 0 : (RB == 2 ? (warp & 1) : warp);
+    const int my_ks = RB == 1 ? warp : (RB == 2 ? (warp >> 1) : 0);
+    const int NK = AT_BN / KS;
+    const bool active = my_rb < RB;
+    const int n_seg_max = n_parts - 1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HDP / 8][4];
+    // up to 128 dims the Q rows stay in registers as MMA fragments while a pair's tiles go by
+    constexpr bool QR = HDP <= 128;
+    constexpr int QF = QR ? HDP / 16 : 1;
+    uint32_t qf[QF][4];
+#pragma unroll
+    for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < QF; ++i) qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0u;
+    uint32_t cph = 0, phase = 0;
+    int slot = 0;
+    // a barrier of the four consumer warps, bounded like every other wait
+    auto cons_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&cbar));
+      const bool fine = __all_sync(0xffffffffu, mbar_wait(smem_u32(&cbar), cph, abort_flag) ? 1 : 0);
+      cph ^= 1u;
+      return fine;
+    };
+    for (int n = 0; n < n_tiles; ++n) {
+      const int my_slot = slot;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full[my_slot]), phase, abort_flag) ? 1 : 0)) break;
+      if (++slot == stages) { slot = 0; phase ^= 1u; }
+      const AdDesc d = s_desc[(n >> 5) & 1][n & 31];
+      if (d.valid != 1) {          // a tile that was passed over
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
-        break;
+        if (lane == 0) mbar_arrive(smem_u32(&empty[my_slot]));
+        continue;
       }
-      const __nv_bfloat16* qs = ring + (size_t)slot * stage_elems;
-      const __nv_bfloat16* ks = qs + q_elems;
-      const __nv_bfloat16* vs = ks + tile_elems;
-      const int key0 = d.split * AT_BN;
-      for (int rb = 0; rb < G; rb += 16) {
-        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-        float o[HDP / 8][4];
+      if (d.flags & AD_FIRST) {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
 #pragma unroll
         for (int i = 0; i < HDP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      }
+      const __nv_bfloat16* qs = qring + ((size_t)d.qslot * q_rows + (size_t)my_rb * 16) * LD;
+      if (QR && (d.flags & AD_FIRST)) {
+        // the pair's Q rows came with this tile: keep them as MMA fragments for all of its tiles
+#pragma unroll
+        for (int kk = 0; kk < QF; ++kk)
+          ldmatrix_x4(qf[kk], qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+      }
+      __nv_bfloat16* ks = ring + (size_t)my_slot * 2 * tile_elems;
+      const __nv_bfloat16* vs = ks + tile_elems;
+      const int kb = d.key0 + my_ks * NK;                // first key of this warp's slice
+      if (active && kb <= d.pos && kb + NK - 1 >= d.lo) {
         int row_lo[2], row_hi[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          row_hi[r] = (rb + g + 8 * r < G) ? d.pos : -1;
+          row_hi[r] = d.pos;      // rows past the group are computed like the others and never written
           row_lo[r] = d.lo;
         }
-        attend_block<HDP, KV>(qs + (size_t)rb * LD, ks, vs, key0, row_lo, row_hi, scale_log2, m, l, o);
+        if (KS == 4) attend_block<HDP, KV, 16, QR>(qs, ks, vs, kb, row_lo, row_hi, scale_log2, m, l, o, my_ks * 16, qf, kv);
+        else if (KS == 2) attend_block<HDP, KV, 32, QR>(qs, ks, vs, kb, row_lo, row_hi, scale_log2, m, l, o, my_ks * 32, qf, kv);
+        else attend_block<HDP, KV, 64, QR>(qs, ks, vs, kb, row_lo, row_hi, scale_log2, m, l, o, 0, qf, kv);
+      }
+      if (!(d.flags & AD_LAST)) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty[my_slot]));      // this warp has read the tile
+        continue;
+      }
+      // ---- the segment ends here: one partial result (or the final output) per q head ----
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-          l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-          const int row = rb + g + 8 * r;
-          if (row >= G) continue;
-          const size_t at = ((size_t)d.z * nq + d.kvh * G + row) * n_splits_max + d.split;
-          if (qd == 0) { part_ml[at * 2] = m[r]; part_ml[at * 2 + 1] = l[r]; }
+      for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      }
+      const bool fits = d.seg < n_seg_max;
+      if (!fits && tid == 0) qb_set_status(status, QB_STATUS_SCRATCH_SMALL, d.seg, 6);
+      const int count = (d.flags & AD_WHOLE) ? 0 : min(d.seg + 1, n_seg_max);
+      if (KS == 1) {
+        if (active) {
 #pragma unroll
-          for (int i = 0; i < HDP / 8; ++i) {
-            const int dd = i * 8 + qd * 2;
-            if (dd < hd) *reinterpret_cast<float2*>(part_o + at * hd + dd) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+          for (int r = 0; r < 2; ++r) {
+            const int row = my_rb * 16 + g + 8 * r;
+            if (row >= G) continue;
+            const int head = d.kvh * G + row;
+            const size_t row_at = ((size_t)d.z * nq + head) * n_parts;
+            if (d.flags & AD_WHOLE) {
+              const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+              __nv_bfloat16* dst = out + ((size_t)d.tok * nq + head) * hd;
+#pragma unroll
+              for (int i = 0; i < HDP / 8; ++i) {
+                const int dd = i * 8 + qd * 2;
+                if (dd < hd) *reinterpret_cast<uint32_t*>(dst + dd) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+              }
+            } else if (fits) {
+              const size_t at = row_at + d.seg;
+              if (qd == 0) { part_ml[at * 2] = m[r]; part_ml[at * 2 + 1] = l[r]; }
+#pragma unroll
+              for (int i = 0; i < HDP / 8; ++i) {
+                const int dd = i * 8 + qd * 2;
+                if (dd < hd) *reinterpret_cast<float2*>(part_o + at * hd + dd) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+              }
+            }
+            if (qd == 0 && (d.flags & AD_PAIR_END)) part_ml[(row_at + n_parts - 1) * 2] = __int_as_float(count);
           }
         }
+      } else {
+        // the warps hold key slices of the same rows: merge them through the tile's own shared memory
+        if (!cons_sync()) break;                         // every warp has read the tile
+        float* sc = reinterpret_cast<float*>(ks);        // [4 warps][16 rows][HDP], columns XORed by (row & 3) * 8
+        if (active) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int rr = g + 8 * r;
+            if (my_rb * 16 + rr >= G) continue;
+            if (qd == 0) { s_ml[warp][rr][0] = m[r]; s_ml[warp][rr][1] = l[r]; }
+#pragma unroll
+            for (int i = 0; i < HDP / 8; ++i) {
+              const int col = (i * 8 + qd * 2) ^ ((rr & 3) * 8);
+              *reinterpret_cast<float2*>(sc + (size_t)(warp * 16 + rr) * HDP + col) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+            }
+          }
+        }
+        if (!cons_sync()) break;
+        const int ctid = warp * 32 + lane;
+        for (int e = ctid; e < G * hd; e += AD_CONSUMERS * 32) {
+          const int R = e / hd, dd = e - R * hd, rb = R >> 4, rr = R & 15;
+          float M = -INFINITY;
+          for (int s = 0; s < KS; ++s) {
+            const int w = RB == 1 ? s : (rb | (s << 1));
+            M = fmaxf(M, s_ml[w][rr][0]);
+          }
+          float acc = 0.f, L = 0.f;
+          for (int s = 0; s < KS; ++s) {
+            const int w = RB == 1 ? s : (rb | (s << 1));
+            const float ms = s_ml[w][rr][0];
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            acc += f * sc[(size_t)(w * 16 + rr) * HDP + (dd ^ ((rr & 3) * 8))];
+            L += f * s_ml[w][rr][1];
+          }
+          const int head = d.kvh * G + R;
+          const size_t row_at = ((size_t)d.z * nq + head) * n_parts;
+          if (d.flags & AD_WHOLE) {
+            out[((size_t)d.tok * nq + head) * hd + dd] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+          } else if (fits) {
+            const size_t at = row_at + d.seg;
+            part_o[at * hd + dd] = acc;
+            if (dd == 0) { part_ml[at * 2] = M; part_ml[at * 2 + 1] = L; }
+          }
+          if (dd == 0 && (d.flags & AD_PAIR_END)) part_ml[(row_at + n_parts - 1) * 2] = __int_as_float(count);
+        }
+        if (!cons_sync()) break;                         // the merged rows have been read
+        // the tile goes back as zeros: rows that the next copy does not cover must stay finite
+        for (size_t i = ctid; i < 2 * tile_elems / 8; i += AD_CONSUMERS * 32) reinterpret_cast<uint4*>(ks)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));      // the tile's rows have been read: the slot is free
+      if (lane == 0) mbar_arrive(smem_u32(&empty[my_slot]));
     }
   }
   __syncthreads();
@@ -664,21 +952,23 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
 }
 
-// out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits that hold visible keys
+// The pairs that the blocks' ranges cut: out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over
+// the pair's segments, in index order.  The last entry of a row of part_ml holds the number of segments
+// (0: the decode kernel wrote the final output itself).
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  __nv_bfloat16* __restrict__ out, const int* __restrict__ dec_tok,
-                                  const int* __restrict__ tok_pos, int nq, int hd, int window, int n_splits_max,
-                                  int split_keys) {
-  const int z = blockIdx.y, t = dec_tok[z], head = blockIdx.x;
-  const int pos = tok_pos[t];
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s_first = lo / split_keys, s_last = min(pos / split_keys, n_splits_max - 1);
-  const size_t base = ((size_t)z * nq + head) * n_splits_max;
+                                  __nv_bfloat16* __restrict__ out, const int* __restrict__ dec_tok, int nq, int hd,
+                                  int n_parts) {
+  const int z = blockIdx.y, head = blockIdx.x;
+  const size_t base = ((size_t)z * nq + head) * n_parts;
+  int n = __float_as_int(part_ml[(base + n_parts - 1) * 2]);
+  if (n <= 0) return;
+  n = min(n, n_parts - 1);
+  const int t = dec_tok[z];
   float M = -INFINITY;
-  for (int s = s_first; s <= s_last; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f, L = 0.f;
-    for (int s = s_first; s <= s_last; ++s) {
+    for (int s = 0; s < n; ++s) {
       const float ms = part_ml[(base + s) * 2];
       const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
       acc += f * part_o[(base + s) * hd + d];
@@ -718,6 +1008,34 @@ int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t hd, 
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : QB_ERR_BAD_ARG;
+}
+
+// The same cache seen as 3-D so that one box is box_rows whole rows (all slabs of 64 dims): slab-major
+// [slabs][rows][64] if the driver takes strides that do not grow, else interleaved [rows][slabs][64].
+// QUANTA_B200_KV_BOXES=interleaved asks for the second form (for tests).
+int make_kv_map_rows(CUtensorMap* map, const void* base, uint64_t rows, uint64_t hd, uint32_t box_rows, int* slab_major) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return QB_ERR_UNSUPPORTED;
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const char* want = getenv("QUANTA_B200_KV_BOXES");
+  const bool try_slab_major = !(want != nullptr && strcmp(want, "interleaved") == 0) && *slab_major != 0;
+  if (try_slab_major) {
+    const cuuint64_t dims[3] = {64, rows, hd / 64};
+    const cuuint64_t strides[2] = {hd * 2, 128};
+    const cuuint32_t box[3] = {64, box_rows, (cuuint32_t)(hd / 64)};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) { *slab_major = 1; return 0; }
+  }
+  *slab_major = 0;
+  const cuuint64_t dims[3] = {64, hd / 64, rows};
+  const cuuint64_t strides[2] = {128, hd * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)(hd / 64), box_rows};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : QB_ERR_UNSUPPORTED;
 }
 
 template <typename Kern>
@@ -783,55 +1101,76 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
   return 0;
 }
 
-// Keys per decode split for a head size (the Python side sizes the scratch with it).
-extern "C" int qb_attn_decode_split_keys(int hd) { (void)hd; return AT_BN; }
+// Entries per (token, q head) row of the decode scratch for contexts of up to max_len keys: the most
+// segments a pair can be cut into by the blocks' equal ranges, and one entry for their count.
+extern "C" int qb_attn_decode_parts(int nkv, int max_len) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return QB_ERR_UNSUPPORTED;
+  if (nkv <= 0 || max_len <= 0) return QB_ERR_BAD_ARG;
+  const int tiles = (max_len + AT_BN - 1) / AT_BN;
+  const int cut = 2 * sms / nkv + 2;
+  return (tiles < cut ? tiles : cut) + 1;
+}
 
-// Scratch, in floats: part_o n_dec*nq*n_splits_max*hd, part_ml n_dec*nq*n_splits_max*2, where
-// n_splits_max >= ceil(longest context / split keys).
+// Scratch, in floats: part_o n_dec*nq*n_parts*hd, part_ml n_dec*nq*n_parts*2, with
+// n_parts >= qb_attn_decode_parts(nkv, longest context).  Up to 64 q heads per kv head.
 extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
                               float* part_ml, const int* dec_tok, int n_dec, const int* tok_pos, const int* tok_req,
                               const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
-                              int num_pages, float scale, int window, int n_splits_max, int* status,
+                              int num_pages, float scale, int window, int n_parts, int* status,
                               cudaStream_t stream) {
   if (n_dec <= 0) return 0;
-  if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535 || n_dec > 65535 || n_splits_max <= 0)
+  if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535 || n_dec > 65535 || n_parts < 2 || page_size <= 0)
     return QB_ERR_UNSUPPORTED;
   const float scale_log2 = scale * 1.4426950408889634f;
-  const int split_keys = AT_BN;
-  const int G = nq / nkv, q_rows = (G + 15) / 16 * 16;
-  int dev = 0, sms = 0;
+  const int G = nq / nkv, q_rows = ad_q_rows(G);
+  if (G > 16 * AD_CONSUMERS) return QB_ERR_UNSUPPORTED;
+  int dev = 0, sms = 0, smem_optin = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (err == cudaSuccess) err = cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (err != cudaSuccess) return (int)err;
-  const long total = (long)n_dec * nkv * n_splits_max;
-  const int blocks = (int)(total < sms ? total : sms);
   // TMA tensor loads when the shapes allow (whole 64-dim slabs, pages that tile 64 keys), else row copies
   const bool pow2 = (page_size & (page_size - 1)) == 0;
-  const bool tma = hd % 64 == 0 && pow2 && (page_size <= AT_BN || page_size % AT_BN == 0) && encode_fn() != nullptr &&
+  const bool tma = (hd == 64 || hd == 128 || hd == 256) && pow2 && (page_size <= AT_BN || page_size % AT_BN == 0) && encode_fn() != nullptr &&
                    (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
   CUtensorMap tm_k, tm_v;
+  int slab_major = 1;
   memset(&tm_k, 0, sizeof(tm_k));
   memset(&tm_v, 0, sizeof(tm_v));
   if (tma) {
     const uint64_t rows = (uint64_t)num_pages * nkv * page_size;
     const uint32_t box_rows = (uint32_t)(page_size < AT_BN ? page_size : AT_BN);
-    int rc = make_kv_map(&tm_k, k_cache, rows, (uint64_t)hd, box_rows);
-    if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, (uint64_t)hd, box_rows);
+    int rc = make_kv_map_rows(&tm_k, k_cache, rows, (uint64_t)hd, box_rows, &slab_major);
+    if (rc == 0) rc = make_kv_map_rows(&tm_v, v_cache, rows, (uint64_t)hd, box_rows, &slab_major);
     if (rc) return rc;
   }
+  const int pages_ld = AT_BN / (page_size < AT_BN ? page_size : AT_BN) + 2;     // page ids a tile can touch
 #define QB_DEC(HDP, TMA_)                                                                                  \
   do {                                                                                                     \
-    const size_t stage_bytes = (ad_q_elems(HDP, q_rows, TMA_) + 2 * ad_tile_elems(HDP, TMA_)) * 2;         \
-    int stages = (int)((size_t)(194 * 1024) / stage_bytes);                                                \
-    stages = stages >= 8 ? 8 : (stages >= 4 ? 4 : stages);   /* a multiple of the consumers: equal shares */ \
+    cudaFuncAttributes fa;                                                                                 \
+    err = cudaFuncGetAttributes(&fa, attn_decode_kernel<HDP, TMA_>);                                       \
+    if (err != cudaSuccess) return (int)err;                                                               \
+    const size_t q_bytes = (size_t)q_rows * (HDP + AT_PAD) * 2;  /* one more Q slot than tiles, 8 zero rows */ \
+    const size_t stage_bytes = 2 * ad_tile_elems(HDP, TMA_) * 2 + q_bytes;                                 \
+    const size_t fixed = 1024 + q_bytes + 8 * (HDP + AT_PAD) * 2 +                                         \
+                         (size_t)(4 * AD_MAX_DEC + 1 + 32 * pages_ld) * sizeof(int);                       \
+    const long room = (long)smem_optin - (long)fa.sharedSizeBytes - (long)fixed;                           \
+    int stages = room > 0 ? (int)((size_t)room / stage_bytes) : 0;                                         \
+    if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;                                                    \
     if (stages < 2) return QB_ERR_UNSUPPORTED;                                                             \
-    const size_t smem = stage_bytes * stages + 1024;         /* room to align the ring to 1024 bytes */    \
+    const size_t smem = stage_bytes * stages + fixed;        /* 1024 of it to align the ring */            \
     int rc = set_smem(attn_decode_kernel<HDP, TMA_>, smem);                                                \
     if (rc) return rc;                                                                                     \
-    attn_decode_kernel<HDP, TMA_><<<blocks, AD_THREADS, smem, stream>>>(                                   \
-        tm_k, tm_v, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-        part_o, part_ml, dec_tok, n_dec, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, \
-        num_pages, scale_log2, window, n_splits_max, stages, q_rows, status);                              \
+    for (int z0 = 0; z0 < n_dec; z0 += AD_MAX_DEC) {                                                       \
+      const int n = n_dec - z0 < AD_MAX_DEC ? n_dec - z0 : AD_MAX_DEC;                                     \
+      attn_decode_kernel<HDP, TMA_><<<sms, AD_THREADS, smem, stream>>>(                                    \
+          tm_k, tm_v, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+          (__nv_bfloat16*)out, part_o + (size_t)z0 * nq * n_parts * hd, part_ml + (size_t)z0 * nq * n_parts * 2, \
+          dec_tok + z0, n, tok_pos, tok_req, block_table, bt_stride, nq, nkv, hd, page_size, num_pages,    \
+          scale_log2, window, n_parts, stages, pages_ld, slab_major, status);                              \
+    }                                                                                                      \
   } while (0)
   if (tma) {
     if (hd <= 64) QB_DEC(64, true);
@@ -843,8 +1182,7 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
     else QB_DEC(256, false);
   }
 #undef QB_DEC
-  attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, tok_pos, nq,
-                                                         hd, window, n_splits_max, split_keys);
+  attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, nq, hd, n_parts);
   QB_LAUNCH_CHECK();
   return 0;
 }
@@ -855,7 +1193,7 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
 // ------------------------------------------------------------------------------------------------
 #include "no_alloc.h"
 
-// Partial results of the split-key kernel for one call at a time.  Host code must not hand this
+// Partial results of the decode kernel for one call at a time.  Host code must not hand this
 // name to a kernel: on the host it is only a stand-in for the symbol; the device address is looked
 // up once per device below.
 static __device__ __align__(256) float qb_noalloc_scratch[QB_NOALLOC_SCRATCH_FLOATS];
@@ -865,9 +1203,9 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
 }  // namespace
 
-extern "C" long long qb_attn_decode_noalloc_floats(int n_dec, int nq, int hd, int n_splits_max) {
-  if (n_dec <= 0 || nq <= 0 || hd <= 0 || n_splits_max <= 0) return 0;
-  return (long long)n_dec * nq * n_splits_max * (hd + 2);
+extern "C" long long qb_attn_decode_noalloc_floats(int n_dec, int nq, int hd, int n_parts) {
+  if (n_dec <= 0 || nq <= 0 || hd <= 0 || n_parts <= 0) return 0;
+  return (long long)n_dec * nq * n_parts * (hd + 2);
 }
 
 extern "C" long long qb_attn_decode_noalloc_capacity(void) { return (long long)QB_NOALLOC_SCRATCH_FLOATS; }
@@ -875,11 +1213,11 @@ extern "C" long long qb_attn_decode_noalloc_capacity(void) { return (long long)Q
 extern "C" int qb_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* dec_tok, int n_dec, const int* tok_pos, const int* tok_req,
                                       const int* block_table, int bt_stride, int nq, int nkv, int hd, int page_size,
-                                      int num_pages, float scale, int window, int n_splits_max, int* status,
+                                      int num_pages, float scale, int window, int n_parts, int* status,
                                       cudaStream_t stream) {
   if (n_dec <= 0) return 0;
-  if (nq <= 0 || hd <= 0 || n_splits_max <= 0) return QB_ERR_BAD_ARG;
-  const long long need = qb_attn_decode_noalloc_floats(n_dec, nq, hd, n_splits_max);
+  if (nq <= 0 || hd <= 0 || n_parts <= 0) return QB_ERR_BAD_ARG;
+  const long long need = qb_attn_decode_noalloc_floats(n_dec, nq, hd, n_parts);
   if (need > (long long)QB_NOALLOC_SCRATCH_FLOATS) return QB_NOALLOC_TOO_LARGE;
   int dev = -1;
   cudaError_t err = cudaGetDevice(&dev);
@@ -895,7 +1233,7 @@ extern "C" int qb_attn_decode_noalloc(const void* q, const void* k_cache, const 
   }
   float* part_o = g_noalloc_ptr[dev];
   // the (max, sum) pairs follow the partial outputs; the offset keeps them 8-byte aligned
-  float* part_ml = part_o + (size_t)n_dec * nq * n_splits_max * hd;
+  float* part_ml = part_o + (size_t)n_dec * nq * n_parts * hd;
   return qb_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec, tok_pos, tok_req, block_table,
-                        bt_stride, nq, nkv, hd, page_size, num_pages, scale, window, n_splits_max, status, stream);
+                        bt_stride, nq, nkv, hd, page_size, num_pages, scale, window, n_parts, status, stream);
 }

@@ -3,8 +3,9 @@
  * This entry point has no counterpart in the reference (pmrjge/quanta has no device code of its own);
  * it exists for users of this library's C ABI.
  *
- * Who needs it.  The split-key decode attention (qb_attn_decode) writes a partial result per split
- * of the keys and merges them, so it wants scratch memory from its caller.  Some callers have none to
+ * Who needs it.  The decode attention (qb_attn_decode) cuts the keys of long contexts over several
+ * blocks, which leave partial results that a second kernel merges, so it wants scratch memory from
+ * its caller (n_parts = qb_attn_decode_parts(kv heads, longest context) entries per token and head).  Some callers have none to
  * give and cannot get any: a host program that handed the whole device to a pool of its own (a
  * serving process that sized its cache to the last byte and treats any later cudaMalloc as a
  * failure); a plug-in loaded into such a process through this C ABI, with no handle on that pool; a
@@ -16,7 +17,7 @@
  * Contract.
  *  - Same inputs and outputs as qb_attn_decode, without the two scratch pointers.  The call allocates
  *    nothing and calls no allocating routine (no cudaMalloc, cudaFree, no torch).
- *  - Sizes: n_dec * nq * n_splits_max * (hd + 2) floats must fit in the array; a larger problem is
+ *  - Sizes: n_dec * nq * n_parts * (hd + 2) floats must fit in the array; a larger problem is
  *    refused with QB_NOALLOC_TOO_LARGE and nothing is launched.  qb_attn_decode_noalloc_floats()
  *    returns what a call needs; qb_attn_decode_noalloc_capacity() the size of the array.
  *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
@@ -37,13 +38,13 @@
 extern "C" {
 #endif
 
-long long qb_attn_decode_noalloc_floats(int n_dec, int nq, int hd, int n_splits_max);
+long long qb_attn_decode_noalloc_floats(int n_dec, int nq, int hd, int n_parts);
 long long qb_attn_decode_noalloc_capacity(void);
 
 int qb_attn_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* dec_tok,
                            int n_dec, const int* tok_pos, const int* tok_req, const int* block_table, int bt_stride,
                            int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                           int n_splits_max, int* status, cudaStream_t stream);
+                           int n_parts, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -19,7 +19,8 @@ _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 NORM_NONE, NORM_PER_LAYER, NORM_PER_HEAD = 0, 1, 2
 
 _STATUS_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool (block table)",
-                3: "expert id outside the expert table", 4: "a bounded device wait ran out"}
+                3: "expert id outside the expert table", 4: "a bounded device wait ran out",
+                5: "the decode attention scratch has too few entries per row"}
 _KERNEL_TEXT = {1: "embedding", 2: "rope/cache write", 3: "paged attention", 4: "expert plan",
                 5: "expert product", 6: "decode attention", 7: "prefill attention"}
 
@@ -180,8 +181,15 @@ def attn_span_rows(hd: int) -> int:
     return int(lib().qb_attn_span_rows(int(hd)))
 
 
-def attn_decode_split_keys(hd: int) -> int:
-    return int(lib().qb_attn_decode_split_keys(int(hd)))
+def attn_decode_parts(nkv: int, max_len: int) -> int:
+    """Entries per (token, q head) row of the decode attention scratch for contexts of up to ``max_len`` keys."""
+    n = int(lib().qb_attn_decode_parts(int(nkv), int(max_len)))
+    if n < 2:
+        raise KernelError(f"attn_decode_parts({nkv}, {max_len}) failed with code {n}")
+    return n
+
+
+ATTN_DECODE_MAX_GROUP = 64      # q heads per kv head that the decode kernel takes
 
 
 def attn_span(q, k_cache, v_cache, out, tok_pos, block_table, tiles, scale: float, window: int, status) -> None:
@@ -198,20 +206,20 @@ def attn_span(q, k_cache, v_cache, out, tok_pos, block_table, tiles, scale: floa
 
 
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec: int, tok_pos, tok_req, block_table,
-                scale: float, window: int, n_splits_max: int, status) -> None:
-    """bfloat16 tensor-core attention for single tokens, split over the keys; ``part_o`` / ``part_ml``
-    are float32 scratch of at least n_dec*nq*n_splits_max*hd and n_dec*nq*n_splits_max*2 elements."""
+                scale: float, window: int, n_parts: int, status) -> None:
+    """bfloat16 tensor-core attention for single tokens; ``part_o`` / ``part_ml`` are float32 scratch of
+    at least n_dec*nq*n_parts*hd and n_dec*nq*n_parts*2 elements, ``n_parts`` from ``attn_decode_parts``."""
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
     _want(q, torch.bfloat16, "q"); _want(k_cache, torch.bfloat16, "k_cache")
     _want(part_o, torch.float32, "part_o"); _want(part_ml, torch.float32, "part_ml"); _want(dec_tok, torch.int32, "dec_tok")
     if hd2 != hd or out.shape != q.shape or out.dtype != q.dtype:
         raise ValueError("attn_decode: shape/dtype mismatch")
-    if part_o.numel() < n_dec * nq * n_splits_max * hd or part_ml.numel() < n_dec * nq * n_splits_max * 2:
+    if part_o.numel() < n_dec * nq * n_parts * hd or part_ml.numel() < n_dec * nq * n_parts * 2:
         raise ValueError("attn_decode: scratch too small")
     _check(lib().qb_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_ml), _p(dec_tok),
                                 int(n_dec), _p(tok_pos), _p(tok_req), _p(block_table), block_table.shape[1], nq, nkv,
-                                hd, page_size, num_pages, ctypes.c_float(scale), int(window), int(n_splits_max),
+                                hd, page_size, num_pages, ctypes.c_float(scale), int(window), int(n_parts),
                                 _p(status), _stream()), "attn_decode", 2)
 
 

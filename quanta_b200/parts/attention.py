@@ -91,22 +91,27 @@ class GQAttention(Mixer):
 
     def attend(self, q, cache, out, ctx):
         """float32: the SIMT kernel, every token alike.  bfloat16: tensor-core kernels, one for single
-        tokens (split over the keys) and one for portions (tiles of 64 token-by-head rows)."""
+        tokens (the keys of all of them dealt evenly over the SMs) and one for portions (tiles of
+        token-by-head rows)."""
         window = self.window or 0
         if q.dtype != torch.bfloat16:
             kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
                                          self.scale, window, ctx.status)
             return
         dec_tok, n_dec, spans = step_work(ctx, q.device)
+        G = self.nq // self.nkv
+        if n_dec and G > kernels.ATTN_DECODE_MAX_GROUP:
+            # more q heads per kv head than the single-token kernel takes: such a token is a portion of one
+            starts = ctx.host.get("req_start") or [0, ctx.n_tokens]
+            spans = [(r, starts[r], starts[r + 1] - starts[r]) for r in range(len(starts) - 1)]
+            n_dec = 0
         if n_dec:
-            split = kernels.attn_decode_split_keys(self.hd)
-            n_splits = max(1, -(-ctx.max_len_after // split))
-            part_o = torch.empty(n_dec * self.nq * n_splits * self.hd, dtype=torch.float32, device=q.device)
-            part_ml = torch.empty(n_dec * self.nq * n_splits * 2, dtype=torch.float32, device=q.device)
+            n_parts = kernels.attn_decode_parts(self.nkv, max(1, ctx.max_len_after))
+            part_o = torch.empty(n_dec * self.nq * n_parts * self.hd, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(n_dec * self.nq * n_parts * 2, dtype=torch.float32, device=q.device)
             kernels.attn_decode(q, cache.k, cache.v, out, part_o, part_ml, dec_tok, n_dec, ctx.tok_pos, ctx.tok_req,
-                                cache.block_table, self.scale, window, n_splits, ctx.status)
+                                cache.block_table, self.scale, window, n_parts, ctx.status)
         if spans:
-            G = self.nq // self.nkv
             key = ("span_tiles", G, self.hd)
             if key not in ctx.work:
                 rows = kernels.attn_span_rows(self.hd)

@@ -149,7 +149,8 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 3, 48, 4, 0), (4, 4, 16, 16, 0), (12, 2, 128, 8, 0),
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
-                                                   (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37)])
+                                                   (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
+                                                   (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50)])
 @pytest.mark.parametrize("impl", ["simt", "mma"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
     k = K()
@@ -187,17 +188,17 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
         G, row0 = nq // nkv, 0
         dec, tiles = [], []
         for r, (a, n) in enumerate(spans):
-            if n == 1:
+            if n == 1 and G <= k.ATTN_DECODE_MAX_GROUP:      # larger groups: a single token is a portion of one
                 dec.append(row0)
             else:
                 tiles += [[r, row0, n, x] for x in range(0, n * G, k.attn_span_rows(hd))]
             row0 += n
-        split = k.attn_decode_split_keys(hd)
-        n_splits = -(-(max(a + n for a, n in spans)) // split)
-        po = torch.full((len(dec) * nq * n_splits * hd,), float("nan"), device=DEV)
-        pml = torch.full((len(dec) * nq * n_splits * 2,), float("nan"), device=DEV)
-        k.attn_decode(q, kc, vc, out, po, pml, torch.tensor(dec, dtype=torch.int32, device=DEV), len(dec),
-                      tok_pos.to(DEV), tok_req.to(DEV), table.to(DEV), scale, window, n_splits, st)
+        n_parts = k.attn_decode_parts(nkv, max(a + n for a, n in spans))
+        po = torch.full((len(dec) * nq * n_parts * hd,), float("nan"), device=DEV)
+        pml = torch.full((len(dec) * nq * n_parts * 2,), float("nan"), device=DEV)
+        if dec:
+            k.attn_decode(q, kc, vc, out, po, pml, torch.tensor(dec, dtype=torch.int32, device=DEV), len(dec),
+                          tok_pos.to(DEV), tok_req.to(DEV), table.to(DEV), scale, window, n_parts, st)
         k.attn_span(q, kc, vc, out, tok_pos.to(DEV), table.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
                     scale, window, st)
 

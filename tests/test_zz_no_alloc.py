@@ -43,8 +43,7 @@ def _case(seed, contexts, nq=12, nkv=2, hd=128, page=16):
 
 
 def _existing(k, c):
-    split = k.attn_decode_split_keys(c["hd"])
-    n_splits = -(-c["longest"] // split)
+    n_splits = k.attn_decode_parts(c["nkv"], c["longest"])
     out = torch.full_like(c["q"], float("nan"))
     po = torch.empty(c["n"] * c["nq"] * n_splits * c["hd"], device=DEV)
     pml = torch.empty(c["n"] * c["nq"] * n_splits * 2, device=DEV)
