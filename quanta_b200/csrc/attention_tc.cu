@@ -1,0 +1,548 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (head size 128).
+//
+// One block = 128 query rows of ONE request and ONE kv head, where a row is a (token, q head of the
+// group) pair, against the request's keys in blocks of 128:
+//
+//   warp 0     : TMA producer of K blocks, warp 1: of V blocks (boxes of [rows of a page x 64 dims],
+//                128-byte swizzle, two-stage rings with mbarriers).
+//   warp 2     : MMA issuer (one thread).  S = Q K^T as eight tcgen05.mma of K = 16 (M = 128 rows,
+//                N = 128 keys, both operands K-major) into one of two S buffers in TMEM; O_blk = P V
+//                as eight more (N = 128 dims, V is the MN-major operand as it lies in the cache) into
+//                one of two O buffers in TMEM.  tcgen05.commit frees the stages and signals the readers.
+//   warps 3-6  : softmax.  A thread owns one row (one TMEM lane): it reads S with tcgen05.ld, keeps the
+//                running maximum and sum in float32 (exp2 domain), writes P as bfloat16 into the
+//                swizzled shared-memory tile the next MMA reads, and adds O_blk, rescaled, to the row's
+//                128 float32 accumulators in registers.  The S = Q K^T of the next block and the P V of
+//                the block before run while the threads work on a block: a thread takes the maximum of
+//                block j, adds the P V of block j-1, then writes the probabilities of block j.
+//
+// (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
+// probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
+// Each row is masked by its own token's position (and window), so portions of any length run, from the
+// cache that earlier steps and this step's rope kernel wrote.  No multicast, no clusters.  Every wait is
+// bounded; when one runs out the block records it in the status words, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TC_BM = 128;           // query rows per block (UMMA M)
+constexpr int TC_BN = 128;           // keys per block
+constexpr int TC_HD = 128;           // head size
+constexpr int TC_THREADS = 7 * 32;
+constexpr int TC_MAX_PAGES = 2048;
+constexpr uint32_t TC_TILE_BYTES = TC_BM * TC_HD * 2;       // 32 KB: Q, P, and each K or V stage
+constexpr uint32_t TC_SLAB_BYTES = TC_BM * 128;             // one slab: 128 rows x 64 elements
+constexpr uint32_t TC_SPIN_LIMIT = 4u * 1000u * 1000u;
+constexpr uint64_t TC_WAIT_NS = 200ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// The thread sleeps in the instruction until the phase completes or about a microsecond has passed, so
+// that a waiting warp leaves the issue slots of its scheduler to the warps that work.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when another role gave up or the limit (iterations and 0.2 s) is reached.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 127u) == 127u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > TC_WAIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+// one [box rows x 64 dims] box of a cache seen as a 2-D tensor [rows, head_dim]; no multicast
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int dim0, int row, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(dim0), "r"(row), "r"(bar) : "memory");
+}
+
+// Operand tile in shared memory in lines of 128 bytes with the 128-byte swizzle, 8-line groups 1024 bytes
+// apart.  K-major (Q, K, P: a line is 64 k elements of one row): stride offset 1024, leading offset unused.
+// MN-major (V as the N operand: a line is 64 dims of one key): stride offset 1024 between groups of 8
+// keys, leading offset one slab between groups of 64 dims.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t leading_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((leading_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // 128-byte swizzle
+  return d;
+}
+// kind::f16, bfloat16 x bfloat16 -> float32; b_mn: the B operand is MN-major
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 2^x on the special-function unit; x is at most 0 here, tiny results flush to zero
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct TcShared {
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full[2], p_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                    const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
+                    const int* __restrict__ tiles, int nq, int nkv, int page_size, int num_pages,
+                    float scale_log2, int window, int* status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_s = smem_u32(base), p_s = q_s + TC_TILE_BYTES, k_s = p_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
+  __shared__ TcShared sh;
+  __shared__ int s_page[TC_MAX_PAGES];
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
+  const int kvh = blockIdx.y, G = nq / nkv;
+  const int n_rows = min(TC_BM, n_tok * G - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* bt = block_table + (size_t)req * bt_stride;
+
+  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
+  const int key_end = tok_pos[last_tok];
+  const int p_first = tok_pos[first_tok];
+  const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;   // the lowest key any row reads
+  const int key_begin = lo_min / TC_BN * TC_BN;
+  const int n_blocks = (key_end - key_begin) / TC_BN + 1;
+
+  // Q rows into the swizzled tile (zero past the last row); the K and V rings start as zeros, so that
+  // rows no copy covers hold zeros or older keys, never anything that is not a number
+  for (int c = tid; c < TC_BM * (TC_HD / 8); c += TC_THREADS) {
+    const int r = c / (TC_HD / 8), ch = c % (TC_HD / 8);      // 16-byte chunk ch of row r
+    const int R = row0 + r;
+    const bool ok = r < n_rows;
+    const __nv_bfloat16* src = q;
+    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD + ch * 8;
+    cp_async16(q_s + (ch >> 3) * TC_SLAB_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), src, ok);
+  }
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TC_THREADS)
+    reinterpret_cast<uint4*>(base + 2 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
+  const int pi0 = key_begin / page_size;
+  const int n_pi = key_end / page_size - pi0 + 1;
+  const bool pages_in_smem = n_pi <= TC_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = tid; i < n_pi; i += TC_THREADS) s_page[i] = bt[pi0 + i];
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&sh.k_full[s]), 1);
+      mbar_init(smem_u32(&sh.k_empty[s]), 1);
+      mbar_init(smem_u32(&sh.v_full[s]), 1);
+      mbar_init(smem_u32(&sh.v_empty[s]), 1);
+      mbar_init(smem_u32(&sh.s_full[s]), 1);
+      mbar_init(smem_u32(&sh.o_full[s]), 1);
+    }
+    mbar_init(smem_u32(&sh.p_full), 128);
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {      // the whole TMEM: two S buffers and two O buffers of 128 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&sh.tmem_base)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q and the zeros, before TMA and the MMAs
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp < 2) {
+    // ---------------- TMA producers: warp 0 streams K blocks, warp 1 V blocks ----------------
+    const CUtensorMap* map = warp == 0 ? &tm_k : &tm_v;
+    uint64_t* full = warp == 0 ? sh.k_full : sh.v_full;
+    uint64_t* empty = warp == 0 ? sh.k_empty : sh.v_empty;
+    const uint32_t ring = warp == 0 ? k_s : v_s;
+    const int box_rows = min(page_size, TC_BN);
+    bool ok = true;
+    for (int b = 0; b < n_blocks && ok; ++b) {
+      const int slot = b & 1;
+      const uint32_t ph = (uint32_t)(b >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      const int key0 = key_begin + b * TC_BN;
+      const int n_keys = min(TC_BN, key_end - key0 + 1);
+      const int n_req = 2 * ((n_keys + box_rows - 1) / box_rows);      // boxes: pages with visible keys x two slabs
+      const uint32_t bar = smem_u32(&full[slot]);
+      // a page id outside the pool is recorded and its rows are not copied (the byte count must match);
+      // keys before every row's window are not fetched: their pages may have been given back already
+      int skipped = 0;
+      for (int i = lane; i < n_req; i += 32) {
+        const int key = key0 + (i >> 1) * box_rows;
+        if (key + box_rows - 1 < lo_min) { ++skipped; continue; }
+        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+        if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++skipped; }
+      }
+      skipped = __reduce_add_sync(0xffffffffu, skipped);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_req - skipped) * (uint32_t)box_rows * 128u);
+      __syncwarp();
+      for (int i = lane; i < n_req; i += 32) {
+        const int slab = i & 1, box = i >> 1;
+        const int key = key0 + box * box_rows;
+        if (key + box_rows - 1 < lo_min) continue;
+        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+        if (pg < 0 || pg >= num_pages) continue;
+        const int row = (pg * nkv + kvh) * page_size + key % page_size;
+        tma_load_box(ring + slot * TC_TILE_BYTES + slab * TC_SLAB_BYTES + box * box_rows * 128, map, slab * 64, row, bar);
+      }
+    }
+    if (!ok) {
+      // gave up: let the copies already issued land before the block's shared memory is given away
+      const uint64_t t0 = global_ns();
+      while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+  } else if (warp == 2) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc(TC_BM, TC_BN, false), idesc_pv = umma_idesc(TC_BM, TC_HD, true);
+      bool ok = true;
+      // S[i & 1] = Q K_i^T
+      auto issue_qk = [&](int i) {
+        const int slot = i & 1;
+        ok = mbar_wait(smem_u32(&sh.k_full[slot]), (uint32_t)(i >> 1) & 1u, abort_flag);
+        if (!ok) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t kt = k_s + slot * TC_TILE_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < TC_HD / 16; ++k16) {
+          // 16 dims = 32 bytes along the swizzled line; dims 64.. are the second slab
+          const uint32_t off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
+          umma_bf16(tmem_base + (uint32_t)(slot * TC_BN), umma_desc(q_s + off, 0), umma_desc(kt + off, 0), idesc_qk,
+                    k16 != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sh.k_empty[slot]));       // the K stage is free once these MMAs have read it
+        umma_commit(smem_u32(&sh.s_full[slot]));
+      };
+      issue_qk(0);
+      if (ok && n_blocks > 1) issue_qk(1);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int slot = j & 1;
+        ok = mbar_wait(smem_u32(&sh.p_full), (uint32_t)j & 1u, abort_flag);      // P_j written, S_j and O_{j-2} read
+        if (!ok) break;
+        ok = mbar_wait(smem_u32(&sh.v_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vt = v_s + slot * TC_TILE_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < TC_BN / 16; ++k16) {
+          // A: 16 keys along P's lines; B: 16 keys = two groups of 8 lines of V, both 64-dim slabs
+          const uint32_t a_off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
+          umma_bf16(tmem_base + (uint32_t)(2 * TC_BN + slot * TC_HD), umma_desc(p_s + a_off, 0),
+                    umma_desc(vt + k16 * 2048, TC_SLAB_BYTES), idesc_pv, k16 != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sh.v_empty[slot]));
+        umma_commit(smem_u32(&sh.o_full[slot]));
+        if (j + 2 < n_blocks) issue_qk(j + 2);
+      }
+    }
+  } else {
+    // ---------------- softmax: one row a thread ----------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int R = row0 + r;
+    const bool valid = r < n_rows;
+    const int pos_r = valid ? tok_pos[tok0 + R / G] : -1;
+    const int lo_r = (window > 0 && pos_r - window + 1 > 0) ? pos_r - window + 1 : 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t p_row = p_s + r * 128;
+    float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+    float o[TC_HD];
+#pragma unroll
+    for (int i = 0; i < TC_HD; ++i) o[i] = 0.f;
+    bool ok = true;
+    // o = o * corr + O buffer `slot`
+    auto add_block = [&](int slot, float corr) {
+      // chunks of 16 columns, the next one on its way while this one is added
+      const uint32_t a0 = lane_addr + (uint32_t)(2 * TC_BN + slot * TC_HD);
+      uint32_t va[16], vb[16];
+      tmem_ld16(a0, va);
+#pragma unroll
+      for (int c = 0; c < TC_HD / 16; c += 2) {
+        tmem_wait_ld();
+        tmem_ld16(a0 + (uint32_t)((c + 1) * 16), vb);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[c * 16 + i] = o[c * 16 + i] * corr + __uint_as_float(va[i]);
+        tmem_wait_ld();
+        if (c + 2 < TC_HD / 16) tmem_ld16(a0 + (uint32_t)((c + 2) * 16), va);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[(c + 1) * 16 + i] = o[(c + 1) * 16 + i] * corr + __uint_as_float(vb[i]);
+      }
+    };
+    // Iteration j: the maximum of block j, then block j-1's P V (it ran meanwhile) is added, then block
+    // j's probabilities.  One more iteration adds the last block.
+    for (int j = 0; j <= n_blocks; ++j) {
+      const int slot = j & 1;
+      const int key0 = key_begin + j * TC_BN;
+      const bool all_visible = key0 >= lo_r && key0 + TC_BN - 1 <= pos_r;
+      const uint32_t s_addr = lane_addr + (uint32_t)(slot * TC_BN);
+      float msafe = 0.f, corr = 1.f, m_new = m;
+      if (j < n_blocks) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.s_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag) ? 1 : 0);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // pass 1: the row's maximum over the block (four running maxima: short dependency chains)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        uint32_t va[16], vb[16];
+        auto take = [&](const uint32_t (&v)[16], int c) {
+          if (all_visible) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int key = key0 + c * 16 + i;
+              if (key >= lo_r && key <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+            }
+          }
+        };
+        tmem_ld16(s_addr, va);
+#pragma unroll 1
+        for (int c = 0; c < TC_BN / 16; c += 2) {
+          tmem_wait_ld();
+          tmem_ld16(s_addr + (uint32_t)((c + 1) * 16), vb);
+          take(va, c);
+          tmem_wait_ld();
+          if (c + 2 < TC_BN / 16) tmem_ld16(s_addr + (uint32_t)((c + 2) * 16), va);
+          take(vb, c + 1);
+        }
+        // the scale is positive: the maximum of the scaled scores
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        m_new = fmaxf(m, mx);
+        msafe = m_new == -INFINITY ? 0.f : m_new;
+        corr = ex2(m - msafe);              // m = -inf: 0
+      }
+      if (j > 0) {
+        // block j-1: once its P V is done, P's tile is free as well
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full[slot ^ 1]), (uint32_t)((j - 1) >> 1) & 1u, abort_flag) ? 1 : 0);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        add_block(slot ^ 1, corr_prev);
+      }
+      if (j == n_blocks) break;
+      // pass 2: probabilities, their sum, P as bfloat16 into the swizzled tile; 32 keys at a time, so
+      // that the special-function unit has a long run of exponentials between two waits
+      float sum2[2] = {0.f, 0.f};
+      {
+        uint32_t va[32], vb[32];
+        auto take = [&](const uint32_t (&v)[32], int c) {        // keys c*32 .. c*32+31
+          uint32_t pk[16];
+          if (all_visible) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
+              const float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
+              sum2[0] += p0;
+              sum2[1] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const int key = key0 + c * 32 + i;
+              float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
+              float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
+              if (key < lo_r || key > pos_r) p0 = 0.f;
+              if (key + 1 < lo_r || key + 1 > pos_r) p1 = 0.f;
+              sum2[0] += p0;
+              sum2[1] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          }
+          // four 16-byte chunks of the row's line in the 64-key slab c >> 1
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const int chunk = (c & 1) * 4 + h;
+            const uint32_t dst = p_row + (c >> 1) * TC_SLAB_BYTES + ((chunk ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[h * 4]), "r"(pk[h * 4 + 1]),
+                         "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
+          }
+        };
+        tmem_ld32(s_addr, va);
+#pragma unroll 1
+        for (int c = 0; c < TC_BN / 32; c += 2) {
+          tmem_wait_ld();
+          tmem_ld32(s_addr + (uint32_t)((c + 1) * 32), vb);
+          take(va, c);
+          tmem_wait_ld();
+          if (c + 2 < TC_BN / 32) tmem_ld32(s_addr + (uint32_t)((c + 2) * 32), va);
+          take(vb, c + 1);
+        }
+      }
+      l = l * corr + (sum2[0] + sum2[1]);
+      m = m_new;
+      corr_prev = corr;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, before the MMA reads it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(&sh.p_full));
+    }
+    if (ok && valid) {
+      {
+        {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD;
+#pragma unroll
+          for (int i = 0; i < TC_HD; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
+            w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+            w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
+            w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + i) = w;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A cache [rows, 128] bfloat16 row-major, boxes of [box_rows, 64 dims], 128-byte swizzle
+int make_kv_map(CUtensorMap* map, const void* base, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return QB_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {TC_HD, rows};
+  const cuuint64_t strides[1] = {TC_HD * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : QB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// 1 if the tcgen05 kernel takes these shapes (head size 128, power-of-two pages that tile 128 keys).
+extern "C" int qb_attn_span_tc_supported(int nq, int nkv, int hd, int page_size) {
+  if (hd != TC_HD || nkv <= 0 || nq % nkv || nkv > 65535 || page_size <= 0) return 0;
+  if ((page_size & (page_size - 1)) != 0) return 0;
+  if (!(page_size <= TC_BN || page_size % TC_BN == 0)) return 0;
+  return encode_fn() != nullptr ? 1 : 0;
+}
+
+// Same arguments and tile list (128 rows a tile) as qb_attn_span.
+extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
+                               const int* block_table, int bt_stride, const int* tiles, int n_tiles, int nq, int nkv,
+                               int hd, int page_size, int num_pages, float scale, int window, int* status,
+                               cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (!qb_attn_span_tc_supported(nq, nkv, hd, page_size)) return QB_ERR_UNSUPPORTED;
+  if ((((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q | (uintptr_t)out) & 15) != 0) return QB_ERR_UNSUPPORTED;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap tm_k, tm_v;
+  memset(&tm_k, 0, sizeof(tm_k));
+  memset(&tm_v, 0, sizeof(tm_v));
+  const uint64_t rows = (uint64_t)num_pages * nkv * page_size;
+  const uint32_t box_rows = (uint32_t)(page_size < TC_BN ? page_size : TC_BN);
+  int rc = make_kv_map(&tm_k, k_cache, rows, box_rows);
+  if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, box_rows);
+  if (rc) return rc;
+  const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
+  cudaError_t err = cudaFuncSetAttribute(attn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return (int)err;
+  attn_span_tc_kernel<<<dim3(n_tiles, nkv), TC_THREADS, smem, stream>>>(
+      tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
+      page_size, num_pages, scale_log2, window, status);
+  QB_LAUNCH_CHECK();
+  return 0;
+}

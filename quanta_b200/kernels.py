@@ -192,6 +192,11 @@ def attn_decode_parts(nkv: int, max_len: int) -> int:
 ATTN_DECODE_MAX_GROUP = 64      # q heads per kv head that the decode kernel takes
 
 
+def attn_span_tc_supported(nq: int, nkv: int, hd: int, page_size: int) -> bool:
+    """Whether portions of these shapes run on the tcgen05 kernel (else on the mma.sync kernel)."""
+    return bool(lib().qb_attn_span_tc_supported(int(nq), int(nkv), int(hd), int(page_size)))
+
+
 def attn_span(q, k_cache, v_cache, out, tok_pos, block_table, tiles, scale: float, window: int, status) -> None:
     """bfloat16 tensor-core attention for prompt portions.  ``tiles`` int32 [n, 4]: request row, first
     token row of the portion, tokens in the portion, first flattened (token*G + head) row of the tile."""

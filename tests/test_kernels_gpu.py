@@ -151,11 +151,17 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
                                                    (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
                                                    (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50)])
-@pytest.mark.parametrize("impl", ["simt", "mma"])
-def test_paged_attention(dtype, nq, nkv, hd, page, window, impl):
+@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only"])
+def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
+    """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05 for
+    portions where the shapes allow); the same with the mma.sync kernels for every portion."""
     k = K()
-    if impl == "mma" and dtype != torch.bfloat16:
+    if impl != "simt" and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernels are the bfloat16 path")
+    if impl == "mma_only":
+        if not k.attn_span_tc_supported(nq, nkv, hd, page):
+            pytest.skip("these shapes run on the mma.sync kernels anyway")
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma")
     torch.manual_seed(1)
     # (first position, tokens): prompt portions beside decode tokens; a portion that starts past a split edge
     spans = [(0, 13), (70, 1), (33, 9), (129, 1), (250, 30), (600, 1)]
