@@ -1,0 +1,117 @@
+"""Times single kernels of the engine on synthetic inputs, one JSON line a case.
+
+    python bench_kernels.py attn_decode  --batch 4 --context 131072
+    python bench_kernels.py attn_span    --tokens 8192 --start 122880
+    python bench_kernels.py attn_sweep                      # the cases quoted under profiles/
+
+Shapes default to the M2-family attention (48 q heads, 8 kv heads of 128, pages of 16 tokens).  Caches
+are random, pages are dealt in a random order, every request of a decode case has the same context.
+Times are medians of CUDA-event intervals around one call, after warm-up; inputs are larger than L2
+except in the smallest cases, which say so by their size.  ``GB/s`` counts the keys and values read
+once; ``TFLOP/s`` counts 4 * head_dim flops per (query head, visible key).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from quanta_b200 import kernels as k
+
+DEV = "cuda:0"
+
+
+def timed(fn, n: int = 10, warm: int = 3) -> float:
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(n):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def attn_decode(batch: int, context: int, nq: int, nkv: int, hd: int, page: int) -> dict:
+    """One new token of ``batch`` requests against ``context`` cached keys each."""
+    max_pages = -(-context // page)
+    num_pages = batch * max_pages
+    table = torch.randperm(num_pages, dtype=torch.int32).view(batch, max_pages).to(DEV)
+    kc = torch.randn(num_pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.randn(num_pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    q = torch.randn(batch, nq, hd, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    tok_pos = torch.full((batch,), context - 1, dtype=torch.int32, device=DEV)
+    tok_req = torch.arange(batch, dtype=torch.int32, device=DEV)
+    dec = torch.arange(batch, dtype=torch.int32, device=DEV)
+    st = k.new_status(DEV)
+    n_parts = k.attn_decode_parts(nkv, context)
+    po = torch.empty(batch * nq * n_parts * hd, device=DEV)
+    pml = torch.empty(batch * nq * n_parts * 2, device=DEV)
+    ms = timed(lambda: k.attn_decode(q, kc, vc, out, po, pml, dec, batch, tok_pos, tok_req, table, hd ** -0.5, 0,
+                                     n_parts, st))
+    k.raise_on_status(st.cpu())
+    gb = batch * context * nkv * hd * 2 * 2 / 1e9
+    return {"kernel": "attn_decode+merge", "batch": batch, "context": context, "q_heads": nq, "kv_heads": nkv,
+            "head_dim": hd, "page": page, "ms": round(ms, 4), "kv_gb": round(gb, 3), "GB/s": round(gb / ms * 1e3, 1)}
+
+
+def attn_span(tokens: int, start: int, nq: int, nkv: int, hd: int, page: int) -> dict:
+    """A portion of ``tokens`` prompt tokens of one request whose cache already holds ``start`` keys."""
+    max_pages = -(-(start + tokens) // page)
+    table = torch.randperm(max_pages, dtype=torch.int32).view(1, -1).to(DEV)
+    kc = torch.randn(max_pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.randn(max_pages, nkv, page, hd, device=DEV, dtype=torch.bfloat16)
+    q = torch.randn(tokens, nq, hd, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    tok_pos = torch.arange(start, start + tokens, dtype=torch.int32, device=DEV)
+    group = nq // nkv
+    rows = k.attn_span_rows(hd)
+    tiles = [[0, 0, tokens, r0] for r0 in range(0, tokens * group, rows)]
+    tiles.reverse()                       # the tiles that read the most keys first, as the engine orders them
+    tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    st = k.new_status(DEV)
+    ms = timed(lambda: k.attn_span(q, kc, vc, out, tok_pos, table, tiles, hd ** -0.5, 0, st))
+    k.raise_on_status(st.cpu())
+    keys = sum(range(start + 1, start + tokens + 1))
+    flops = 4.0 * hd * nq * keys
+    return {"kernel": "attn_span", "tcgen05": bool(k.attn_span_tc_supported(nq, nkv, hd, page)), "tokens": tokens,
+            "start": start, "q_heads": nq, "kv_heads": nkv, "head_dim": hd, "page": page, "ms": round(ms, 4),
+            "TFLOP/s": round(flops / ms / 1e9, 1)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["attn_decode", "attn_span", "attn_sweep"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--start", type=int, default=0)
+    ap.add_argument("--q-heads", type=int, default=48)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page", type=int, default=16)
+    a = ap.parse_args()
+    shape = (a.q_heads, a.kv_heads, a.head_dim, a.page)
+    if a.what == "attn_decode":
+        print(json.dumps(attn_decode(a.batch, a.context, *shape)), flush=True)
+    elif a.what == "attn_span":
+        print(json.dumps(attn_span(a.tokens, a.start, *shape)), flush=True)
+    else:
+        for batch, context in [(1, 4096), (8, 4096), (64, 4096), (32, 16384), (8, 32768), (1, 131072), (4, 131072)]:
+            print(json.dumps(attn_decode(batch, context, *shape)), flush=True)
+            torch.cuda.empty_cache()
+        for tokens, start in [(2048, 0), (8192, 0), (8192, 122880)]:
+            print(json.dumps(attn_span(tokens, start, *shape)), flush=True)
+            torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -16,19 +16,34 @@ template <int NPL>   // experts per lane, E <= 32*NPL
 __global__ void router_topk_kernel(const float* __restrict__ logits, int n_partials,
                                    const float* __restrict__ bias, int* __restrict__ idx_out,
                                    float* __restrict__ w_out, int T, int E, int k, int renorm, float scale) {
-  // logits: [n_partials][T][E]; the partial products of the inner dimension are added in index order.
-  // One block per token: all threads add the partials (many independent loads in flight), then the
-  // first warp selects.
+  // logits: [n_partials][T][E], partial products of chunks of the inner dimension.  One block per token.
+  // The partials of an expert are added by `groups` threads, each a contiguous range in index order, and
+  // the groups' sums are then added in group order: the order depends on E and n_partials only, never on
+  // the step, and every thread has only a few independent loads to wait for.  The first warp selects.
   __shared__ float s_logit[1024];
+  __shared__ float s_part[1056];
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
   const size_t pstride = (size_t)T * E;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    float x = 0.f;
+  const int e_round = (E + 31) / 32 * 32;
+  const int groups = max(1, min((int)blockDim.x / e_round, n_partials));
+  const int per = (n_partials + groups - 1) / groups;
+  for (int i = threadIdx.x; i < groups * e_round; i += blockDim.x) {
+    const int g = i / e_round, e = i % e_round;
+    if (e < E) {
+      const int p_end = min(n_partials, (g + 1) * per);
+      float x = 0.f;
 #pragma unroll 8
-    for (int p = 0; p < n_partials; ++p) x += lg[p * pstride + e];
+      for (int p = g * per; p < p_end; ++p) x += lg[p * pstride + e];
+      s_part[i] = x;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float x = s_part[e];
+    for (int g = 1; g < groups; ++g) x += s_part[g * e_round + e];
     s_logit[e] = x;
   }
   __syncthreads();
@@ -97,7 +112,8 @@ extern "C" int qb_router_topk(const float* logits, int n_partials, const float* 
   if (T <= 0) return 0;
   if (k <= 0 || k > E || n_partials <= 0) return QB_ERR_BAD_ARG;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
-  const int warps = 4, blocks = T;
+  // many threads add the partials side by side; the selecting warp's arrays set the register need for large E
+  const int warps = E <= 256 ? 32 : 8, blocks = T;
 #define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale)
   if (E <= 32) QB_ROUTE(1);
   else if (E <= 64) QB_ROUTE(2);

@@ -116,6 +116,10 @@ class GQAttention(Mixer):
             if key not in ctx.work:
                 rows = kernels.attn_span_rows(self.hd)
                 tiles = [[r, t0, n, r0] for (r, t0, n) in spans for r0 in range(0, n * G, rows)]
+                # tiles that read the most keys first: the short ones fill the SMs at the end
+                after = ctx.host.get("req_len_after")
+                if after is not None:
+                    tiles.sort(key=lambda t: -(after[t[0]] - t[2] + min(t[2], (t[3] + rows) // G)))
                 ctx.work[key] = torch.tensor(tiles, dtype=torch.int32).to(q.device, non_blocking=True)
             kernels.attn_span(q, cache.k, cache.v, out, ctx.tok_pos, cache.block_table, ctx.work[key], self.scale,
                               window, ctx.status)
