@@ -19,6 +19,8 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from ..parts.base import KVCacheSpec
 
 
@@ -95,6 +97,7 @@ class CacheGroup:
     positions: list[int]                 # schedule positions whose K/V live in this group's pages
     pool: PagePool
     tables: dict = field(default_factory=dict)     # request id -> list of page ids (-1: given back)
+    arrays: dict = field(default_factory=dict)     # request id -> int32 array with the same entries (for packing a step)
 
     @property
     def window(self):
@@ -142,6 +145,7 @@ class CacheManager:
         self.requests[rid] = RequestRecord(slot)
         for g in self.groups:
             g.tables[rid] = []
+            g.arrays[rid] = np.full(16, -1, dtype=np.int32)
         return slot
 
     def length(self, rid) -> int:
@@ -179,7 +183,17 @@ class CacheManager:
                 raise OutOfPages(f"request {rid!r} needs {n} more page(s) to hold {new_length} tokens; "
                                  f"{g.pool.free_count} free of {g.pool.num_pages}")
         for g, n in zip(self.groups, needs):
-            g.tables[rid].extend(g.pool.take(n))
+            if n == 0:
+                continue
+            table, new = g.tables[rid], g.pool.take(n)
+            start = len(table)
+            table.extend(new)
+            arr = g.arrays[rid]
+            if len(table) > arr.size:
+                grown = np.full(max(2 * arr.size, len(table)), -1, dtype=np.int32)
+                grown[:start] = arr[:start]
+                arr = g.arrays[rid] = grown
+            arr[start:len(table)] = new
         rec.reserved = max(rec.reserved, new_length)
 
     def advance(self, rid, n_tokens: int) -> None:
@@ -198,16 +212,27 @@ class CacheManager:
                 g.pool.give_back(gone)
                 for i in range(first):
                     table[i] = -1
+                g.arrays[rid][:first] = -1
 
     def free(self, rid) -> None:
         rec = self.requests.pop(rid)
         for g in self.groups:
             g.pool.give_back([p for p in g.tables.pop(rid) if p >= 0])
+            g.arrays.pop(rid, None)
         self.slots.give_back(rec.slot)
 
     # ---- views for a step ---------------------------------------------------------------------------
     def block_table_rows(self, group: int, rids: list) -> list[list[int]]:
         return [self.groups[group].tables[r] for r in rids]
+
+    def block_table_matrix(self, group: int, rids: list, max_pages: int) -> np.ndarray:
+        """int32 ``[len(rids), max_pages]``: the requests' page ids, -1 where a request holds none."""
+        g = self.groups[group]
+        out = np.full((len(rids), max_pages), -1, dtype=np.int32)
+        for r, rid in enumerate(rids):
+            n = min(len(g.tables[rid]), max_pages)
+            out[r, :n] = g.arrays[rid][:n]
+        return out
 
     def stats(self) -> dict:
         return {"groups": [{"pages": g.pool.num_pages, "used": g.pool.used_count,
@@ -226,6 +251,9 @@ class CacheManager:
                 raise AssertionError("a held page is on the free list")
             if len(free) + len(held) != g.pool.num_pages or len(set(free)) != len(free):
                 raise AssertionError("a page is lost or listed free twice")
+            for rid, t in g.tables.items():
+                if g.arrays[rid][: len(t)].tolist() != t:
+                    raise AssertionError("the packed copy of a block table differs from the table")
         slots = [r.slot for r in self.requests.values()]
         if len(set(slots)) != len(slots) or len(slots) + self.slots.free_count != self.slots.num_slots:
             raise AssertionError("state slots are inconsistent")

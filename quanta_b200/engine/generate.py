@@ -16,7 +16,7 @@ import torch
 
 from ..sampling.sampler import Sampler
 from .model import Model, load_model
-from .scheduler import Request, SamplingParams, Scheduler
+from .scheduler import PlannedEntry, Request, SamplingParams, Scheduler
 from .step import Engine, StepEntry
 
 
@@ -55,6 +55,7 @@ class LLM:
         self.sampler = Sampler(self.engine.device)
         self.sched_opts = dict(max_step_tokens=max_step_tokens, prefill_chunk=prefill_chunk, max_position=max_position)
         self.default_eos = tuple(getattr(self.config, "eos_token_ids", ()) or ())
+        self.lookahead = True        # launch decode steps ahead of the host's read of the step before
         self.last_stats: dict = {}
         self.step_log: list = []     # per step of the last run: tokens fed, tokens sampled, bytes copied, host time
 
@@ -77,30 +78,95 @@ class LLM:
         outs = [r.generated for r in reqs]
         return outs[0] if single else outs
 
+    def _decode_ahead(self, sched: Scheduler, plan: list) -> list | None:
+        """The requests of the decode step that follows ``plan`` if that step can be launched before
+        ``plan``'s tokens are read: every running request decodes in ``plan``, nothing waits, no request
+        needs its earlier tokens on the host (penalties), pages are there without preempting anyone, and
+        the step replays a captured graph.  Requests that reach their length with ``plan`` are left out; a
+        request that stops on an end token in ``plan`` still runs in the step ahead, and its token there is
+        dropped."""
+        eng, mgr = self.engine, self.engine.manager
+        if not self.lookahead or sched.waiting or len(plan) != len(sched.running):
+            return None
+        if any(e.count != 1 or not e.samples for e in plan):
+            return None
+        ahead = []
+        for e in plan:
+            r, p = e.request, e.request.params
+            if p.repetition_penalty != 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0:
+                return None
+            if len(r.generated) + 1 >= p.max_new_tokens:
+                continue
+            if sched.max_position is not None and r.n_tokens + 1 >= sched.max_position:
+                continue
+            ahead.append(r)
+        if not ahead:
+            return None
+        wants = {r.rid: mgr.length(r.rid) + 1 for r in ahead}
+        if not mgr.can_reserve(wants) or not eng.decode_graph_ready(len(ahead), max(wants.values())):
+            return None
+        return ahead
+
     def run(self, requests: list) -> None:
-        """Drive the given requests to completion."""
+        """Drive the given requests to completion.  While the requests only decode, the next step is
+        launched with the ids still on the device, before the host reads them: planning, packing and the
+        launch of a step then run while the device works on the step before."""
         eng = self.engine
         sched = Scheduler(eng.manager, **self.sched_opts)
         for r in requests:
             sched.add(r)
         steps = 0
         self.step_log = []
-        while True:
-            plan = sched.plan()
-            if not plan:
-                break
-            entries = [StepEntry(e.request.rid, e.tokens, (e.count - 1,) if e.samples else ()) for e in plan]
+
+        def launch(plan, entries, samplers, drawn_before):
             logits = eng.step(entries)
-            samplers = [e.request for e in plan if e.samples]
-            sampled = {}
+            handle = None
             if samplers:
-                toks = self.sampler.sample(logits, samplers, status=eng.status)
-                sampled = {r.rid: t for r, t in zip(samplers, toks)}
-            sched.commit(plan, sampled)
-            steps += 1
-            self.step_log.append({"tokens": sum(e.count for e in plan), "sampled": len(samplers),
+                # a replayed decode step: the ids also go to the slots' table, for a step launched ahead
+                decode_only = eng.last_decode_slots is not None and len(samplers) == len(entries)
+                scatter = (eng.slot_token, eng.last_decode_slots) if decode_only else None
+                handle = self.sampler.sample_async(logits, samplers, eng.status, drawn_before=drawn_before,
+                                                   scatter=scatter)
+            self.step_log.append({"tokens": sum(len(e.tokens) for e in entries), "sampled": len(samplers),
                                   "h2d_bytes": eng.last_h2d_bytes, "d2h_bytes": 4 * (len(samplers) + 4),
-                                  "t_end": time.perf_counter()})
+                                  "t_end": None})
+            return handle, self.step_log[-1]
+
+        inflight = None           # (plan, requests that sample, handle, log entry) of the step not yet read
+        while True:
+            if inflight is None:
+                plan = sched.plan()
+                if not plan:
+                    break
+                entries = [StepEntry(e.request.rid, e.tokens, (e.count - 1,) if e.samples else ()) for e in plan]
+                samplers = [e.request for e in plan if e.samples]
+                handle, log = launch(plan, entries, samplers, 0)
+                inflight = (plan, samplers, handle, log)
+            plan, samplers, handle, log = inflight
+            ahead = self._decode_ahead(sched, plan) if handle is not None else None
+            nxt = None
+            if ahead:
+                a_entries = [StepEntry(r.rid, [0], (0,), from_device=True) for r in ahead]
+                a_handle, a_log = launch(None, a_entries, ahead, 1)
+                nxt = (ahead, a_handle, a_log)
+            sampled = {}
+            if handle is not None:
+                sampled = {r.rid: t for r, t in zip(samplers, handle.read())}
+            sched.commit(plan, sampled)
+            log["t_end"] = time.perf_counter()
+            steps += 1
+            inflight = None
+            if nxt is not None:
+                ahead, a_handle, a_log = nxt
+                alive = [r for r in ahead if r.status == "running"]
+                if alive:
+                    # the step ahead becomes the step in flight, for the requests that are still running
+                    a_plan = [PlannedEntry(r, r.n_tokens - 1, 1, True) for r in alive]
+                    inflight = (a_plan, ahead, a_handle, a_log)
+                else:
+                    a_handle.read()                 # nothing of it is kept; wait for it before going on
+                    a_log["t_end"] = time.perf_counter()
+                    steps += 1
         eng.check()
         self.last_stats = {"steps": steps, "cache": eng.manager.stats(),
                            "finish_reasons": {r.rid: r.finish_reason for r in requests},

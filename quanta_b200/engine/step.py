@@ -16,6 +16,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -28,6 +29,7 @@ class StepEntry:
     rid: object
     tokens: list
     want: tuple = ()          # indices into ``tokens`` whose logits are returned
+    from_device: bool = False  # a single decode token whose id is the one last sampled into the request's slot
 
 
 class _DecodeGraph:
@@ -40,6 +42,14 @@ class _DecodeGraph:
         self.host = None          # its pinned host twin
         self.logits = None
         self.launches = 0
+
+
+def _fill(host: torch.Tensor, pieces: list) -> None:
+    """Lay the step's arrays down one after the other in the pinned buffer."""
+    view, off = host.numpy(), 0
+    for p in pieces:
+        view[off: off + p.size] = p
+        off += p.size
 
 
 class Engine:
@@ -75,6 +85,10 @@ class Engine:
         self.use_graphs = bool(use_graphs) and all(getattr(p, "graph_safe", False) for p in model.parts())
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.graph_replays = 0
+        # the token last sampled for the request in each state slot: a decode step can take its ids from
+        # here, so that it can be launched before the host has read them
+        self.slot_token = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
+        self.last_decode_slots = None       # device view: the slots of the rows of the last graph step
 
     # ---- requests -----------------------------------------------------------------------------------
     def _admit(self, rid) -> None:
@@ -102,6 +116,7 @@ class Engine:
         slot are given back."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         mgr = self.manager
+        self.last_decode_slots = None
         seen = set()
         for e in entries:
             if e.rid in seen:
@@ -109,7 +124,9 @@ class Engine:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: an entry must bring at least one token")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if e.from_device and (len(e.tokens) != 1 or not self.decode_graph_ready(len(entries), 0, entries)):
+                raise ValueError(f"request {e.rid!r}: ids from the device need a captured decode step")
+            bad = [] if e.from_device else [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
             if bad:
                 raise ValueError(f"request {e.rid!r}: token id {bad[0]} outside the vocabulary of {self.vocab_size}")
             for w in e.want:
@@ -142,7 +159,7 @@ class Engine:
 
     # ---- packing the step's integers ---------------------------------------------------------------------
     def _pack(self, entries: list[StepEntry], max_pages: int) -> tuple[list, dict]:
-        """The step's integer arrays as python lists, in the fixed order of the device buffer."""
+        """The step's integer arrays (int32 numpy), in the fixed order of the device buffer."""
         mgr = self.manager
         rids = [e.rid for e in entries]
         R = len(entries)
@@ -159,19 +176,13 @@ class Engine:
             req_start.append(row0 + n)
             req_len_after.append(base + n)
             req_slot.append(mgr.slot(e.rid))
-        tables = []
-        for g in range(len(mgr.groups)):
-            flat = []
-            for row in mgr.block_table_rows(g, rids):
-                flat.extend(row[:max_pages])
-                flat.extend([-1] * (max_pages - len(row[:max_pages])))
-            tables.append(flat)
+        tables = [mgr.block_table_matrix(g, rids, max_pages).reshape(-1) for g in range(len(mgr.groups))]
         positions = tok_pos if self.n_axes == 1 else [p for p in tok_pos for _ in range(self.n_axes)]
         dec_rows = [req_start[r] for r in range(R) if req_start[r + 1] - req_start[r] == 1]
         spans = [(r, req_start[r], req_start[r + 1] - req_start[r]) for r in range(R)
                  if req_start[r + 1] - req_start[r] > 1]
-        pieces = [token_ids, tok_pos, tok_req, positions, req_start, req_len_after, req_slot, want_rows, dec_rows,
-                  *tables]
+        pieces = [np.asarray(p, dtype=np.int32) for p in (token_ids, tok_pos, tok_req, positions, req_start,
+                                                          req_len_after, req_slot, want_rows, dec_rows)] + tables
         info = {"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot, "spans": spans,
                 "n_dec": len(dec_rows), "n_want": len(want_rows)}
         return pieces, info
@@ -209,10 +220,10 @@ class Engine:
         max_len_after = max(mgr.length(e.rid) + len(e.tokens) for e in entries)
         max_pages = -(-max_len_after // ps)
         pieces, info = self._pack(entries, max_pages)
-        sizes = [len(p) for p in pieces]
+        sizes = [int(p.size) for p in pieces]
         total = sum(sizes)
         host = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=True)
-        host[:total] = torch.tensor([x for p in pieces for x in p], dtype=torch.int32)
+        _fill(host, pieces)
         dev = host.to(self.device, non_blocking=True)
         self.last_h2d_bytes = total * 4
         d_ids, d_want, ctx, caches = self._context(dev, sizes, R, T, max_pages, info, max_len_after,
@@ -220,13 +231,28 @@ class Engine:
         return self.model.forward(d_ids, ctx, caches, self.state, d_want if info["n_want"] else None)
 
     # ---- decoding through a captured graph ----------------------------------------------------------------------
+    @staticmethod
+    def _bucket(max_len_after: int) -> int:
+        bucket = 512
+        while bucket < max_len_after:
+            bucket *= 2
+        return bucket
+
+    def decode_graph_ready(self, batch: int, max_len_after: int, entries=None) -> bool:
+        """Whether a decode step of ``batch`` requests, the longest ``max_len_after`` tokens afterwards,
+        replays a captured graph (else it runs eagerly and is captured at its second use)."""
+        if not self.use_graphs:
+            return False
+        if entries is not None:
+            max_len_after = max(self.manager.length(e.rid) + 1 for e in entries if self.manager.has(e.rid))
+        g = self._graphs.get((batch, self._bucket(max_len_after)))
+        return g is not None and g.graph is not None
+
     def _run_decode(self, entries: list[StepEntry]) -> torch.Tensor | None:
         mgr, ps = self.manager, self.page_size
         B = len(entries)
         max_len_after = max(mgr.length(e.rid) + 1 for e in entries)
-        bucket = 512
-        while bucket < max_len_after:
-            bucket *= 2
+        bucket = self._bucket(max_len_after)
         key = (B, bucket)
         g = self._graphs.setdefault(key, _DecodeGraph())
         if g.graph is None and g.seen < 1:
@@ -236,16 +262,26 @@ class Engine:
         # every row's logits are computed inside the graph; the wanted ones are picked afterwards
         full = [StepEntry(e.rid, e.tokens, (0,)) for e in entries]
         pieces, info = self._pack(full, max_pages)
-        sizes = [len(p) for p in pieces]
+        sizes = [int(p.size) for p in pieces]
         total = sum(sizes)
         if g.graph is None:
             g.dev = torch.empty(total, dtype=torch.int32, device=self.device)
         # a fresh pinned buffer every step: the host may run ahead of the device, and the pinned
         # allocator does not hand a block out again before the copy that reads it is done
         host = torch.empty(total, dtype=torch.int32, pin_memory=True)
-        host.copy_(torch.tensor([x for p in pieces for x in p], dtype=torch.int32))
+        _fill(host, pieces)
         g.dev.copy_(host, non_blocking=True)
         self.last_h2d_bytes = total * 4
+        slots_at = sum(sizes[:6])            # the req_slot piece
+        self.last_decode_slots = g.dev[slots_at: slots_at + B]
+        if any(e.from_device for e in entries):
+            # ids sampled by the step before, still on the device (rows that brought an id keep it)
+            ids = torch.index_select(self.slot_token, 0, self.last_decode_slots)
+            if all(e.from_device for e in entries):
+                g.dev[:B].copy_(ids)
+            else:
+                mask = torch.tensor([e.from_device for e in entries], device=self.device)
+                g.dev[:B].copy_(torch.where(mask, ids, g.dev[:B]))
         if g.graph is None:
             d_ids, d_want, ctx, caches = self._context(g.dev, sizes, B, B, max_pages, info, bucket, 1, with_host=False)
             torch.cuda.synchronize()

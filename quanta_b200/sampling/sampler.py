@@ -15,6 +15,21 @@ import torch
 from .. import kernels
 
 
+class Sampled:
+    """The ids a step sampled, on their way to the host: ``read()`` waits for this step's copy only, not
+    for work queued on the device after it."""
+
+    def __init__(self, host: torch.Tensor, n: int, event, status: torch.Tensor | None):
+        self.host, self.n, self.event, self.status = host, n, event, status
+
+    def read(self) -> list[int]:
+        self.event.synchronize()
+        if self.status is not None and int(self.host[self.n]):
+            self.status.zero_()
+            kernels.raise_on_status(self.host[self.n:])
+        return [int(t) for t in self.host[: self.n]]
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
@@ -23,6 +38,14 @@ class Sampler:
         """``logits`` [n, vocab] float32 on the device, ``requests[i]`` has ``.params`` and
         ``.generated``.  Returns n token ids (host).  If ``status`` is given its words are read in the
         same copy and a device-side refusal raises."""
+        return self.sample_async(logits, requests, status).read()
+
+    def sample_async(self, logits: torch.Tensor, requests: list, status: torch.Tensor | None = None, *,
+                     drawn_before: int = 0, scatter=None) -> Sampled:
+        """Launch the sampling and the copy of the ids to the host; ``read()`` of the result gives them.
+        ``drawn_before``: tokens each request has sampled that are not in ``.generated`` yet (their draw
+        numbers are taken).  ``scatter``: ``(table, rows)`` device tensors: ``table[rows[i]] = id i`` as
+        well, for a step that takes its ids from the device."""
         n, V = logits.shape
         if n != len(requests):
             raise ValueError(f"{n} logits rows for {len(requests)} requests")
@@ -36,7 +59,7 @@ class Sampler:
             lo, hi = seed & 0xFFFFFFFF, seed >> 32
             fl += [float(p.temperature), float(p.top_p), float(p.min_p), 0.0]
             il += [int(p.top_k), lo - (1 << 32) if lo >= (1 << 31) else lo, hi - (1 << 32) if hi >= (1 << 31) else hi,
-                   len(r.generated)]
+                   len(r.generated) + drawn_before]
             pl += [float(p.repetition_penalty), float(p.frequency_penalty), float(p.presence_penalty)]
             if p.repetition_penalty != 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0:
                 penalised = True
@@ -55,10 +78,13 @@ class Sampler:
                                     torch.tensor(pl, dtype=torch.float32).to(dev))
         out = torch.empty(n + (4 if status is not None else 0), dtype=torch.int32, device=dev)
         kernels.sample_rows(logits.contiguous(), fparams, iparams, out[:n])
+        if scatter is not None:
+            table, rows = scatter
+            table.index_copy_(0, rows.long(), out[:n])
         if status is not None:
             out[n:].copy_(status)
-        host = out.cpu()
-        if status is not None and int(host[n]):
-            status.zero_()
-            kernels.raise_on_status(host[n:])
-        return [int(t) for t in host[:n]]
+        host = torch.empty(out.shape, dtype=torch.int32, pin_memory=True)
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return Sampled(host, n, event, status)

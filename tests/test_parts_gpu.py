@@ -395,6 +395,40 @@ def test_eos_and_few_pages(model_dirs, plain_models):
     assert cut == want[0][: want[0].index(stop)]
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16")])
+def test_steps_launched_ahead_give_the_same_tokens(model_dirs, name, dtype):
+    """Decode steps are launched before the host has read the tokens of the step before (their ids stay on
+    the device).  With that switched off the same tokens must come out: greedy and sampled, with requests
+    of different lengths, with a request that stops on an end token in the middle (its token of the step
+    ahead is dropped) and with penalties (which need the tokens on the host: no step ahead then)."""
+    from quanta_b200.engine.generate import LLM
+    from quanta_b200.engine.scheduler import SamplingParams
+    vocab = TINY[name]["vocab_size"]
+    prompts = [H.random_tokens(5 + 3 * i, vocab, 300 + i) for i in range(4)]
+    llm = LLM(model_dirs[name], dtype=dtype, page_size=4, num_pages=96, max_requests=4, prefill_chunk=8)
+
+    def both(params):
+        llm.lookahead = True
+        ahead = llm.generate(prompts, params)
+        replays = llm.engine.graph_replays
+        log = list(llm.step_log)
+        llm.lookahead = False
+        plain_order = llm.generate(prompts, params)
+        assert ahead == plain_order
+        return ahead, log, replays
+
+    lengths = [SamplingParams(max_new_tokens=n, temperature=0.0) for n in (40, 7, 23, 31)]
+    greedy, log, _ = both(lengths)
+    assert [len(g) for g in greedy] == [40, 7, 23, 31]
+    assert sum(e["sampled"] for e in log) >= 40 + 7 + 23 + 31          # steps ahead may sample a token that is dropped
+    stop = greedy[0][17]
+    cut, _, _ = both([SamplingParams(max_new_tokens=40, temperature=0.0, eos_token_ids=(stop,))] + lengths[1:])
+    assert cut[0] == greedy[0][: greedy[0].index(stop)] and cut[1:] == greedy[1:]
+    sampled, _, _ = both([SamplingParams(max_new_tokens=20, temperature=0.9, top_k=50, seed=7 + i) for i in range(4)])
+    assert len({tuple(x) for x in sampled}) == 4
+    both([SamplingParams(max_new_tokens=12, temperature=0.7, seed=3, repetition_penalty=1.2, presence_penalty=0.1)] * 4)
+
+
 def test_command_line(model_dirs):
     cmd = [sys.executable, "-m", "quanta_b200", "generate", "--model", str(model_dirs["A"]), "--dtype", "float32",
            "--prompt-ids", "5,17,3", "--max-new-tokens", "4", "--block-size", "4", "--num-pages", "16", "--eos-id", "600"]
