@@ -115,7 +115,7 @@ class LLM:
         sched = Scheduler(eng.manager, **self.sched_opts)
         for r in requests:
             sched.add(r)
-        steps = 0
+        steps = steps_ahead = 0
         self.step_log = []
 
         def launch(plan, entries, samplers, drawn_before):
@@ -149,6 +149,7 @@ class LLM:
                 a_entries = [StepEntry(r.rid, [0], (0,), from_device=True) for r in ahead]
                 a_handle, a_log = launch(None, a_entries, ahead, 1)
                 nxt = (ahead, a_handle, a_log)
+                steps_ahead += 1
             sampled = {}
             if handle is not None:
                 sampled = {r.rid: t for r, t in zip(samplers, handle.read())}
@@ -168,7 +169,7 @@ class LLM:
                     a_log["t_end"] = time.perf_counter()
                     steps += 1
         eng.check()
-        self.last_stats = {"steps": steps, "cache": eng.manager.stats(),
+        self.last_stats = {"steps": steps, "steps_ahead": steps_ahead, "cache": eng.manager.stats(),
                            "finish_reasons": {r.rid: r.finish_reason for r in requests},
                            "preemptions": sum(r.preemptions for r in requests)}
 

@@ -410,23 +410,25 @@ def test_steps_launched_ahead_give_the_same_tokens(model_dirs, name, dtype):
     def both(params):
         llm.lookahead = True
         ahead = llm.generate(prompts, params)
-        replays = llm.engine.graph_replays
+        n_ahead = llm.last_stats["steps_ahead"]
         log = list(llm.step_log)
         llm.lookahead = False
         plain_order = llm.generate(prompts, params)
-        assert ahead == plain_order
-        return ahead, log, replays
+        assert ahead == plain_order and llm.last_stats["steps_ahead"] == 0
+        return ahead, log, n_ahead
 
     lengths = [SamplingParams(max_new_tokens=n, temperature=0.0) for n in (40, 7, 23, 31)]
-    greedy, log, _ = both(lengths)
-    assert [len(g) for g in greedy] == [40, 7, 23, 31]
+    greedy, log, n_ahead = both(lengths)
+    assert [len(g) for g in greedy] == [40, 7, 23, 31] and n_ahead >= 20
     assert sum(e["sampled"] for e in log) >= 40 + 7 + 23 + 31          # steps ahead may sample a token that is dropped
     stop = greedy[0][17]
     cut, _, _ = both([SamplingParams(max_new_tokens=40, temperature=0.0, eos_token_ids=(stop,))] + lengths[1:])
     assert cut[0] == greedy[0][: greedy[0].index(stop)] and cut[1:] == greedy[1:]
     sampled, _, _ = both([SamplingParams(max_new_tokens=20, temperature=0.9, top_k=50, seed=7 + i) for i in range(4)])
     assert len({tuple(x) for x in sampled}) == 4
-    both([SamplingParams(max_new_tokens=12, temperature=0.7, seed=3, repetition_penalty=1.2, presence_penalty=0.1)] * 4)
+    _, _, n_ahead = both([SamplingParams(max_new_tokens=12, temperature=0.7, seed=3, repetition_penalty=1.2,
+                                         presence_penalty=0.1)] * 4)
+    assert n_ahead == 0
 
 
 def test_command_line(model_dirs):
