@@ -73,7 +73,7 @@ def attn_span(tokens: int, start: int, nq: int, nkv: int, hd: int, page: int) ->
     out = torch.empty_like(q)
     tok_pos = torch.arange(start, start + tokens, dtype=torch.int32, device=DEV)
     group = nq // nkv
-    rows = k.attn_span_rows(hd)
+    rows = k.attn_span_rows(hd, nq, nkv, page)
     tiles = [[0, 0, tokens, r0] for r0 in range(0, tokens * group, rows)]
     tiles.reverse()                       # the tiles that read the most keys first, as the engine orders them
     tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)

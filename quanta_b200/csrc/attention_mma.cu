@@ -1049,11 +1049,21 @@ int set_smem(Kern kern, size_t smem) {
 
 }  // namespace
 
-// Query rows (token x head of the group) per tile of the span kernel, for a head size.
-extern "C" int qb_attn_span_rows(int hd) { return hd <= 128 ? 128 : 64; }
-
-// the tcgen05 kernel for the shapes it takes (attention_tc.cu)
+// Query rows (token x head of the group) per tile of the span kernels, for the shapes of a layer
+// (nq <= 0: of the mma.sync kernel alone).
 extern "C" int qb_attn_span_tc_supported(int nq, int nkv, int hd, int page_size);
+extern "C" int qb_attn_span_tc_rows(void);
+static bool span_uses_tc(int nq, int nkv, int hd, int page_size) {
+  const char* want = getenv("QUANTA_B200_SPAN_KERNEL");
+  const bool force_mma = want != nullptr && strcmp(want, "mma") == 0;
+  return !force_mma && nq > 0 && qb_attn_span_tc_supported(nq, nkv, hd, page_size);
+}
+extern "C" int qb_attn_span_rows(int hd, int nq, int nkv, int page_size) {
+  if (span_uses_tc(nq, nkv, hd, page_size)) return qb_attn_span_tc_rows();
+  return hd <= 128 ? 128 : 64;
+}
+
+// the tcgen05 kernels for the shapes they take (attention_tc.cu)
 extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
                                const int* block_table, int bt_stride, const int* tiles, int n_tiles, int nq, int nkv,
                                int hd, int page_size, int num_pages, float scale, int window, int* status,
@@ -1066,14 +1076,9 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
                             cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (hd % 16 || hd > 256 || hd <= 0 || nq % nkv || nkv > 65535) return QB_ERR_UNSUPPORTED;
-  {
-    const char* want = getenv("QUANTA_B200_SPAN_KERNEL");
-    const bool force_mma = want != nullptr && strcmp(want, "mma") == 0;
-    if (!force_mma && qb_attn_span_tc_supported(nq, nkv, hd, page_size) &&
-        (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)q | (uintptr_t)out) & 15) == 0)
-      return qb_attn_span_tc(q, k_cache, v_cache, out, tok_pos, block_table, bt_stride, tiles, n_tiles, nq, nkv, hd,
-                             page_size, num_pages, scale, window, status, stream);
-  }
+  if (span_uses_tc(nq, nkv, hd, page_size))
+    return qb_attn_span_tc(q, k_cache, v_cache, out, tok_pos, block_table, bt_stride, tiles, n_tiles, nq, nkv, hd,
+                           page_size, num_pages, scale, window, status, stream);
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_tiles, nkv);
   const bool pow2 = (page_size & (page_size - 1)) == 0;

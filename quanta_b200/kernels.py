@@ -176,9 +176,9 @@ def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table
         _p(status), _stream()), "paged_attention_simt")
 
 
-def attn_span_rows(hd: int) -> int:
-    """Query rows (token x head-of-group) per tile of the span kernel for a head size."""
-    return int(lib().qb_attn_span_rows(int(hd)))
+def attn_span_rows(hd: int, nq: int, nkv: int, page_size: int) -> int:
+    """Query rows (token x head-of-group) per tile of the kernel that runs portions of these shapes."""
+    return int(lib().qb_attn_span_rows(int(hd), int(nq), int(nkv), int(page_size)))
 
 
 def attn_decode_parts(nkv: int, max_len: int) -> int:

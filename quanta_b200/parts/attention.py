@@ -112,9 +112,9 @@ class GQAttention(Mixer):
             kernels.attn_decode(q, cache.k, cache.v, out, part_o, part_ml, dec_tok, n_dec, ctx.tok_pos, ctx.tok_req,
                                 cache.block_table, self.scale, window, n_parts, ctx.status)
         if spans:
-            key = ("span_tiles", G, self.hd)
+            key = ("span_tiles", G, self.hd, kernels.attn_span_rows(self.hd, self.nq, self.nkv, cache.page_size))
             if key not in ctx.work:
-                rows = kernels.attn_span_rows(self.hd)
+                rows = kernels.attn_span_rows(self.hd, self.nq, self.nkv, cache.page_size)
                 tiles = [[r, t0, n, r0] for (r, t0, n) in spans for r0 in range(0, n * G, rows)]
                 # tiles that read the most keys first: the short ones fill the SMs at the end
                 after = ctx.host.get("req_len_after")

@@ -151,17 +151,18 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
                                                    (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
                                                    (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50)])
-@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only"])
+@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only", "tc_one_tile"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
-    """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05 for
-    portions where the shapes allow); the same with the mma.sync kernels for every portion."""
+    """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05, two
+    query tiles a block, for portions where the shapes allow); the same with the mma.sync kernel for every
+    portion; and with the one-tile tcgen05 kernel."""
     k = K()
     if impl != "simt" and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernels are the bfloat16 path")
-    if impl == "mma_only":
+    if impl in ("mma_only", "tc_one_tile"):
         if not k.attn_span_tc_supported(nq, nkv, hd, page):
             pytest.skip("these shapes run on the mma.sync kernels anyway")
-        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma")
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc1")
     torch.manual_seed(1)
     # (first position, tokens): prompt portions beside decode tokens; a portion that starts past a split edge
     spans = [(0, 13), (70, 1), (33, 9), (129, 1), (250, 30), (600, 1)]
@@ -197,7 +198,7 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
             if n == 1 and G <= k.ATTN_DECODE_MAX_GROUP:      # larger groups: a single token is a portion of one
                 dec.append(row0)
             else:
-                tiles += [[r, row0, n, x] for x in range(0, n * G, k.attn_span_rows(hd))]
+                tiles += [[r, row0, n, x] for x in range(0, n * G, k.attn_span_rows(hd, nq, nkv, page))]
             row0 += n
         n_parts = k.attn_decode_parts(nkv, max(a + n for a, n in spans))
         po = torch.full((len(dec) * nq * n_parts * hd,), float("nan"), device=DEV)
