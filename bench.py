@@ -246,7 +246,7 @@ def run_ours(args) -> dict:
               "top_k": 8, "expert_width": 1536, "vocab": 200064, "global_batch": B, "seq_len": context,
               "prompt_len": prompt_len, "kv_block": page, "parallelism": "single GPU",
               "l2": "no flush: each step reads >20 GB of weights, inputs larger than L2"}
-    return {"metric": "decode tokens/s (batch 8, 2048-token prompts, context 4096)", "value": round(value, 1),
+    return {"metric": f"decode tokens/s (batch {B}, {prompt_len}-token prompts, context {context})", "value": round(value, 1),
             "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded uniform token ids, seeded random weights)",
