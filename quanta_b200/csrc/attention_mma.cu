@@ -964,15 +964,49 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   if (n <= 0) return;
   n = min(n, n_parts - 1);
   const int t = dec_tok[z];
-  float M = -INFINITY;
-  for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+  if (n > 64) {
+    // very many segments (few kv heads): one after the other
+    float M = -INFINITY;
+    for (int s = 0; s < n; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      float acc = 0.f, L = 0.f;
+      for (int s = 0; s < n; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        acc += f * part_o[(base + s) * hd + d];
+        L += f * part_ml[(base + s) * 2 + 1];
+      }
+      out[((size_t)t * nq + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    return;
+  }
+  // the segments' (max, sum) once into shared memory, all loads side by side; then their weights
+  __shared__ float s_f[64], s_l[64];
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    float ms[2], ls[2], M = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = lane + 32 * i;
+      ms[i] = s < n ? part_ml[(base + s) * 2] : -INFINITY;
+      ls[i] = s < n ? part_ml[(base + s) * 2 + 1] : 0.f;
+      M = fmaxf(M, ms[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      s_f[lane + 32 * i] = ms[i] == -INFINITY ? 0.f : exp2f(ms[i] - M);
+      s_l[lane + 32 * i] = ls[i];
+    }
+  }
+  __syncthreads();
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f, L = 0.f;
-    for (int s = 0; s < n; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-      acc += f * part_o[(base + s) * hd + d];
-      L += f * part_ml[(base + s) * 2 + 1];
+#pragma unroll 8
+    for (int s = 0; s < n; ++s) {         // in segment order
+      acc += s_f[s] * part_o[(base + s) * hd + d];
+      L += s_f[s] * s_l[s];
     }
     out[((size_t)t * nq + head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }

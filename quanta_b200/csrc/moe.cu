@@ -99,12 +99,12 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_parti
     sum += sc;
     if (lane == 0) {
       idx_out[(size_t)t * k + r] = bi;
-      w_out[(size_t)t * k + r] = sc;
+      s_part[r] = sc;               // the partial sums are done with: keep the chosen scores here
     }
   }
   __syncwarp();
   const float denom = (renorm && k > 1) ? sum + 1e-20f : 1.f;
-  for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = w_out[(size_t)t * k + r] / denom * scale;
+  for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = s_part[r] / denom * scale;
 }
 
 extern "C" int qb_router_topk(const float* logits, int n_partials, const float* bias, int* idx_out, float* w_out,
