@@ -231,6 +231,35 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
         assert torch.allclose(out.float().cpu(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("n_dec,nq,nkv,hd,page", [(300, 4, 2, 64, 16), (70, 6, 1, 128, 8), (530, 2, 2, 32, 4)])
+def test_decode_attention_many_tokens(n_dec, nq, nkv, hd, page):
+    """More single tokens than one launch of the decode kernel takes (their positions live in shared
+    memory), contexts from 1 to a few hundred keys, every request with pages of its own."""
+    k = K()
+    torch.manual_seed(n_dec)
+    g = torch.Generator().manual_seed(n_dec)
+    ctx_len = torch.randint(1, 400, (n_dec,), generator=g)
+    ctx_len[0], ctx_len[1], ctx_len[-1] = 1, 64, 65
+    max_pages = int(-(-ctx_len.max() // page))
+    num_pages = n_dec * max_pages
+    table = torch.randperm(num_pages, generator=g, dtype=torch.int64).to(torch.int32).view(n_dec, max_pages)
+    kc = torch.randn(num_pages, nkv, page, hd, device=DEV).bfloat16()
+    vc = torch.randn(num_pages, nkv, page, hd, device=DEV).bfloat16()
+    q = torch.randn(n_dec, nq, hd, device=DEV).bfloat16()
+    tok_pos = (ctx_len - 1).to(torch.int32)
+    tok_req = torch.arange(n_dec, dtype=torch.int32)
+    out = torch.full_like(q, float("nan"))
+    n_parts = k.attn_decode_parts(nkv, int(ctx_len.max()))
+    po = torch.full((n_dec * nq * n_parts * hd,), float("nan"), device=DEV)
+    pml = torch.full((n_dec * nq * n_parts * 2,), float("nan"), device=DEV)
+    st = k.new_status(DEV)
+    k.attn_decode(q, kc, vc, out, po, pml, torch.arange(n_dec, dtype=torch.int32, device=DEV), n_dec, tok_pos.to(DEV),
+                  tok_req.to(DEV), table.to(DEV), hd ** -0.5, 0, n_parts, st)
+    assert int(st[0]) == 0
+    want = attention_reference(q, kc, vc, table.tolist(), tok_pos, tok_req, hd ** -0.5, 0)
+    assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
 def test_gemm_nt_simt(a_dtype, b_dtype):
     M, N, K_ = 45, 257, 1003
