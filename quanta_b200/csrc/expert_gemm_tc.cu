@@ -347,7 +347,8 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)NT * EG_BK * 2;
   // Two blocks share an SM (shared memory is the limit), so that one block's prologue and epilogue run
   // under the other's main loop; each gets a ring of about 105 KB.
-  int stages = (int)((105 * 1024) / stage_bytes);
+  // a tile of 256 token rows has a block to itself on its SM (its two accumulators fill the TMEM)
+  int stages = (int)((size_t)(NT > 128 ? 200 * 1024 : 105 * 1024) / stage_bytes);
   if (stages > 8) stages = 8;
   const int k_blocks = (K + EG_BK - 1) / EG_BK;
   if (stages > k_blocks) stages = k_blocks;

@@ -9,6 +9,7 @@ launched.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -304,13 +305,18 @@ def moe_stream(mode: int, x, weights, out, sorted_pair, pair_w, plan, n_experts:
                                top_k, K, N, min(n_experts, n_pairs), int(max_rows), _stream()), "moe_stream")
 
 
-def expert_tile_rows(n_tokens: int) -> int:
+def expert_tile_rows(n_tokens: int, rows_per_expert: float = 0.0) -> int:
     """Token tile (the MMA's N) of the tcgen05 expert kernel for a step of ``n_tokens`` tokens: an expert
-    never receives more rows than there are tokens."""
+    never receives more rows than there are tokens; with some hundred rows an expert on average
+    (``rows_per_expert``) the products are compute bound and the largest tile reads the operands least
+    often."""
     for nt in (16, 32, 64):
         if n_tokens <= nt:
             return nt
-    return 128
+    big = int(os.environ.get("QUANTA_B200_EXPERT_TILE", "0"))
+    if big:
+        return big
+    return 256 if rows_per_expert >= 384 else 128
 
 
 def gather_rows(x, out, sorted_pair, top_k: int) -> None:

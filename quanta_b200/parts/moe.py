@@ -95,7 +95,7 @@ class SigmoidTopKExperts(FeedForward):
         idx, w = self.route(x)
         n_pairs = T * self.k
         path = self.path_for(x)
-        bm = kernels.expert_tile_rows(T) if path == "tc" else kernels.MOE_SIMT_BM
+        bm = kernels.expert_tile_rows(T, n_pairs / self.E) if path == "tc" else kernels.MOE_SIMT_BM
         plan_words, max_tiles = kernels.moe_plan_sizes(n_pairs, self.E, bm)
         ints = torch.empty(plan_words + n_pairs + 2 * max_tiles, dtype=torch.int32, device=dev)
         plan = ints[:plan_words]
