@@ -126,9 +126,12 @@ class Engine:
                 raise ValueError(f"request {e.rid!r}: an entry must bring at least one token")
             if e.from_device and (len(e.tokens) != 1 or not self.decode_graph_ready(len(entries), 0, entries)):
                 raise ValueError(f"request {e.rid!r}: ids from the device need a captured decode step")
-            bad = [] if e.from_device else [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
-            if bad:
-                raise ValueError(f"request {e.rid!r}: token id {bad[0]} outside the vocabulary of {self.vocab_size}")
+            if not e.from_device:
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                bad = ids[(ids < 0) | (ids >= self.vocab_size)]
+                if bad.size:
+                    raise ValueError(f"request {e.rid!r}: token id {int(bad[0])} outside the vocabulary of "
+                                     f"{self.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.rid!r}: wanted place {w} outside its {len(e.tokens)} tokens")
@@ -165,19 +168,21 @@ class Engine:
         R = len(entries)
         token_ids, tok_pos, tok_req, want_rows = [], [], [], []
         req_start, req_len_after, req_slot = [0], [], []
+        row0 = 0
         for r, e in enumerate(entries):
             base = mgr.length(e.rid)
-            row0 = len(token_ids)
             n = len(e.tokens)
-            token_ids.extend(int(t) for t in e.tokens)
-            tok_pos.extend(range(base, base + n))
-            tok_req.extend([r] * n)
+            token_ids.append(np.asarray(e.tokens, dtype=np.int32))
+            tok_pos.append(np.arange(base, base + n, dtype=np.int32))
+            tok_req.append(np.full(n, r, dtype=np.int32))
             want_rows.extend(row0 + int(w) for w in e.want)
-            req_start.append(row0 + n)
+            row0 += n
+            req_start.append(row0)
             req_len_after.append(base + n)
             req_slot.append(mgr.slot(e.rid))
+        token_ids, tok_pos, tok_req = np.concatenate(token_ids), np.concatenate(tok_pos), np.concatenate(tok_req)
         tables = [mgr.block_table_matrix(g, rids, max_pages).reshape(-1) for g in range(len(mgr.groups))]
-        positions = tok_pos if self.n_axes == 1 else [p for p in tok_pos for _ in range(self.n_axes)]
+        positions = tok_pos if self.n_axes == 1 else np.repeat(tok_pos, self.n_axes)
         dec_rows = [req_start[r] for r in range(R) if req_start[r + 1] - req_start[r] == 1]
         spans = [(r, req_start[r], req_start[r + 1] - req_start[r]) for r in range(R)
                  if req_start[r + 1] - req_start[r] > 1]
