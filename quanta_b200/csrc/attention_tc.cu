@@ -1,22 +1,14 @@
 // Paged causal attention for prompt portions on the 5th-generation tensor cores (head size 128).
 //
 // A block takes query rows of ONE request and ONE kv head, where a row is a (token, q head of the group)
-// pair, against the request's keys in blocks of 128.  Two kernels: one query tile of 128 rows a block
-// (described here), and two tiles a block (further down; the one that runs unless
-// QUANTA_B200_SPAN_KERNEL=tc1).
-//
-//   warp 0     : TMA producer of K blocks, warp 1: of V blocks (boxes of [rows of a page x 64 dims],
-//                128-byte swizzle, two-stage rings with mbarriers).
-//   warp 2     : MMA issuer (one thread).  S = Q K^T as eight tcgen05.mma of K = 16 (M = 128 rows,
-//                N = 128 keys, both operands K-major) into one of two S buffers in TMEM; O_blk = P V
-//                as eight more (N = 128 dims, V is the MN-major operand as it lies in the cache) into
-//                one of two O buffers in TMEM.  tcgen05.commit frees the stages and signals the readers.
-//   warps 3-6  : softmax.  A thread owns one row (one TMEM lane): it reads S with tcgen05.ld, keeps the
-//                running maximum and sum in float32 (exp2 domain), writes P as bfloat16 into the
-//                swizzled shared-memory tile the next MMA reads, and adds O_blk, rescaled, to the row's
-//                128 float32 accumulators in registers.  The S = Q K^T of the next block and the P V of
-//                the block before run while the threads work on a block: a thread takes the maximum of
-//                block j, adds the P V of block j-1, then writes the probabilities of block j.
+// pair, against the request's keys in blocks of 128: S = Q K^T and O += P V are tcgen05.mma (M = 128 rows,
+// N = 128, eight steps of K = 16 each; Q, K and P are K-major operands in shared memory with the 128-byte
+// swizzle, V is the MN-major operand exactly as it lies in the cache), S and O live in TMEM, and softmax
+// warps turn S into P between the two products (tcgen05.ld, float32 online softmax in the exp2 domain,
+// P as bfloat16 into the swizzled tile).  K and V come by TMA tensor loads, one box per page and 64-dim
+// slab.  Two kernels, described where they stand: two query tiles a block with O accumulated in
+// registers, and one query tile a block with O accumulated in TMEM (the one that runs unless
+// QUANTA_B200_SPAN_KERNEL=tc2).
 //
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
 // probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
@@ -35,7 +27,6 @@ namespace {
 constexpr int TC_BM = 128;           // query rows per block (UMMA M)
 constexpr int TC_BN = 128;           // keys per block
 constexpr int TC_HD = 128;           // head size
-constexpr int TC_THREADS = 7 * 32;
 constexpr int TC_MAX_PAGES = 2048;
 constexpr uint32_t TC_TILE_BYTES = TC_BM * TC_HD * 2;       // 32 KB: Q, P, and each K or V stage
 constexpr uint32_t TC_SLAB_BYTES = TC_BM * 128;             // one slab: 128 rows x 64 elements
@@ -146,339 +137,14 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
-}
-
-struct TcShared {
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full[2], p_full;
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-__global__ void __launch_bounds__(TC_THREADS, 1)
-attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
-                    const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
-                    const int* __restrict__ tiles, int nq, int nkv, int page_size, int num_pages,
-                    float scale_log2, int window, int* status) {
-  extern __shared__ unsigned char smem_dyn[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  const uint32_t q_s = smem_u32(base), p_s = q_s + TC_TILE_BYTES, k_s = p_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
-  __shared__ TcShared sh;
-  __shared__ int s_page[TC_MAX_PAGES];
-  volatile int* abort_flag = &sh.abort_flag;
-
-  const int* tile = tiles + 4 * blockIdx.x;
-  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
-  const int kvh = blockIdx.y, G = nq / nkv;
-  const int n_rows = min(TC_BM, n_tok * G - row0);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int* bt = block_table + (size_t)req * bt_stride;
-
-  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
-  const int key_end = tok_pos[last_tok];
-  const int p_first = tok_pos[first_tok];
-  const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;   // the lowest key any row reads
-  const int key_begin = lo_min / TC_BN * TC_BN;
-  const int n_blocks = (key_end - key_begin) / TC_BN + 1;
-
-  // Q rows into the swizzled tile (zero past the last row); the K and V rings start as zeros, so that
-  // rows no copy covers hold zeros or older keys, never anything that is not a number
-  for (int c = tid; c < TC_BM * (TC_HD / 8); c += TC_THREADS) {
-    const int r = c / (TC_HD / 8), ch = c % (TC_HD / 8);      // 16-byte chunk ch of row r
-    const int R = row0 + r;
-    const bool ok = r < n_rows;
-    const __nv_bfloat16* src = q;
-    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD + ch * 8;
-    cp_async16(q_s + (ch >> 3) * TC_SLAB_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), src, ok);
-  }
-  asm volatile("cp.async.commit_group;\n" ::);
-  for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TC_THREADS)
-    reinterpret_cast<uint4*>(base + 2 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
-  const int pi0 = key_begin / page_size;
-  const int n_pi = key_end / page_size - pi0 + 1;
-  const bool pages_in_smem = n_pi <= TC_MAX_PAGES;
-  if (pages_in_smem)
-    for (int i = tid; i < n_pi; i += TC_THREADS) s_page[i] = bt[pi0 + i];
-  if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&sh.k_full[s]), 1);
-      mbar_init(smem_u32(&sh.k_empty[s]), 1);
-      mbar_init(smem_u32(&sh.v_full[s]), 1);
-      mbar_init(smem_u32(&sh.v_empty[s]), 1);
-      mbar_init(smem_u32(&sh.s_full[s]), 1);
-      mbar_init(smem_u32(&sh.o_full[s]), 1);
-    }
-    mbar_init(smem_u32(&sh.p_full), 128);
-    sh.abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 2) {      // the whole TMEM: two S buffers and two O buffers of 128 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&sh.tmem_base)), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("cp.async.wait_group 0;\n" ::);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q and the zeros, before TMA and the MMAs
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = sh.tmem_base;
-
-  if (warp < 2) {
-    // ---------------- TMA producers: warp 0 streams K blocks, warp 1 V blocks ----------------
-    const CUtensorMap* map = warp == 0 ? &tm_k : &tm_v;
-    uint64_t* full = warp == 0 ? sh.k_full : sh.v_full;
-    uint64_t* empty = warp == 0 ? sh.k_empty : sh.v_empty;
-    const uint32_t ring = warp == 0 ? k_s : v_s;
-    const int box_rows = min(page_size, TC_BN);
-    bool ok = true;
-    for (int b = 0; b < n_blocks && ok; ++b) {
-      const int slot = b & 1;
-      const uint32_t ph = (uint32_t)(b >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
-      if (!ok) break;
-      const int key0 = key_begin + b * TC_BN;
-      const int n_keys = min(TC_BN, key_end - key0 + 1);
-      const int n_req = 2 * ((n_keys + box_rows - 1) / box_rows);      // boxes: pages with visible keys x two slabs
-      const uint32_t bar = smem_u32(&full[slot]);
-      // a page id outside the pool is recorded and its rows are not copied (the byte count must match);
-      // keys before every row's window are not fetched: their pages may have been given back already
-      int skipped = 0;
-      for (int i = lane; i < n_req; i += 32) {
-        const int key = key0 + (i >> 1) * box_rows;
-        if (key + box_rows - 1 < lo_min) { ++skipped; continue; }
-        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
-        if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++skipped; }
-      }
-      skipped = __reduce_add_sync(0xffffffffu, skipped);
-      if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_req - skipped) * (uint32_t)box_rows * 128u);
-      __syncwarp();
-      for (int i = lane; i < n_req; i += 32) {
-        const int slab = i & 1, box = i >> 1;
-        const int key = key0 + box * box_rows;
-        if (key + box_rows - 1 < lo_min) continue;
-        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
-        if (pg < 0 || pg >= num_pages) continue;
-        const int row = (pg * nkv + kvh) * page_size + key % page_size;
-        tma_load_box(ring + slot * TC_TILE_BYTES + slab * TC_SLAB_BYTES + box * box_rows * 128, map, slab * 64, row, bar);
-      }
-    }
-    if (!ok) {
-      // gave up: let the copies already issued land before the block's shared memory is given away
-      const uint64_t t0 = global_ns();
-      while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
-    }
-  } else if (warp == 2) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      const uint32_t idesc_qk = umma_idesc(TC_BM, TC_BN, false), idesc_pv = umma_idesc(TC_BM, TC_HD, true);
-      bool ok = true;
-      // S[i & 1] = Q K_i^T
-      auto issue_qk = [&](int i) {
-        const int slot = i & 1;
-        ok = mbar_wait(smem_u32(&sh.k_full[slot]), (uint32_t)(i >> 1) & 1u, abort_flag);
-        if (!ok) return;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kt = k_s + slot * TC_TILE_BYTES;
-#pragma unroll
-        for (int k16 = 0; k16 < TC_HD / 16; ++k16) {
-          // 16 dims = 32 bytes along the swizzled line; dims 64.. are the second slab
-          const uint32_t off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
-          umma_bf16(tmem_base + (uint32_t)(slot * TC_BN), umma_desc(q_s + off, 0), umma_desc(kt + off, 0), idesc_qk,
-                    k16 != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sh.k_empty[slot]));       // the K stage is free once these MMAs have read it
-        umma_commit(smem_u32(&sh.s_full[slot]));
-      };
-      issue_qk(0);
-      if (ok && n_blocks > 1) issue_qk(1);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int slot = j & 1;
-        ok = mbar_wait(smem_u32(&sh.p_full), (uint32_t)j & 1u, abort_flag);      // P_j written, S_j and O_{j-2} read
-        if (!ok) break;
-        ok = mbar_wait(smem_u32(&sh.v_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t vt = v_s + slot * TC_TILE_BYTES;
-#pragma unroll
-        for (int k16 = 0; k16 < TC_BN / 16; ++k16) {
-          // A: 16 keys along P's lines; B: 16 keys = two groups of 8 lines of V, both 64-dim slabs
-          const uint32_t a_off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
-          umma_bf16(tmem_base + (uint32_t)(2 * TC_BN + slot * TC_HD), umma_desc(p_s + a_off, 0),
-                    umma_desc(vt + k16 * 2048, TC_SLAB_BYTES), idesc_pv, k16 != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sh.v_empty[slot]));
-        umma_commit(smem_u32(&sh.o_full[slot]));
-        if (j + 2 < n_blocks) issue_qk(j + 2);
-      }
-    }
-  } else {
-    // ---------------- softmax: one row a thread ----------------
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const int R = row0 + r;
-    const bool valid = r < n_rows;
-    const int pos_r = valid ? tok_pos[tok0 + R / G] : -1;
-    const int lo_r = (window > 0 && pos_r - window + 1 > 0) ? pos_r - window + 1 : 0;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t p_row = p_s + r * 128;
-    float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-    float o[TC_HD];
-#pragma unroll
-    for (int i = 0; i < TC_HD; ++i) o[i] = 0.f;
-    bool ok = true;
-    // o = o * corr + O buffer `slot`
-    auto add_block = [&](int slot, float corr) {
-      // chunks of 16 columns, the next one on its way while this one is added
-      const uint32_t a0 = lane_addr + (uint32_t)(2 * TC_BN + slot * TC_HD);
-      uint32_t va[16], vb[16];
-      tmem_ld16(a0, va);
-#pragma unroll
-      for (int c = 0; c < TC_HD / 16; c += 2) {
-        tmem_wait_ld();
-        tmem_ld16(a0 + (uint32_t)((c + 1) * 16), vb);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[c * 16 + i] = o[c * 16 + i] * corr + __uint_as_float(va[i]);
-        tmem_wait_ld();
-        if (c + 2 < TC_HD / 16) tmem_ld16(a0 + (uint32_t)((c + 2) * 16), va);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[(c + 1) * 16 + i] = o[(c + 1) * 16 + i] * corr + __uint_as_float(vb[i]);
-      }
-    };
-    // Iteration j: the maximum of block j, then block j-1's P V (it ran meanwhile) is added, then block
-    // j's probabilities.  One more iteration adds the last block.
-    for (int j = 0; j <= n_blocks; ++j) {
-      const int slot = j & 1;
-      const int key0 = key_begin + j * TC_BN;
-      const bool all_visible = key0 >= lo_r && key0 + TC_BN - 1 <= pos_r;
-      const uint32_t s_addr = lane_addr + (uint32_t)(slot * TC_BN);
-      float msafe = 0.f, corr = 1.f, m_new = m;
-      if (j < n_blocks) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.s_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag) ? 1 : 0);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // pass 1: the row's maximum over the block (four running maxima: short dependency chains)
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        uint32_t va[16], vb[16];
-        auto take = [&](const uint32_t (&v)[16], int c) {
-          if (all_visible) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int key = key0 + c * 16 + i;
-              if (key >= lo_r && key <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-            }
-          }
-        };
-        tmem_ld16(s_addr, va);
-#pragma unroll 1
-        for (int c = 0; c < TC_BN / 16; c += 2) {
-          tmem_wait_ld();
-          tmem_ld16(s_addr + (uint32_t)((c + 1) * 16), vb);
-          take(va, c);
-          tmem_wait_ld();
-          if (c + 2 < TC_BN / 16) tmem_ld16(s_addr + (uint32_t)((c + 2) * 16), va);
-          take(vb, c + 1);
-        }
-        // the scale is positive: the maximum of the scaled scores
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-        m_new = fmaxf(m, mx);
-        msafe = m_new == -INFINITY ? 0.f : m_new;
-        corr = ex2(m - msafe);              // m = -inf: 0
-      }
-      if (j > 0) {
-        // block j-1: once its P V is done, P's tile is free as well
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full[slot ^ 1]), (uint32_t)((j - 1) >> 1) & 1u, abort_flag) ? 1 : 0);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        add_block(slot ^ 1, corr_prev);
-      }
-      if (j == n_blocks) break;
-      // pass 2: probabilities, their sum, P as bfloat16 into the swizzled tile; 32 keys at a time, so
-      // that the special-function unit has a long run of exponentials between two waits
-      float sum2[2] = {0.f, 0.f};
-      {
-        uint32_t va[32], vb[32];
-        auto take = [&](const uint32_t (&v)[32], int c) {        // keys c*32 .. c*32+31
-          uint32_t pk[16];
-          if (all_visible) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
-              const float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
-              sum2[0] += p0;
-              sum2[1] += p1;
-              pk[i >> 1] = pack_bf16(p0, p1);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const int key = key0 + c * 32 + i;
-              float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
-              float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
-              if (key < lo_r || key > pos_r) p0 = 0.f;
-              if (key + 1 < lo_r || key + 1 > pos_r) p1 = 0.f;
-              sum2[0] += p0;
-              sum2[1] += p1;
-              pk[i >> 1] = pack_bf16(p0, p1);
-            }
-          }
-          // four 16-byte chunks of the row's line in the 64-key slab c >> 1
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const int chunk = (c & 1) * 4 + h;
-            const uint32_t dst = p_row + (c >> 1) * TC_SLAB_BYTES + ((chunk ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[h * 4]), "r"(pk[h * 4 + 1]),
-                         "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
-          }
-        };
-        tmem_ld32(s_addr, va);
-#pragma unroll 1
-        for (int c = 0; c < TC_BN / 32; c += 2) {
-          tmem_wait_ld();
-          tmem_ld32(s_addr + (uint32_t)((c + 1) * 32), vb);
-          take(va, c);
-          tmem_wait_ld();
-          if (c + 2 < TC_BN / 32) tmem_ld32(s_addr + (uint32_t)((c + 2) * 32), va);
-          take(vb, c + 1);
-        }
-      }
-      l = l * corr + (sum2[0] + sum2[1]);
-      m = m_new;
-      corr_prev = corr;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, before the MMA reads it
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&sh.p_full));
-    }
-    if (ok && valid) {
-      {
-        {
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD;
-#pragma unroll
-          for (int i = 0; i < TC_HD; i += 8) {
-            uint4 w;
-            w.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
-            w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-            w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
-            w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-            *reinterpret_cast<uint4*>(dst + i) = w;
-          }
-        }
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-  }
-  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -838,6 +504,357 @@ attn_span_tc2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
 }
 
+// ------------------------------------------------------------------------------------------------
+// One query tile per block, O accumulated in TMEM, two softmax threads per row.
+//
+//   warp 0: TMA producer of K blocks, warp 1: of V blocks (two stages each), warp 2: MMA issuer,
+//   warps 3-10: softmax; warps 3-6 take keys 0..63 of a block, warps 7-10 keys 64..127, of the row that is
+//   their TMEM lane.  TMEM: two S buffers and ONE O of 128 columns that every P V adds to.
+//   The exponentials use a reference maximum that is only raised when the row maximum has grown by more
+//   than 2^8 since (then the row's O and sum are rescaled, each thread its 64 columns, after the P V
+//   before has finished); otherwise P V (j) needs nothing from the threads but P(j), and the threads
+//   never read O until the end.  Both threads of a row take the maximum over all 128 keys (the same
+//   decision without talking to each other) and the exponentials of their own 64.
+// ------------------------------------------------------------------------------------------------
+constexpr int TC3_THREADS = 11 * 32;
+constexpr float TC3_TAU = 8.0f;
+
+struct Tc3Shared {
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full, p_full, p_empty, fin;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+__global__ void __launch_bounds__(TC3_THREADS, 1)
+attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                     const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
+                     const int* __restrict__ tiles, int nq, int nkv, int page_size, int num_pages,
+                     float scale_log2, int window, int* status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_s = smem_u32(base), p_s = q_s + TC_TILE_BYTES, k_s = p_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
+  __shared__ Tc3Shared sh;
+  __shared__ int s_page[TC_MAX_PAGES];
+  __shared__ float s_l[2][TC_BM];
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int* tile = tiles + 4 * blockIdx.x;
+  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
+  const int kvh = blockIdx.y, G = nq / nkv;
+  const int n_rows = min(TC_BM, n_tok * G - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* bt = block_table + (size_t)req * bt_stride;
+
+  const int first_tok = tok0 + row0 / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
+  const int key_end = tok_pos[last_tok];
+  const int p_first = tok_pos[first_tok];
+  const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;   // the lowest key any row reads
+  const int key_begin = lo_min / TC_BN * TC_BN;
+  const int n_blocks = (key_end - key_begin) / TC_BN + 1;
+
+  for (int c = tid; c < TC_BM * (TC_HD / 8); c += TC3_THREADS) {
+    const int r = c / (TC_HD / 8), ch = c % (TC_HD / 8);      // 16-byte chunk ch of row r
+    const int R = row0 + r;
+    const bool ok = r < n_rows;
+    const __nv_bfloat16* src = q;
+    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD + ch * 8;
+    cp_async16(q_s + (ch >> 3) * TC_SLAB_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), src, ok);
+  }
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TC3_THREADS)
+    reinterpret_cast<uint4*>(base + 2 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
+  const int pi0 = key_begin / page_size;
+  const int n_pi = key_end / page_size - pi0 + 1;
+  const bool pages_in_smem = n_pi <= TC_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = tid; i < n_pi; i += TC3_THREADS) s_page[i] = bt[pi0 + i];
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&sh.k_full[s]), 1);
+      mbar_init(smem_u32(&sh.k_empty[s]), 1);
+      mbar_init(smem_u32(&sh.v_full[s]), 1);
+      mbar_init(smem_u32(&sh.v_empty[s]), 1);
+      mbar_init(smem_u32(&sh.s_full[s]), 1);
+    }
+    mbar_init(smem_u32(&sh.o_full), 1);
+    mbar_init(smem_u32(&sh.p_full), 256);
+    mbar_init(smem_u32(&sh.p_empty), 1);
+    mbar_init(smem_u32(&sh.fin), 256);
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {      // two S buffers and O: 384 columns, allocated as 512
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&sh.tmem_base)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q and the zeros, before TMA and the MMAs
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = sh.tmem_base;
+  const uint32_t o_col = 2 * TC_BN;
+
+  if (warp < 2) {
+    // ---------------- TMA producers: warp 0 streams K blocks, warp 1 V blocks ----------------
+    const CUtensorMap* map = warp == 0 ? &tm_k : &tm_v;
+    uint64_t* full = warp == 0 ? sh.k_full : sh.v_full;
+    uint64_t* empty = warp == 0 ? sh.k_empty : sh.v_empty;
+    const uint32_t ring = warp == 0 ? k_s : v_s;
+    const int box_rows = min(page_size, TC_BN);
+    bool ok = true;
+    for (int b = 0; b < n_blocks && ok; ++b) {
+      const int slot = b & 1;
+      const uint32_t ph = (uint32_t)(b >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), ph ^ 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      const int key0 = key_begin + b * TC_BN;
+      const int n_keys = min(TC_BN, key_end - key0 + 1);
+      const int n_req = 2 * ((n_keys + box_rows - 1) / box_rows);      // boxes: pages with visible keys x two slabs
+      const uint32_t bar = smem_u32(&full[slot]);
+      int skipped = 0;
+      for (int i = lane; i < n_req; i += 32) {
+        const int key = key0 + (i >> 1) * box_rows;
+        if (key + box_rows - 1 < lo_min) { ++skipped; continue; }
+        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+        if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++skipped; }
+      }
+      skipped = __reduce_add_sync(0xffffffffu, skipped);
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_req - skipped) * (uint32_t)box_rows * 128u);
+      __syncwarp();
+      for (int i = lane; i < n_req; i += 32) {
+        const int slab = i & 1, box = i >> 1;
+        const int key = key0 + box * box_rows;
+        if (key + box_rows - 1 < lo_min) continue;
+        const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
+        if (pg < 0 || pg >= num_pages) continue;
+        const int row = (pg * nkv + kvh) * page_size + key % page_size;
+        tma_load_box(ring + slot * TC_TILE_BYTES + slab * TC_SLAB_BYTES + box * box_rows * 128, map, slab * 64, row, bar);
+      }
+    }
+    if (!ok) {
+      const uint64_t t0 = global_ns();
+      while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+  } else if (warp == 2) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc(TC_BM, TC_BN, false), idesc_pv = umma_idesc(TC_BM, TC_HD, true);
+      bool ok = true;
+      auto issue_qk = [&](int i) {
+        const int slot = i & 1;
+        ok = mbar_wait(smem_u32(&sh.k_full[slot]), (uint32_t)(i >> 1) & 1u, abort_flag);
+        if (!ok) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t kt = k_s + slot * TC_TILE_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < TC_HD / 16; ++k16) {
+          const uint32_t off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
+          umma_bf16(tmem_base + (uint32_t)(slot * TC_BN), umma_desc(q_s + off, 0), umma_desc(kt + off, 0), idesc_qk,
+                    k16 != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sh.k_empty[slot]));
+        umma_commit(smem_u32(&sh.s_full[slot]));
+      };
+      issue_qk(0);
+      if (ok && n_blocks > 1) issue_qk(1);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int slot = j & 1;
+        ok = mbar_wait(smem_u32(&sh.p_full), (uint32_t)j & 1u, abort_flag);      // P(j) written, S(j) read, O rescaled if need be
+        if (!ok) break;
+        ok = mbar_wait(smem_u32(&sh.v_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vt = v_s + slot * TC_TILE_BYTES;
+#pragma unroll
+        for (int k16 = 0; k16 < TC_BN / 16; ++k16) {
+          const uint32_t a_off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
+          umma_bf16(tmem_base + o_col, umma_desc(p_s + a_off, 0), umma_desc(vt + k16 * 2048, TC_SLAB_BYTES), idesc_pv,
+                    (j | k16) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sh.v_empty[slot]));
+        umma_commit(smem_u32(&sh.p_empty));
+        umma_commit(smem_u32(&sh.o_full));
+        if (j + 2 < n_blocks) issue_qk(j + 2);
+      }
+    }
+  } else {
+    // ---------------- softmax: two threads a row, 64 keys of a block each ----------------
+    const int quad = warp & 3, half = (warp - 3) >> 2;
+    const int r = quad * 32 + lane;
+    const int R = row0 + r;
+    const bool valid = r < n_rows;
+    const int pos_r = valid ? tok_pos[tok0 + R / G] : -1;
+    const int lo_r = (window > 0 && pos_r - window + 1 > 0) ? pos_r - window + 1 : 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t o_addr = lane_addr + o_col + (uint32_t)(half * 64);       // this thread's 64 columns of O
+    const uint32_t p_row = p_s + half * TC_SLAB_BYTES + r * 128;             // its 64 keys are one slab of P
+    float m_true = -INFINITY, m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks; ++j) {
+      const int slot = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.s_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int key0 = key_begin + j * TC_BN;
+      const bool all_visible = key0 >= lo_r && key0 + TC_BN - 1 <= pos_r;
+      const uint32_t s_addr = lane_addr + (uint32_t)(slot * TC_BN);
+      // pass 1: the row's maximum over all 128 keys of the block (three-operand max, 32 keys a load)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      {
+        uint32_t va[32], vb[32];
+        auto take = [&](const uint32_t (&v)[32], int c) {
+          if (all_visible) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = key0 + c * 32 + i;
+              if (key >= lo_r && key <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+            }
+          }
+        };
+        tmem_ld32(s_addr, va);
+#pragma unroll 1
+        for (int c = 0; c < TC_BN / 32; c += 2) {
+          tmem_wait_ld();
+          tmem_ld32(s_addr + (uint32_t)((c + 1) * 32), vb);
+          take(va, c);
+          tmem_wait_ld();
+          if (c + 2 < TC_BN / 32) tmem_ld32(s_addr + (uint32_t)((c + 2) * 32), va);
+          take(vb, c + 1);
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      m_true = fmaxf(m_true, mx);
+      // raise the reference only when the maximum has grown a lot: O and the sum are rescaled then
+      const bool raise = m_true > m_ref + TC3_TAU;          // also true while the reference is -inf and a key is visible
+      if (__any_sync(0xffffffffu, raise && j > 0)) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (raise) {
+          const float f = ex2(m_ref - m_true);              // reference -inf: 0
+          l *= f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[16];
+            tmem_ld16(o_addr + (uint32_t)(c * 16), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st16(o_addr + (uint32_t)(c * 16), v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      if (raise) m_ref = m_true;
+      const float msafe = m_ref == -INFINITY ? 0.f : m_ref;
+      // P's tile is free once the P V of the block before has read it
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.p_empty), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
+        if (!ok) break;
+      }
+      // pass 2: the probabilities of this thread's 64 keys, as bfloat16 into its slab of P
+      float sum2[2] = {0.f, 0.f};
+      {
+        const int kbase = key0 + half * 64;
+        const bool vis = all_visible;
+        uint32_t va[32], vb[32];
+        auto take = [&](const uint32_t (&v)[32], int c) {        // keys kbase + c*32 .. +31
+          uint32_t pk[16];
+          if (vis) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
+              const float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
+              sum2[0] += p0;
+              sum2[1] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const int key = kbase + c * 32 + i;
+              float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
+              float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
+              if (key < lo_r || key > pos_r) p0 = 0.f;
+              if (key + 1 < lo_r || key + 1 > pos_r) p1 = 0.f;
+              sum2[0] += p0;
+              sum2[1] += p1;
+              pk[i >> 1] = pack_bf16(p0, p1);
+            }
+          }
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const int chunk = c * 4 + h;
+            const uint32_t dst = p_row + ((chunk ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[h * 4]), "r"(pk[h * 4 + 1]),
+                         "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
+          }
+        };
+        const uint32_t mine = s_addr + (uint32_t)(half * 64);
+        tmem_ld32(mine, va);
+        tmem_ld32(mine + 32u, vb);
+        tmem_wait_ld();
+        take(va, 0);
+        take(vb, 1);
+      }
+      l += sum2[0] + sum2[1];
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, before the MMA reads it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(&sh.p_full));
+    }
+    if (ok) {
+      // the end: both halves' sums, then each thread its 64 columns of O
+      s_l[half][r] = l;
+      mbar_arrive(smem_u32(&sh.fin));
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.fin), 0u, abort_flag) ? 1 : 0);
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full), (uint32_t)(n_blocks - 1) & 1u, abort_flag) ? 1 : 0);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float lt = s_l[0][r] + s_l[1][r];
+        const float inv = lt > 0.f ? 1.f / lt : 0.f;
+        __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD + half * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[16];
+          tmem_ld16(o_addr + (uint32_t)(c * 16), v);
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 16 + i) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -880,11 +897,11 @@ extern "C" int qb_attn_span_tc_supported(int nq, int nkv, int hd, int page_size)
   return encode_fn() != nullptr ? 1 : 0;
 }
 
-// Query rows per tile of the tcgen05 kernels: 256 (two tiles a block); QUANTA_B200_SPAN_KERNEL=tc1 keeps
-// the one-tile kernel (128), for tests and measurements.
+// Query rows per tile of the tcgen05 kernels: 128 (one tile a block, O in TMEM); QUANTA_B200_SPAN_KERNEL=tc2
+// runs the two-tile kernel (256), for tests and measurements.
 extern "C" int qb_attn_span_tc_rows(void) {
   const char* want = getenv("QUANTA_B200_SPAN_KERNEL");
-  return (want != nullptr && strcmp(want, "tc1") == 0) ? TC_BM : 2 * TC_BM;
+  return (want != nullptr && strcmp(want, "tc2") == 0) ? 2 * TC_BM : TC_BM;
 }
 
 // Same arguments as qb_attn_span; the tile list has qb_attn_span_tc_rows() rows a tile.
@@ -906,9 +923,9 @@ extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v
   if (rc) return rc;
   if (qb_attn_span_tc_rows() == TC_BM) {
     const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
-    cudaError_t err = cudaFuncSetAttribute(attn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(attn_span_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
-    attn_span_tc_kernel<<<dim3(n_tiles, nkv), TC_THREADS, smem, stream>>>(
+    attn_span_tc3_kernel<<<dim3(n_tiles, nkv), TC3_THREADS, smem, stream>>>(
         tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
         page_size, num_pages, scale_log2, window, status);
   } else {

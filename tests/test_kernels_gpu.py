@@ -151,18 +151,18 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
                                                    (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
                                                    (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50)])
-@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only", "tc_one_tile"])
+@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only", "tc_two_tiles"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
-    """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05, two
-    query tiles a block, for portions where the shapes allow); the same with the mma.sync kernel for every
-    portion; and with the one-tile tcgen05 kernel."""
+    """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05 with
+    O in TMEM for portions where the shapes allow); the same with the mma.sync kernel for every portion;
+    and with the two-tile tcgen05 kernel."""
     k = K()
     if impl != "simt" and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernels are the bfloat16 path")
-    if impl in ("mma_only", "tc_one_tile"):
+    if impl in ("mma_only", "tc_two_tiles"):
         if not k.attn_span_tc_supported(nq, nkv, hd, page):
             pytest.skip("these shapes run on the mma.sync kernels anyway")
-        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc1")
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc2")
     torch.manual_seed(1)
     # (first position, tokens): prompt portions beside decode tokens; a portion that starts past a split edge
     spans = [(0, 13), (70, 1), (33, 9), (129, 1), (250, 30), (600, 1)]
