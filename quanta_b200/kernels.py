@@ -242,6 +242,27 @@ def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, k_chunk: i
                                  int(k_chunk), _stream()), "gemm_nt_simt")
 
 
+def split3_bf16(w: torch.Tensor) -> torch.Tensor:
+    """A float32 tensor as three bfloat16 tensors ``[3, *w.shape]`` whose sum is ``w`` to float32 accuracy
+    (each is the bfloat16 rounding of what the ones before leave over)."""
+    _want(w, torch.float32, "w")
+    w = w.contiguous()
+    out = torch.empty((3, *w.shape), dtype=torch.bfloat16, device=w.device)
+    _check(lib().qb_split3_bf16(_p(w), _p(out), ctypes.c_longlong(w.numel()), _stream()), "split3_bf16")
+    return out
+
+
+def router_gemm_mma(x: torch.Tensor, pieces: torch.Tensor, logits: torch.Tensor) -> None:
+    """``logits[T, E] = x[T, K] @ (pieces[0] + pieces[1] + pieces[2]).T`` in float32 on the tensor cores,
+    ``pieces`` from ``split3_bf16`` of the float32 gate; the inner dimension in fixed chunks of 64."""
+    T, K = x.shape
+    _want(x, torch.bfloat16, "x"); _want(pieces, torch.bfloat16, "pieces"); _want(logits, torch.float32, "logits")
+    E = pieces.shape[1]
+    if pieces.shape[0] != 3 or pieces.shape[2] != K or logits.numel() != T * E or not logits.is_contiguous():
+        raise ValueError("router_gemm_mma: shape mismatch")
+    _check(lib().qb_router_gemm_mma(_p(x), _p(pieces), _p(logits), T, E, K, _stream()), "router_gemm_mma")
+
+
 def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> None:
     """``logits`` [T, E], or [P, T, E] partial sums that are added in index order first."""
     _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")

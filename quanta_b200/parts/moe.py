@@ -31,7 +31,7 @@ class SigmoidTopKExperts(FeedForward):
         self.H, self.I, self.E, self.k = int(hidden_size), int(expert_size), int(n_experts), int(top_k)
         self.use_bias, self.renorm, self.scaling = bool(use_bias), bool(renormalize), float(scaling)
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
-        self.gate_w = self.bias = self.w13 = self.w2 = None
+        self.gate_w = self.bias = self.w13 = self.w2 = self.gate_pieces = None
         self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
 
     def tensor_specs(self):
@@ -59,6 +59,9 @@ class SigmoidTopKExperts(FeedForward):
             self.w13[e, self.I:].copy_(fetch(n["w3"].format(e=e)))
             self.w2[e].copy_(fetch(n["w2"].format(e=e)))
         del first
+        # prompt portions take their router logits on the tensor cores, from the gate as three bfloat16 pieces
+        if dt == torch.bfloat16 and self.H % 8 == 0:
+            self.gate_pieces = kernels.split3_bf16(self.gate_w)
 
     # Which kernels run the expert products: "tc" (tcgen05 + TMA), "stream" (mma.sync, weights from
     # registers), "simt" (float32 CUDA cores).  "auto": float32 and odd sizes -> simt; bfloat16 -> stream
@@ -67,6 +70,7 @@ class SigmoidTopKExperts(FeedForward):
     # QUANTA_B200_EXPERT_KERNELS (a tuning knob, for measurements).
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
     stream_max_tokens = 0
+    router_mma_min_tokens = 256      # steps of fewer tokens read the float32 gate once on the CUDA cores
 
     def path_for(self, x) -> str:
         ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
@@ -80,11 +84,16 @@ class SigmoidTopKExperts(FeedForward):
     def route(self, x):
         """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
         T = x.shape[0]
-        # the inner dimension is cut at fixed multiples of 128, whatever T: few rows still fill the GPU,
-        # and a token's logits are bit-identical however the step is cut
-        chunk = 128
-        logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
-        kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
+        if self.gate_pieces is not None and x.dtype == torch.bfloat16 and T >= self.router_mma_min_tokens:
+            # many tokens: float32-accurate logits on the tensor cores (fixed chunks of the inner dimension)
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=x.device)
+            kernels.router_gemm_mma(x, self.gate_pieces, logits)
+        else:
+            # the inner dimension is cut at fixed multiples of 128, whatever T: few rows still fill the GPU,
+            # and a token's logits do not depend on how the step is cut
+            chunk = 128
+            logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
+            kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
         idx = torch.empty((T, self.k), dtype=torch.int32, device=x.device)
         w = torch.empty((T, self.k), dtype=torch.float32, device=x.device)
         kernels.router_topk(logits, self.bias, idx, w, self.renorm, self.scaling)

@@ -260,6 +260,27 @@ def test_decode_attention_many_tokens(n_dec, nq, nkv, hd, page):
     assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("T,E,Kd", [(300, 256, 3072), (64, 100, 200), (1, 8, 64), (1000, 520, 328), (257, 33, 72)])
+def test_router_gemm_mma(T, E, Kd):
+    """Router logits on the tensor cores from the gate as three bfloat16 pieces: float32 accuracy against
+    a float64 product, the pieces add up to the gate, and a row does not depend on the rows beside it."""
+    k = K()
+    torch.manual_seed(E)
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    gate = torch.randn(E, Kd, device=DEV) / Kd ** 0.5
+    pieces = k.split3_bf16(gate)
+    assert pieces.shape == (3, E, Kd)
+    back = pieces[0].double() + pieces[1].double() + pieces[2].double()
+    assert float((back - gate.double()).abs().max()) <= 2.0 ** -22 * float(gate.abs().max())
+    logits = torch.full((T, E), float("nan"), device=DEV)
+    k.router_gemm_mma(x, pieces, logits)
+    want = x.double() @ gate.double().T
+    assert torch.allclose(logits.double(), want, atol=2e-5, rtol=1e-5)
+    alone = torch.empty((1, E), device=DEV)
+    k.router_gemm_mma(x[T // 2: T // 2 + 1].contiguous(), pieces, alone)
+    assert torch.equal(alone[0], logits[T // 2])
+
+
 @pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
 def test_gemm_nt_simt(a_dtype, b_dtype):
     M, N, K_ = 45, 257, 1003
