@@ -60,7 +60,7 @@ class SigmoidTopKExperts(FeedForward):
             self.w2[e].copy_(fetch(n["w2"].format(e=e)))
         del first
         # prompt portions take their router logits on the tensor cores, from the gate as three bfloat16 pieces
-        if dt == torch.bfloat16 and self.H % 8 == 0:
+        if dt == torch.bfloat16 and self.H % 8 == 0 and self.gate_w.is_cuda:
             self.gate_pieces = kernels.split3_bf16(self.gate_w)
 
     # Which kernels run the expert products: "tc" (tcgen05 + TMA), "stream" (mma.sync, weights from

@@ -18,7 +18,7 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200) and the compiled kernels")
 
 
-# Three tiny configurations that differ in every size and option: head counts and groups, sizes that
+# Tiny configurations that differ in every size and option: head counts and groups, sizes that
 # are no power of two, layers, vocabulary, eps, rotary share and base, q/k norm (over all heads, per
 # head, none), experts, top-k, bias, renormalisation, scale factor, tied head.
 TINY = {
@@ -38,8 +38,15 @@ TINY = {
               num_local_experts=12, num_experts_per_tok=3, use_routing_bias=True, norm_topk_prob=False,
               routed_scaling_factor=0.5, rms_norm_eps=1e-5, tie_word_embeddings=False,
               architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3", eos_token_id=332),
+    # the head size, page size and widths that take the kernels of the full-size model (tcgen05 prefill
+    # attention, TMA decode attention, tcgen05 experts, tensor-core router), at a small scale
+    "D": dict(vocab_size=777, hidden_size=256, intermediate_size=192, num_hidden_layers=2,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=128, rotary_dim=64, rope_theta=5e6,
+              use_qk_norm=True, qk_norm_type="per_layer", num_local_experts=16, num_experts_per_tok=4,
+              use_routing_bias=True, rms_norm_eps=1e-6, tie_word_embeddings=False,
+              architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3", eos_token_id=776),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 @pytest.fixture(scope="session")

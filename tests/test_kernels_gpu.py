@@ -69,9 +69,9 @@ def test_add_rmsnorm(H, out_dtype):
 def _paged(kc, vc, table, req, length, kvh):
     """Gather a request's keys/values [length, hd] of one kv head from the pages."""
     P_ = kc.shape[2]
-    ks = [kc[table[req][p // P_], kvh, p % P_] for p in range(length)]
-    vs = [vc[table[req][p // P_], kvh, p % P_] for p in range(length)]
-    return torch.stack(ks).float(), torch.stack(vs).float()
+    pos = torch.arange(length)
+    pages = torch.as_tensor(table[req])[pos // P_].long()
+    return kc[pages, kvh, pos % P_].float(), vc[pages, kvh, pos % P_].float()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -136,13 +136,15 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
     T, nq, hd = q.shape
     nkv = kc.shape[1]
     out = torch.zeros(T, nq, hd)
+    kc, vc, G = kc.cpu(), vc.cpu(), nq // nkv
     for t in range(T):
         p, r = int(tok_pos[t]), int(tok_req[t])
         lo = max(0, p - window + 1) if window else 0
-        for h in range(nq):
-            ks, vs = _paged(kc.cpu(), vc.cpu(), table, r, p + 1, h // (nq // nkv))
-            s = (ks[lo:] @ q[t, h].float().cpu()) * scale
-            out[t, h] = torch.softmax(s, 0) @ vs[lo:]
+        for kvh in range(nkv):
+            ks, vs = _paged(kc, vc, table, r, p + 1, kvh)
+            for h in range(kvh * G, (kvh + 1) * G):
+                s = (ks[lo:] @ q[t, h].float().cpu()) * scale
+                out[t, h] = torch.softmax(s, 0) @ vs[lo:]
     return out
 
 

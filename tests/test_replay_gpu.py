@@ -25,7 +25,8 @@ from tests.conftest import TINY
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 FP32_TOL = 2e-5
-LENGTHS = {"A": (5, 11, 16, 75, 50), "B": (7, 23, 64, 33, 97), "C": (2, 49, 80, 17, 65)}
+LENGTHS = {"A": (5, 11, 16, 75, 50), "B": (7, 23, 64, 33, 97), "C": (2, 49, 80, 17, 65),
+           "D": (40, 300, 129, 270, 64)}            # D: several 128-key blocks and 64-key tiles a request
 
 
 def _requests(name):
@@ -75,13 +76,13 @@ CUTS = {
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cutting_matches_plain(model_dirs, plain_models, name, dtype):
     reqs = _requests(name)
     act = None if dtype == "float32" else torch.bfloat16
     want = _plain(plain_models, name, act)
     tol = _tolerance(plain_models, name, dtype)
-    page_size = {"A": 4, "B": 8, "C": 16}[name]
+    page_size = {"A": 4, "B": 8, "C": 16, "D": 16}[name]
     results = {}
     for cut, make in CUTS.items():
         steps = make(reqs)
