@@ -37,7 +37,7 @@ def _loaded(model_dirs, name, dtype="float32"):
     return load_model(model_dirs[name], dtype=dtype)[0]
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_norm_attention_experts_alone(model_dirs, plain_models, name):
     from quanta_b200.parts.base import LayerCache
     model = _loaded(model_dirs, name)
@@ -331,7 +331,8 @@ def test_toy_position_encoding_in_the_real_attention(model_dirs):
 
 
 # ---- generation through the entry point ------------------------------------------------------------------
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16"), ("D", "float32"),
+                                        ("D", "bfloat16")])
 def test_greedy_generation_matches_plain(model_dirs, plain_models, name, dtype):
     from quanta_b200 import generate
     from quanta_b200.engine.generate import LLM

@@ -118,7 +118,7 @@ def test_long_decoding(model_dirs, plain_models, dtype):
     _compare(got, want, tol, f"long decoding {dtype}")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_first_tokens(model_dirs, plain_models, name):
     """Positions 0, 1, 2 of a sequence, fed one at a time and as one portion."""
     toks = H.random_tokens(3, TINY[name]["vocab_size"], seed=11)
