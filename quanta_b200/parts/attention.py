@@ -37,6 +37,9 @@ class GQAttention(Mixer):
         self.position = make("position", position) if isinstance(position, tuple) else position
         self.names = dict(names)      # q, k, v, o, and q_norm, k_norm when normed
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        # more q heads per kv head than the single-token kernel takes: single tokens run as portions of one,
+        # whose tile list comes from the host each step, so such a model's decode steps are not captured
+        self.graph_safe = self.nq // self.nkv <= kernels.ATTN_DECODE_MAX_GROUP
 
     def children(self):
         return [self.position]

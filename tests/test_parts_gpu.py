@@ -432,6 +432,41 @@ def test_steps_launched_ahead_give_the_same_tokens(model_dirs, name, dtype):
     assert n_ahead == 0
 
 
+def test_more_q_heads_per_kv_head_than_the_decode_kernel_takes(tmp_path):
+    """72 q heads on one kv head: single tokens run as portions of one (no captured decode step); and a
+    head size of 80 beside it (no TMA boxes, no tcgen05 attention).  Both against the plain implementation,
+    decoding token by token after a prompt."""
+    from safetensors.torch import load_file
+    from quanta_b200.config import MiniMaxM3Config
+    from quanta_b200.engine.model import load_model, write_random_model
+    from quanta_b200.engine.step import Engine
+    common = dict(architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3", rms_norm_eps=1e-6,
+                  tie_word_embeddings=False, num_hidden_layers=1, use_routing_bias=True, use_qk_norm=True)
+    cases = {
+        "wide_group": dict(vocab_size=400, hidden_size=256, intermediate_size=128, num_attention_heads=72,
+                           num_key_value_heads=1, head_dim=128, rotary_dim=64, rope_theta=5e6, qk_norm_type="per_layer",
+                           num_local_experts=8, num_experts_per_tok=2),
+        "head_80": dict(vocab_size=1001, hidden_size=120, intermediate_size=72, num_attention_heads=5,
+                        num_key_value_heads=5, head_dim=80, rotary_dim=40, rope_theta=1e4, qk_norm_type="per_head",
+                        num_local_experts=5, num_experts_per_tok=5),
+    }
+    for name, raw in cases.items():
+        raw = dict(common, **raw)
+        d = tmp_path / name
+        write_random_model(MiniMaxM3Config.from_dict(raw), 5, d)
+        plain = (load_file(str(d / "model.safetensors")), P.read_config(d))
+        reqs = {"a": H.random_tokens(150, raw["vocab_size"], 1), "b": H.random_tokens(70, raw["vocab_size"], 2)}
+        want = H.plain_logits(plain, reqs, act=torch.bfloat16)
+        exact = H.plain_logits(plain, reqs)
+        tol = 2.0 * max(float((want[k] - exact[k]).abs().max()) for k in want)
+        model, _ = load_model(d, dtype="bfloat16")
+        eng = Engine(model, num_pages=32, page_size=16, max_requests=4)
+        assert eng.use_graphs == (name != "wide_group")
+        for cut in (H.cut_tail_decode(reqs, 40), H.cut_mixed(reqs, 2, seed=4)):
+            got = H.replay(eng, cut)
+            assert H.first_wrong(got, want, tol) is None, (name, H.worst_error(got, want), tol)
+
+
 def test_command_line(model_dirs):
     cmd = [sys.executable, "-m", "quanta_b200", "generate", "--model", str(model_dirs["A"]), "--dtype", "float32",
            "--prompt-ids", "5,17,3", "--max-new-tokens", "4", "--block-size", "4", "--num-pages", "16", "--eos-id", "600"]
