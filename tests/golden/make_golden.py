@@ -14,7 +14,7 @@ weights, renormalisation, scaling), and the attention core with per-head q/k nor
 concatenated heads, the SiLU SwiGLU expert (the oracle has only the clamped activation), and the
 expert sum without a shared expert.
 
-Run:  python tests/golden/make_golden.py [/path/to/reference]
+Run:  python tests/golden/make_golden.py /path/to/reference
 """
 
 import ast
@@ -60,7 +60,9 @@ def cases():
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/the/reference/checkout")
+    ref = Path(sys.argv[1])
     ns = load_oracle(ref)
     cfg, c = cases()
     out = {}

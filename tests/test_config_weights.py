@@ -71,7 +71,10 @@ def test_config_matches_reference_parser(tmp_path):
     """Field by field against the reference's own pure-Python parser, when its sources are present."""
     import importlib.util
     import pathlib
-    ref = pathlib.Path("/root/reference/src/quanta/minimax/config.py")
+    import os
+    # the checkout of the reference: QUANTA_REFERENCE_DIR, or a "reference" folder beside this repository
+    root = pathlib.Path(os.environ.get("QUANTA_REFERENCE_DIR") or pathlib.Path(__file__).resolve().parents[2] / "reference")
+    ref = root / "src" / "quanta" / "minimax" / "config.py"
     if not ref.exists():
         pytest.skip("reference sources not present")
     spec = importlib.util.spec_from_file_location("ref_minimax_config", ref)
