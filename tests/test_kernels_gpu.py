@@ -152,7 +152,8 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 3, 48, 4, 0), (4, 4, 16, 16, 0), (12, 2, 128, 8, 0),
                                                    (5, 1, 256, 5, 0), (6, 2, 64, 4, 11), (40, 2, 32, 16, 0),
                                                    (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
-                                                   (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50)])
+                                                   (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50),
+                                                   (4, 2, 256, 16, 0), (6, 1, 192, 8, 0), (16, 2, 128, 128, 0)])
 @pytest.mark.parametrize("impl", ["simt", "mma", "mma_only", "tc_two_tiles"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
     """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05 with
