@@ -84,6 +84,7 @@ class Engine:
         # graphs only when every part says its step reads nothing from the host
         self.use_graphs = bool(use_graphs) and all(getattr(p, "graph_safe", False) for p in model.parts())
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self._graph_pool = None        # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
         # the token last sampled for the request in each state slot: a decode step can take its ids from
         # here, so that it can be launched before the host has read them
@@ -292,7 +293,9 @@ class Engine:
             torch.cuda.synchronize()
             before = kernels.LAUNCHES
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 g.logits = self.model.forward(d_ids, ctx, caches, self.state, d_want)
             g.launches = kernels.LAUNCHES - before
             g.graph = graph
