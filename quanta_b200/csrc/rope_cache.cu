@@ -51,11 +51,18 @@ __global__ void qknorm_rope_write_kernel(
   __syncthreads();
 
   if (norm_kind == NORM_PER_LAYER) {
-    float sq = 0.f, sk = 0.f;
-    for (int i = threadIdx.x; i < qn; i += blockDim.x) sq += buf[i] * buf[i];
-    for (int i = threadIdx.x; i < kn; i += blockDim.x) sk += buf[qn + i] * buf[qn + i];
-    const float tq = qb_block_sum(sq, scratch);
-    const float tk = qb_block_sum(sk, scratch);
+    // a warp per head, then the heads' sums in head order: the same additions whatever the block size
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < nq + nkv; h += nwarps) {
+      float sh = 0.f;
+      for (int d = lane; d < hd; d += 32) sh += buf[h * hd + d] * buf[h * hd + d];
+      sh = qb_warp_sum(sh);
+      if (lane == 0) head_r[h] = sh;
+    }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+    for (int h = 0; h < nq; ++h) tq += head_r[h];
+    for (int h = 0; h < nkv; ++h) tk += head_r[nq + h];
     const float rq = rsqrtf(tq / (float)qn + eps), rk = rsqrtf(tk / (float)kn + eps);
 #pragma unroll 4
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
@@ -141,7 +148,9 @@ extern "C" int qb_qknorm_rope_write(
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    kern<<<T, 256, smem, stream>>>((const A*)qkv, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w, k_norm_w,
+    // steps of few tokens: more threads a token, so that each of the kernel's phases is short
+    const int threads = T <= 64 ? 1024 : 256;
+    kern<<<T, threads, smem, stream>>>((const A*)qkv, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w, k_norm_w,
                                    norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos, tok_req,
                                    block_table, bt_stride, T, nq, nkv, hd, rd, page_size, num_pages, status);
   });
