@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..matmul import linear
+from ..matmul import empty_rows, linear
 from .base import KVCacheSpec, Mixer, TensorSpec, make, register
 
 _NORM_KIND = {None: kernels.NORM_NONE, "per_layer": kernels.NORM_PER_LAYER, "per_head": kernels.NORM_PER_HEAD}
@@ -88,7 +88,7 @@ class GQAttention(Mixer):
             qkv, q, cache.k if cache.write else None, cache.v if cache.write else None, self.q_norm_w,
             self.k_norm_w, _NORM_KIND[self.qk_norm], self.eps, inv_freq, pair_axis, ctx.positions, ctx.tok_pos,
             ctx.tok_req, cache.block_table, self.nq, self.nkv, self.hd, rd, cache.page_size, ctx.status)
-        out = torch.empty_like(q)
+        out = empty_rows(T, self.nq, self.hd, dtype=x.dtype, device=x.device)
         self.attend(q, cache, out, ctx)
         return linear(out.view(T, self.nq * self.hd), self.w_o)
 

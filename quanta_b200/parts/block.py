@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..matmul import linear
+from ..matmul import empty_rows, linear
 from .base import Block, Part, TensorSpec, make, register
 
 
@@ -29,10 +29,10 @@ class PreNormBlock(Block):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
     def forward(self, h, pending, ctx, cache, state):
-        x = torch.empty((h.shape[0], self.hidden), dtype=ctx.dtype, device=h.device)
+        x = empty_rows(h.shape[0], self.hidden, dtype=ctx.dtype, device=h.device)
         self.mixer_norm.forward(h, pending, x)
         a = self.mixer.forward(x, ctx, cache, state)
-        x2 = torch.empty_like(x)
+        x2 = empty_rows(h.shape[0], self.hidden, dtype=ctx.dtype, device=h.device)
         self.feed_forward_norm.forward(h, a, x2)
         return self.feed_forward.forward(x2, ctx)
 
@@ -81,6 +81,6 @@ class OutputHead(Part):
 
     def forward(self, h, pending, rows, ctx):
         n = rows.numel()
-        x = torch.empty((n, self.H), dtype=ctx.dtype, device=h.device)
+        x = empty_rows(n, self.H, dtype=ctx.dtype, device=h.device)
         self.norm.forward(h, pending, x, rows=rows, store_h=False)
         return linear(x, self.weight, out_dtype=torch.float32)

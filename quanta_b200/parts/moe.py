@@ -14,7 +14,7 @@ import os
 import torch
 
 from .. import kernels
-from ..matmul import linear
+from ..matmul import empty_rows, linear
 from .base import FeedForward, TensorSpec, register
 
 
@@ -159,6 +159,6 @@ class SwiGLUDense(FeedForward):
 
     def forward(self, x, ctx):
         gu = linear(x, self.w_gu)
-        act = torch.empty((x.shape[0], self.I), dtype=x.dtype, device=x.device)
+        act = empty_rows(x.shape[0], self.I, dtype=x.dtype, device=x.device)
         kernels.silu_mul(gu, act)
         return linear(act, self.w_down)
