@@ -13,18 +13,17 @@
 // routing: one warp per token
 // ---------------------------------------------------------------------------------------------
 template <int NPL>   // experts per lane, E <= 32*NPL
-__global__ void router_topk_kernel(const float* __restrict__ logits, int n_partials,
-                                   const float* __restrict__ bias, int* __restrict__ idx_out,
-                                   float* __restrict__ w_out, int T, int E, int k, int renorm, float scale) {
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int n_partials,
+                                            const float* __restrict__ bias, int* __restrict__ idx_out,
+                                            float* __restrict__ w_out, int T, int E, int k, int renorm, float scale,
+                                            float* s_logit, float* s_part) {
   // logits: [n_partials][T][E], partial products of chunks of the inner dimension.  One block per token.
   // The partials of an expert are added by `groups` threads, each a contiguous range in index order, and
   // the groups' sums are then added in group order: the order depends on E and n_partials only, never on
-  // the step, and every thread has only a few independent loads to wait for.  The first warp selects.
-  __shared__ float s_logit[1024];
-  __shared__ float s_part[1056];
+  // the step, and every thread has only a few independent loads to wait for.  The first warp selects;
+  // its lane 0 writes the chosen experts.  s_logit: 1024 floats, s_part: 1056.
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x;
-  if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
   const size_t pstride = (size_t)T * E;
   const int e_round = (E + 31) / 32 * 32;
@@ -47,7 +46,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_parti
     s_logit[e] = x;
   }
   __syncthreads();
-  if (threadIdx.x >= 32) return;
+  if (threadIdx.x >= 32) return;      // of this function: the caller's other warps go on
   float choice[NPL], score[NPL], logit[NPL];
   unsigned taken = 0u;
 #pragma unroll
@@ -105,6 +104,16 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_parti
   __syncwarp();
   const float denom = (renorm && k > 1) ? sum + 1e-20f : 1.f;
   for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = s_part[r] / denom * scale;
+}
+
+template <int NPL>
+__global__ void router_topk_kernel(const float* __restrict__ logits, int n_partials,
+                                   const float* __restrict__ bias, int* __restrict__ idx_out,
+                                   float* __restrict__ w_out, int T, int E, int k, int renorm, float scale) {
+  __shared__ float s_logit[1024];
+  __shared__ float s_part[1056];
+  if ((int)blockIdx.x >= T) return;
+  route_token<NPL>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale, s_logit, s_part);
 }
 
 extern "C" int qb_router_topk(const float* logits, int n_partials, const float* bias, int* idx_out, float* w_out,
@@ -189,18 +198,24 @@ __global__ void moe_scatter_kernel(const int* __restrict__ idx, int n_pairs, int
 
 // The whole plan in one block, for steps with few pairs (decoding): counts in shared memory, the same
 // scans as above, then the scatter.  One launch instead of a memset and three kernels.
-__global__ void moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
-                                      int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
-                                      int* __restrict__ tile_row0, int max_tiles, int* status) {
-  __shared__ int s_cnt[1024];
-  __shared__ int s_til[1024];
-  __shared__ int s_act[1024];
-  __shared__ int s_cur[1024];
+struct PlanShared {
+  int cnt[1024], til[1024], act[1024], cur[1024];
+};
+
+// A block of 1024 threads; idx is read past L1 (another block of the same launch may have written it).
+__device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int E, int BM, int* __restrict__ plan,
+                                                int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                                                int* __restrict__ tile_row0, int max_tiles, int* status,
+                                                PlanShared& sh) {
+  int* s_cnt = sh.cnt;
+  int* s_til = sh.til;
+  int* s_act = sh.act;
+  int* s_cur = sh.cur;
   const int e = threadIdx.x;
   s_cur[e] = 0;
   __syncthreads();
   for (int i = e; i < n_pairs; i += 1024) {
-    const int x = idx[i];
+    const int x = __ldcg(idx + i);
     if (x < 0 || x >= E) { qb_set_status(status, QB_STATUS_BAD_EXPERT, x, 4); continue; }
     atomicAdd(&s_cur[x], 1);
   }
@@ -237,10 +252,64 @@ __global__ void moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, 
   s_cur[e] = off;                     // running write position of each expert
   __syncthreads();
   for (int i = e; i < n_pairs; i += 1024) {
-    const int x = idx[i];
+    const int x = __ldcg(idx + i);
     if (x < 0 || x >= E) continue;
     sorted_pair[atomicAdd(&s_cur[x], 1)] = i;
   }
+}
+
+__global__ void moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
+                                      int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                                      int* __restrict__ tile_row0, int max_tiles, int* status) {
+  __shared__ PlanShared sh;
+  plan_small_body(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh);
+}
+
+// Routing and the plan of a step of few tokens in one launch: one block a token selects; the block that
+// finishes last (a counter in global memory, left at zero again) lays the plan down for all of them.
+// Every block ends by itself: nothing waits.
+template <int NPL>
+__global__ void __launch_bounds__(1024)
+router_topk_plan_kernel(const float* __restrict__ logits, int n_partials, const float* __restrict__ bias,
+                        int* idx_out, float* __restrict__ w_out, int T, int E, int k, int renorm, float scale,
+                        int* counter, int BM, int* __restrict__ plan, int* __restrict__ sorted_pair,
+                        int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles, int* status) {
+  __shared__ float s_logit[1024];
+  __shared__ float s_part[1056];
+  __shared__ PlanShared sh;
+  __shared__ int s_last;
+  if ((int)blockIdx.x >= T) return;
+  route_token<NPL>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale, s_logit, s_part);
+  __syncthreads();
+  if (threadIdx.x == 0) {             // the thread that wrote this token's experts
+    __threadfence();
+    const int before = atomicAdd(counter, 1);
+    s_last = before == T - 1;
+    if (s_last) *counter = 0;         // every other block has counted already
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  plan_small_body(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh);
+}
+
+// counter: one int32 that is zero before the call and zero after it
+extern "C" int qb_router_topk_plan(const float* logits, int n_partials, const float* bias, int* idx_out,
+                                   float* w_out, int T, int E, int k, int renorm, float scale, int* counter, int BM,
+                                   int* plan, int* sorted_pair, int* tile_expert, int* tile_row0, int max_tiles,
+                                   int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (k <= 0 || k > E || n_partials <= 0 || counter == nullptr) return QB_ERR_BAD_ARG;
+  if (E > 256 || (long long)T * k > 4096) return QB_ERR_UNSUPPORTED;
+#define QB_ROUTE(N) router_topk_plan_kernel<N><<<T, 1024, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, \
+    k, renorm, scale, counter, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status)
+  if (E <= 32) QB_ROUTE(1);
+  else if (E <= 64) QB_ROUTE(2);
+  else if (E <= 128) QB_ROUTE(4);
+  else QB_ROUTE(8);
+#undef QB_ROUTE
+  QB_LAUNCH_CHECK();
+  return 0;
 }
 
 extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan, int* sorted_pair,

@@ -275,6 +275,27 @@ def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> Non
                                 ctypes.c_float(scale), _stream()), "router_topk")
 
 
+def router_topk_plan_supported(n_tokens: int, n_experts: int, top_k: int) -> bool:
+    return n_experts <= 256 and n_tokens * top_k <= 4096
+
+
+def router_topk_plan(logits, bias, idx_out, w_out, renorm: bool, scale: float, counter, bm: int, plan, sorted_pair,
+                     tile_expert, tile_row0, status) -> None:
+    """``router_topk`` and ``moe_plan`` of a step of few tokens as one launch.  ``counter``: one int32 that
+    is zero before the call; the kernel leaves it zero."""
+    _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
+    _want(counter, torch.int32, "counter")
+    n_partials = 1 if logits.dim() == 2 else logits.shape[0]
+    T, E = logits.shape[-2:]
+    k = idx_out.shape[1]
+    if bias is not None:
+        _want(bias, torch.float32, "bias")
+    _check(lib().qb_router_topk_plan(_p(logits), n_partials, _p(bias), _p(idx_out), _p(w_out), T, E, k, int(renorm),
+                                     ctypes.c_float(scale), _p(counter), bm, _p(plan), _p(sorted_pair),
+                                     _p(tile_expert), _p(tile_row0), tile_expert.numel(), _p(status), _stream()),
+           "router_topk_plan")
+
+
 MOE_SIMT_BM = 32
 
 

@@ -33,6 +33,7 @@ class SigmoidTopKExperts(FeedForward):
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
         self.gate_w = self.bias = self.w13 = self.w2 = self.gate_pieces = None
         self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
+        self._plan_counter = None    # the fused routing-and-plan kernel's counter of finished blocks (zero at rest)
 
     def tensor_specs(self):
         n = self.names
@@ -71,6 +72,7 @@ class SigmoidTopKExperts(FeedForward):
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
     stream_max_tokens = 0
     router_mma_min_tokens = 256      # steps of fewer tokens read the float32 gate once on the CUDA cores
+    fused_plan_max_tokens = 64       # steps of at most this many tokens select and plan in one launch
 
     def path_for(self, x) -> str:
         ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
@@ -81,8 +83,8 @@ class SigmoidTopKExperts(FeedForward):
             return choice
         return "stream" if x.shape[0] <= self.stream_max_tokens else "tc"
 
-    def route(self, x):
-        """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
+    def router_logits(self, x):
+        """float32 ``[T, E]``, or ``[chunks, T, E]`` partial sums that the selection adds in index order."""
         T = x.shape[0]
         if self.gate_pieces is not None and x.dtype == torch.bfloat16 and T >= self.router_mma_min_tokens:
             # many tokens: float32-accurate logits on the tensor cores (fixed chunks of the inner dimension)
@@ -94,14 +96,30 @@ class SigmoidTopKExperts(FeedForward):
             chunk = 128
             logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
             kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
+        return logits
+
+    def route(self, x):
+        """Router of this part alone: ``(idx int32 [T,k], weights float32 [T,k])``."""
+        T = x.shape[0]
+        logits = self.router_logits(x)
         idx = torch.empty((T, self.k), dtype=torch.int32, device=x.device)
         w = torch.empty((T, self.k), dtype=torch.float32, device=x.device)
         kernels.router_topk(logits, self.bias, idx, w, self.renorm, self.scaling)
         return idx, w
 
     def forward(self, x, ctx):
-        T, dev = x.shape[0], x.device
+        T = x.shape[0]
+        if (x.is_cuda and T <= self.fused_plan_max_tokens
+                and kernels.router_topk_plan_supported(T, self.E, self.k)):
+            # few tokens: the block that selects last lays the plan down too
+            return self.experts(x, None, None, ctx)
         idx, w = self.route(x)
+        return self.experts(x, idx, w, ctx)
+
+    def experts(self, x, idx, w, ctx):
+        """The chosen experts' SwiGLU of every token, weighted: float32 ``[T, k, hidden]``, one slot a choice.
+        ``idx`` None: route here, in one launch with the plan."""
+        T, dev = x.shape[0], x.device
         n_pairs = T * self.k
         path = self.path_for(x)
         bm = kernels.expert_tile_rows(T, n_pairs / self.E) if path == "tc" else kernels.MOE_SIMT_BM
@@ -111,7 +129,16 @@ class SigmoidTopKExperts(FeedForward):
         sorted_pair = ints[plan_words: plan_words + n_pairs]
         tile_expert = ints[plan_words + n_pairs: plan_words + n_pairs + max_tiles]
         tile_row0 = ints[plan_words + n_pairs + max_tiles:]
-        kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+        if idx is None:
+            logits = self.router_logits(x)
+            idx = torch.empty((T, self.k), dtype=torch.int32, device=dev)
+            w = torch.empty((T, self.k), dtype=torch.float32, device=dev)
+            if self._plan_counter is None:
+                self._plan_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            kernels.router_topk_plan(logits, self.bias, idx, w, self.renorm, self.scaling, self._plan_counter, bm,
+                                     plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+        else:
+            kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
         self.last_counts = plan[: self.E]
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)

@@ -323,6 +323,48 @@ def test_router_topk(E, k, bias, renorm, scale):
     assert torch.allclose(w, want_w, atol=1e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("T,E,k,P,bm", [(1, 256, 8, 24, 16), (8, 256, 8, 24, 16), (3, 12, 3, 1, 32), (64, 200, 6, 5, 128),
+                                        (37, 16, 4, 2, 32)])
+def test_router_topk_and_plan_in_one_launch(T, E, k, P, bm):
+    """The fused kernel of small steps against the two kernels it stands for, several times over (the
+    counter of finished blocks must be back at zero after every launch)."""
+    kern = K()
+    assert kern.router_topk_plan_supported(T, E, k)
+    torch.manual_seed(T * 7 + E)
+    bias = 0.05 * torch.randn(E, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = kern.new_status(DEV)
+    plan_words, max_tiles = kern.moe_plan_sizes(T * k, E, bm)
+    for rep in range(3):
+        logits = torch.randn(P, T, E, device=DEV)
+        if P == 1:
+            logits = logits[0].contiguous()
+        idx_a = torch.empty(T, k, device=DEV, dtype=torch.int32)
+        w_a = torch.empty(T, k, device=DEV)
+        kern.router_topk(logits, bias, idx_a, w_a, True, 1.5)
+        a = [torch.zeros(n, dtype=torch.int32, device=DEV) for n in (plan_words, T * k, max_tiles, max_tiles)]
+        kern.moe_plan(idx_a, E, bm, *a, st)
+        idx_b = torch.empty_like(idx_a)
+        w_b = torch.empty_like(w_a)
+        b = [torch.zeros(n, dtype=torch.int32, device=DEV) for n in (plan_words, T * k, max_tiles, max_tiles)]
+        kern.router_topk_plan(logits, bias, idx_b, w_b, True, 1.5, counter, bm, *b, st)
+        assert int(counter) == 0
+        assert torch.equal(idx_a, idx_b) and torch.equal(w_a, w_b)
+        counts, offsets = a[0][:E], a[0][2 * E: 3 * E + 1]
+        assert torch.equal(counts, b[0][:E]) and torch.equal(offsets, b[0][2 * E: 3 * E + 1])
+        assert torch.equal(a[0][3 * E + 1: 3 * E + 3], b[0][3 * E + 1: 3 * E + 3])       # tiles, active experts
+        n_tiles, n_active = int(a[0][3 * E + 1]), int(a[0][3 * E + 2])
+        assert torch.equal(a[0][3 * E + 4: 3 * E + 4 + n_active], b[0][3 * E + 4: 3 * E + 4 + n_active])
+        assert torch.equal(a[2][:n_tiles], b[2][:n_tiles]) and torch.equal(a[3][:n_tiles], b[3][:n_tiles])
+        # the rows of an expert may come in any order: compare them as sets
+        off = offsets.tolist()
+        pa, pb = a[1].tolist(), b[1].tolist()
+        for e in range(E):
+            assert sorted(pa[off[e]: off[e + 1]]) == sorted(pb[off[e]: off[e + 1]])
+        assert sorted(pb) == list(range(T * k))
+    kern.raise_on_status(st.cpu())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("path", ["simt", "stream", "tc"])
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2),
