@@ -12,48 +12,16 @@
 // ---------------------------------------------------------------------------------------------
 // routing: one warp per token
 // ---------------------------------------------------------------------------------------------
-template <int NPL>   // experts per lane, E <= 32*NPL
-__device__ __forceinline__ void route_token(const float* __restrict__ logits, int n_partials,
-                                            const float* __restrict__ bias, int* __restrict__ idx_out,
-                                            float* __restrict__ w_out, int T, int E, int k, int renorm, float scale,
-                                            float* s_logit, float* s_part) {
-  // logits: [n_partials][T][E], partial products of chunks of the inner dimension.  One block per token.
-  // The partials of an expert are added by `groups` threads, each a contiguous range in index order, and
-  // the groups' sums are then added in group order: the order depends on E and n_partials only, never on
-  // the step, and every thread has only a few independent loads to wait for.  The first warp selects;
-  // its lane 0 writes the chosen experts.  s_logit: 1024 floats, s_part: 1056.
+// One warp selects for one token: the k largest of sigmoid(logit) (+ bias), the lower expert index first
+// among equals; the weights are the bias-free scores, renormalised and scaled.  Lane l holds experts
+// l, l + 32, ...; s_score: k floats of shared memory that belong to this warp.
+template <int NPL>
+__device__ __forceinline__ void select_topk(const float (&logit)[NPL], const float* __restrict__ bias,
+                                            int* __restrict__ idx_row, float* __restrict__ w_row, float* s_score,
+                                            int E, int k, int renorm, float scale) {
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  const float* lg = logits + (size_t)t * E;
-  const size_t pstride = (size_t)T * E;
-  const int e_round = (E + 31) / 32 * 32;
-  const int groups = max(1, min((int)blockDim.x / e_round, n_partials));
-  const int per = (n_partials + groups - 1) / groups;
-  for (int i = threadIdx.x; i < groups * e_round; i += blockDim.x) {
-    const int g = i / e_round, e = i % e_round;
-    if (e < E) {
-      const int p_end = min(n_partials, (g + 1) * per);
-      float x = 0.f;
-#pragma unroll 8
-      for (int p = g * per; p < p_end; ++p) x += lg[p * pstride + e];
-      s_part[i] = x;
-    }
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    float x = s_part[e];
-    for (int g = 1; g < groups; ++g) x += s_part[g * e_round + e];
-    s_logit[e] = x;
-  }
-  __syncthreads();
-  if (threadIdx.x >= 32) return;      // of this function: the caller's other warps go on
-  float choice[NPL], score[NPL], logit[NPL];
+  float choice[NPL], score[NPL];
   unsigned taken = 0u;
-#pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int e = lane + 32 * i;
-    logit[i] = e < E ? s_logit[e] : 0.f;
-  }
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
@@ -97,13 +65,57 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
     const float sc = __shfl_sync(0xffffffffu, mine, bi & 31);     // the bias-free score of the chosen expert
     sum += sc;
     if (lane == 0) {
-      idx_out[(size_t)t * k + r] = bi;
-      s_part[r] = sc;               // the partial sums are done with: keep the chosen scores here
+      idx_row[r] = bi;
+      s_score[r] = sc;
     }
   }
   __syncwarp();
   const float denom = (renorm && k > 1) ? sum + 1e-20f : 1.f;
-  for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = s_part[r] / denom * scale;
+  for (int r = lane; r < k; r += 32) w_row[r] = s_score[r] / denom * scale;
+}
+
+template <int NPL>   // experts per lane, E <= 32*NPL
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int n_partials,
+                                            const float* __restrict__ bias, int* __restrict__ idx_out,
+                                            float* __restrict__ w_out, int T, int E, int k, int renorm, float scale,
+                                            float* s_logit, float* s_part) {
+  // logits: [n_partials][T][E], partial products of chunks of the inner dimension.  One block per token.
+  // The partials of an expert are added by `groups` threads, each a contiguous range in index order, and
+  // the groups' sums are then added in group order: the order depends on E and n_partials only, never on
+  // the step, and every thread has only a few independent loads to wait for.  The first warp selects;
+  // its lane 0 writes the chosen experts.  s_logit: 1024 floats, s_part: 1056.
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const float* lg = logits + (size_t)t * E;
+  const size_t pstride = (size_t)T * E;
+  const int e_round = (E + 31) / 32 * 32;
+  const int groups = max(1, min((int)blockDim.x / e_round, n_partials));
+  const int per = (n_partials + groups - 1) / groups;
+  for (int i = threadIdx.x; i < groups * e_round; i += blockDim.x) {
+    const int g = i / e_round, e = i % e_round;
+    if (e < E) {
+      const int p_end = min(n_partials, (g + 1) * per);
+      float x = 0.f;
+#pragma unroll 8
+      for (int p = g * per; p < p_end; ++p) x += lg[p * pstride + e];
+      s_part[i] = x;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float x = s_part[e];
+    for (int g = 1; g < groups; ++g) x += s_part[g * e_round + e];
+    s_logit[e] = x;
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) return;      // of this function: the caller's other warps go on
+  float logit[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    logit[i] = e < E ? s_logit[e] : 0.f;
+  }
+  select_topk<NPL>(logit, bias, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_part, E, k, renorm, scale);
 }
 
 template <int NPL>
@@ -116,11 +128,53 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int n_parti
   route_token<NPL>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale, s_logit, s_part);
 }
 
+// Steps of many tokens: one warp a token, eight tokens a block; the few partial logits of an expert are
+// added in index order by the lane that holds the expert (the additions of route_token for as few).
+constexpr int TOPK_WARPS = 8, TOPK_WARP_MAX_PARTIALS = 4;
+
+template <int NPL>
+__global__ void __launch_bounds__(TOPK_WARPS * 32)
+router_topk_warp_kernel(const float* __restrict__ logits, int n_partials, const float* __restrict__ bias,
+                        int* __restrict__ idx_out, float* __restrict__ w_out, int T, int E, int k, int renorm,
+                        float scale) {
+  extern __shared__ float s_scores[];            // [TOPK_WARPS][k]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * TOPK_WARPS + warp;
+  if (t >= T) return;
+  const float* lg = logits + (size_t)t * E;
+  const size_t pstride = (size_t)T * E;
+  float logit[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    float x = 0.f;
+    if (e < E)
+      for (int p = 0; p < n_partials; ++p) x += lg[p * pstride + e];
+    logit[i] = x;
+  }
+  select_topk<NPL>(logit, bias, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_scores + (size_t)warp * k, E, k,
+                   renorm, scale);
+}
+
 extern "C" int qb_router_topk(const float* logits, int n_partials, const float* bias, int* idx_out, float* w_out,
                               int T, int E, int k, int renorm, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (k <= 0 || k > E || n_partials <= 0) return QB_ERR_BAD_ARG;
   if (E > 1024) return QB_ERR_UNSUPPORTED;
+  if (T >= 64 && n_partials <= TOPK_WARP_MAX_PARTIALS) {
+    const int blocks = (T + TOPK_WARPS - 1) / TOPK_WARPS;
+    const size_t smem = (size_t)TOPK_WARPS * k * sizeof(float);       // at most 32 KB
+#define QB_ROUTE_W(N) router_topk_warp_kernel<N><<<blocks, TOPK_WARPS * 32, smem, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale)
+    if (E <= 32) QB_ROUTE_W(1);
+    else if (E <= 64) QB_ROUTE_W(2);
+    else if (E <= 128) QB_ROUTE_W(4);
+    else if (E <= 256) QB_ROUTE_W(8);
+    else if (E <= 512) QB_ROUTE_W(16);
+    else QB_ROUTE_W(32);
+#undef QB_ROUTE_W
+    QB_LAUNCH_CHECK();
+    return 0;
+  }
   // many threads add the partials side by side; the selecting warp's arrays set the register need for large E
   const int warps = E <= 256 ? 32 : 8, blocks = T;
 #define QB_ROUTE(N) router_topk_kernel<N><<<blocks, warps * 32, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale)

@@ -6,16 +6,19 @@
 // x * piece is exact in float32 and the sum runs in the float32 accumulators of mma.m16n8k16.  The inner
 // dimension is taken in chunks of 64: a chunk's sum starts from zero and is then added to the running
 // total, in chunk order, whatever the number of tokens, so a token's logits do not depend on the step.
+// The inner dimension is also cut into ranges of RG_KSPLIT (a constant), one block a range, whose sums
+// come out side by side, [ranges][T][E]; the selection kernel adds them in range order.
 // (src/quanta/minimax/moe.py:44, "logits = fp32(x) @ fp32(gate).T".)  Prompt portions use this kernel;
 // steps of few tokens keep the SIMT kernel, which reads the float32 gate once.
 //
-// Block = 64 tokens x 64 experts, four warps of 16 tokens each; operands come through shared memory in two
-// stages filled by cp.async.  Needs K % 8 == 0 (16-byte rows).
+// Block = 128 tokens x 64 experts, eight warps of 32 tokens x 32 experts each (a fragment of the gate serves
+// two fragments of tokens); operands come through shared memory in two stages filled by cp.async.  Needs K % 8 == 0 (16-byte rows).
 #include "common.cuh"
 
 namespace {
 
-constexpr int RG_BM = 64, RG_BN = 64, RG_BK = 64, RG_PAD = 8, RG_LD = RG_BK + RG_PAD, RG_THREADS = 128;
+constexpr int RG_BM = 128, RG_BN = 64, RG_BK = 64, RG_PAD = 8, RG_LD = RG_BK + RG_PAD, RG_THREADS = 256;
+constexpr int RG_KSPLIT = 768;      // inner-dimension range of one block: a multiple of RG_BK
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -42,10 +45,13 @@ router_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   __nv_bfloat16* ws = xs + 2 * RG_BM * RG_LD;                                // [2][3][RG_BN][RG_LD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.y * RG_BM, e0 = blockIdx.x * RG_BN;
-  const int n_stages = (K + RG_BK - 1) / RG_BK;
+  const int k_begin = blockIdx.z * RG_KSPLIT, k_end = min(K, k_begin + RG_KSPLIT);
+  const int n_stages = (k_end - k_begin + RG_BK - 1) / RG_BK;
+  const int wt = warp & 3, we = warp >> 2;      // this warp's 32 tokens and 32 experts of the block's
+  logits += (size_t)blockIdx.z * T * E;
 
   auto fetch = [&](int stage, int buf) {
-    const int k0 = stage * RG_BK;
+    const int k0 = k_begin + stage * RG_BK;
     // 64 rows x 8 chunks of 16 bytes per operand
     for (int c = tid; c < RG_BM * (RG_BK / 8); c += RG_THREADS) {
       const int r = c / (RG_BK / 8), kc = (c % (RG_BK / 8)) * 8;
@@ -62,9 +68,13 @@ router_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
-  float total[RG_BN / 8][4];
+  constexpr int NT = RG_BN / 2 / 8;             // accumulator tiles of 8 experts a warp
+  constexpr int MT = 2;                         // fragments of 16 tokens a warp
+  float total[MT][NT][4];
 #pragma unroll
-  for (int i = 0; i < RG_BN / 8; ++i) total[i][0] = total[i][1] = total[i][2] = total[i][3] = 0.f;
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int i = 0; i < NT; ++i) total[m][i][0] = total[m][i][1] = total[m][i][2] = total[m][i][3] = 0.f;
 
   fetch(0, 0);
   for (int s = 0; s < n_stages; ++s) {
@@ -76,41 +86,53 @@ router_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
       asm volatile("cp.async.wait_group 0;\n" ::);
     }
     __syncthreads();
-    float acc[RG_BN / 8][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < RG_BN / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    const __nv_bfloat16* xa = xs + ((size_t)buf * RG_BM + warp * 16) * RG_LD;
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int i = 0; i < NT; ++i) acc[m][i][0] = acc[m][i][1] = acc[m][i][2] = acc[m][i][3] = 0.f;
+    const __nv_bfloat16* xa = xs + ((size_t)buf * RG_BM + wt * 16 * MT) * RG_LD;
 #pragma unroll
     for (int kk = 0; kk < RG_BK / 16; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(a, xa + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * RG_LD + kk * 16 + 8 * (lane >> 4));
+      uint32_t a[MT][4];
 #pragma unroll
-      for (int np = 0; np < RG_BN / 16; ++np) {
+      for (int m = 0; m < MT; ++m)
+        ldmatrix_x4(a[m], xa + (size_t)(m * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * RG_LD + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
 #pragma unroll
         for (int p = 0; p < 3; ++p) {         // hi, then mid, then lo
-          const __nv_bfloat16* wb = ws + (((size_t)buf * 3 + p) * RG_BN + np * 16) * RG_LD;
+          const __nv_bfloat16* wb = ws + (((size_t)buf * 3 + p) * RG_BN + we * (RG_BN / 2) + np * 16) * RG_LD;
           uint32_t b[4];
           ldmatrix_x4(b, wb + (size_t)((lane & 7) + 8 * (lane >> 4)) * RG_LD + kk * 16 + 8 * ((lane >> 3) & 1));
-          mma16816(acc[2 * np], a, b[0], b[1]);
-          mma16816(acc[2 * np + 1], a, b[2], b[3]);
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            mma16816(acc[m][2 * np], a[m], b[0], b[1]);
+            mma16816(acc[m][2 * np + 1], a[m], b[2], b[3]);
+          }
         }
       }
     }
 #pragma unroll
-    for (int i = 0; i < RG_BN / 8; ++i) {
-      total[i][0] += acc[i][0]; total[i][1] += acc[i][1]; total[i][2] += acc[i][2]; total[i][3] += acc[i][3];
-    }
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        total[m][i][0] += acc[m][i][0]; total[m][i][1] += acc[m][i][1];
+        total[m][i][2] += acc[m][i][2]; total[m][i][3] += acc[m][i][3];
+      }
     __syncthreads();
   }
   // accumulator element: row (lane >> 2) + 8 * (i >> 1), column nt * 8 + (lane & 3) * 2 + (i & 1)
   const int g = lane >> 2, q = lane & 3;
 #pragma unroll
-  for (int nt = 0; nt < RG_BN / 8; ++nt)
+  for (int m = 0; m < MT; ++m)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int t = t0 + warp * 16 + g + 8 * (i >> 1), e = e0 + nt * 8 + q * 2 + (i & 1);
-      if (t < T && e < E) logits[(size_t)t * E + e] = total[nt][i];
-    }
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = t0 + wt * 16 * MT + m * 16 + g + 8 * (i >> 1), e = e0 + we * (RG_BN / 2) + nt * 8 + q * 2 + (i & 1);
+        if (t < T && e < E) logits[(size_t)t * E + e] = total[m][nt][i];
+      }
 }
 
 // out[p][i] = the p-th bfloat16 piece of w[i]: hi, mid, lo
@@ -138,7 +160,10 @@ extern "C" int qb_split3_bf16(const float* w, void* out, long long n, cudaStream
   return 0;
 }
 
-// x bf16 [T, K]; pieces bf16 [3, E, K] (qb_split3_bf16 of the float32 gate); logits float32 [T, E]
+// how many ranges the inner dimension is cut into: the first size of the logits
+extern "C" int qb_router_gemm_mma_parts(int K) { return K <= 0 ? 0 : (K + RG_KSPLIT - 1) / RG_KSPLIT; }
+
+// x bf16 [T, K]; pieces bf16 [3, E, K] (qb_split3_bf16 of the float32 gate); logits float32 [parts, T, E]
 extern "C" int qb_router_gemm_mma(const void* x, const void* pieces, float* logits, int T, int E, int K,
                                   cudaStream_t stream) {
   if (T <= 0 || E <= 0) return 0;
@@ -147,8 +172,8 @@ extern "C" int qb_router_gemm_mma(const void* x, const void* pieces, float* logi
   const size_t smem = (size_t)(2 * RG_BM + 2 * 3 * RG_BN) * RG_LD * sizeof(__nv_bfloat16);
   cudaError_t err = cudaFuncSetAttribute(router_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return (int)err;
-  dim3 grid((E + RG_BN - 1) / RG_BN, (T + RG_BM - 1) / RG_BM);
-  if (grid.y > 65535) return QB_ERR_UNSUPPORTED;
+  dim3 grid((E + RG_BN - 1) / RG_BN, (T + RG_BM - 1) / RG_BM, (K + RG_KSPLIT - 1) / RG_KSPLIT);
+  if (grid.y > 65535 || grid.z > 65535) return QB_ERR_UNSUPPORTED;
   router_gemm_mma_kernel<<<grid, RG_THREADS, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)pieces,
                                                             logits, T, E, K);
   QB_LAUNCH_CHECK();

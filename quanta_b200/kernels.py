@@ -252,14 +252,22 @@ def split3_bf16(w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def router_gemm_mma_parts(K: int) -> int:
+    """Ranges the inner dimension of ``router_gemm_mma`` is cut into (a function of K alone)."""
+    return int(lib().qb_router_gemm_mma_parts(int(K)))
+
+
 def router_gemm_mma(x: torch.Tensor, pieces: torch.Tensor, logits: torch.Tensor) -> None:
-    """``logits[T, E] = x[T, K] @ (pieces[0] + pieces[1] + pieces[2]).T`` in float32 on the tensor cores,
-    ``pieces`` from ``split3_bf16`` of the float32 gate; the inner dimension in fixed chunks of 64."""
+    """``sum_p logits[p, T, E] = x[T, K] @ (pieces[0] + pieces[1] + pieces[2]).T`` in float32 on the tensor
+    cores, ``pieces`` from ``split3_bf16`` of the float32 gate; the inner dimension in fixed chunks of 64,
+    and in ``router_gemm_mma_parts(K)`` fixed ranges whose sums ``router_topk`` adds in order."""
     T, K = x.shape
     _want(x, torch.bfloat16, "x"); _want(pieces, torch.bfloat16, "pieces"); _want(logits, torch.float32, "logits")
     E = pieces.shape[1]
-    if pieces.shape[0] != 3 or pieces.shape[2] != K or logits.numel() != T * E or not logits.is_contiguous():
-        raise ValueError("router_gemm_mma: shape mismatch")
+    parts = router_gemm_mma_parts(K)
+    if (pieces.shape[0] != 3 or pieces.shape[2] != K or logits.numel() != parts * T * E
+            or not logits.is_contiguous()):
+        raise ValueError(f"router_gemm_mma: shape mismatch (logits must be [{parts}, {T}, {E}])")
     _check(lib().qb_router_gemm_mma(_p(x), _p(pieces), _p(logits), T, E, K, _stream()), "router_gemm_mma")
 
 

@@ -88,7 +88,8 @@ class SigmoidTopKExperts(FeedForward):
         T = x.shape[0]
         if self.gate_pieces is not None and x.dtype == torch.bfloat16 and T >= self.router_mma_min_tokens:
             # many tokens: float32-accurate logits on the tensor cores (fixed chunks of the inner dimension)
-            logits = torch.empty((T, self.E), dtype=torch.float32, device=x.device)
+            logits = torch.empty((kernels.router_gemm_mma_parts(self.H), T, self.E), dtype=torch.float32,
+                                 device=x.device)
             kernels.router_gemm_mma(x, self.gate_pieces, logits)
         else:
             # the inner dimension is cut at fixed multiples of 128, whatever T: few rows still fill the GPU,

@@ -275,13 +275,15 @@ def test_router_gemm_mma(T, E, Kd):
     assert pieces.shape == (3, E, Kd)
     back = pieces[0].double() + pieces[1].double() + pieces[2].double()
     assert float((back - gate.double()).abs().max()) <= 2.0 ** -22 * float(gate.abs().max())
-    logits = torch.full((T, E), float("nan"), device=DEV)
+    parts = k.router_gemm_mma_parts(Kd)
+    assert parts == -(-Kd // 768)               # ranges of the inner dimension, a function of its size alone
+    logits = torch.full((parts, T, E), float("nan"), device=DEV)
     k.router_gemm_mma(x, pieces, logits)
     want = x.double() @ gate.double().T
-    assert torch.allclose(logits.double(), want, atol=2e-5, rtol=1e-5)
-    alone = torch.empty((1, E), device=DEV)
+    assert torch.allclose(logits.double().sum(0), want, atol=2e-5, rtol=1e-5)
+    alone = torch.empty((parts, 1, E), device=DEV)
     k.router_gemm_mma(x[T // 2: T // 2 + 1].contiguous(), pieces, alone)
-    assert torch.equal(alone[0], logits[T // 2])
+    assert torch.equal(alone[:, 0], logits[:, T // 2])
 
 
 @pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
@@ -303,15 +305,35 @@ def test_gemm_nt_simt(a_dtype, b_dtype):
                                                    (256, 8, True, True, 1.0), (33, 1, True, True, 1.0),
                                                    (520, 5, True, False, 0.5)])
 def test_router_topk(E, k, bias, renorm, scale):
-    T = 29
-    logits = torch.randn(T, E, device=DEV)
-    logits[3, :] = 0.25                     # a full tie: lower expert indices win
+    _router_topk_case(29, 1, E, k, bias, renorm, scale)
+
+
+@pytest.mark.parametrize("T,P,E,k", [(300, 1, 256, 8), (300, 4, 256, 8), (64, 3, 12, 3), (1000, 2, 520, 5), (77, 1, 1000, 9),
+                                     (129, 2, 33, 33)])
+def test_router_topk_many_tokens(T, P, E, k):
+    """Steps of many tokens select with one warp a token; partial logits are added in index order."""
+    _router_topk_case(T, P, E, k, True, True, 1.5)
+
+
+def _router_topk_case(T, P, E, k, bias, renorm, scale):
+    parts = torch.randn(P, T, E, device=DEV)
+    parts[:, 3, :] = 0.0
+    parts[0, 3, :] = 0.25                   # a full tie: lower expert indices win
+    logits = parts[0].clone()
+    for p in range(1, P):
+        logits += parts[p]                  # the kernel's order of additions
+    if P == 1:
+        parts = parts[0].contiguous()
+    _router_topk_check(parts, logits, T, E, k, bias, renorm, scale)
+
+
+def _router_topk_check(parts, logits, T, E, k, bias, renorm, scale):
     b = (0.05 * torch.randn(E, device=DEV)) if bias else None
     if bias:
         b[: E // 2] = 0.0
     idx = torch.empty(T, k, device=DEV, dtype=torch.int32)
     w = torch.empty(T, k, device=DEV)
-    K().router_topk(logits, b, idx, w, renorm, scale)
+    K().router_topk(parts, b, idx, w, renorm, scale)
     scores = torch.sigmoid(logits)
     choice = scores + b[None] if bias else scores
     want_idx = torch.argsort(-choice, dim=-1, stable=True)[:, :k]
