@@ -3,6 +3,7 @@
     python bench_kernels.py attn_decode  --batch 4 --context 131072
     python bench_kernels.py attn_span    --tokens 8192 --start 122880
     python bench_kernels.py attn_sweep                      # the cases quoted under profiles/
+    python bench_kernels.py router       --tokens 2048      # router logits + selection of a prompt portion
 
 Shapes default to the M2-family attention (48 q heads, 8 kv heads of 128, pages of 16 tokens).  Caches
 are random, pages are dealt in a random order, every request of a decode case has the same context.
@@ -37,6 +38,18 @@ def timed(fn, n: int = 10, warm: int = 3) -> float:
         ts.append(a.elapsed_time(b))
     ts.sort()
     return ts[len(ts) // 2]
+
+
+def timed_graph(fn, reps: int = 20) -> float:
+    """Median time of one call, ``reps`` calls captured back to back in a CUDA graph: the kernel's own
+    time for kernels that are shorter than the host's launch path."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            fn()
+    return timed(g.replay) / reps
 
 
 def attn_decode(batch: int, context: int, nq: int, nkv: int, hd: int, page: int) -> dict:
@@ -87,9 +100,27 @@ def attn_span(tokens: int, start: int, nq: int, nkv: int, hd: int, page: int) ->
             "TFLOP/s": round(flops / ms / 1e9, 1)}
 
 
+def router(tokens: int, hidden: int, experts: int, top_k: int) -> dict:
+    """Router logits (tensor cores, float32 gate in three bfloat16 pieces) and the selection of ``tokens``
+    tokens, each timed as twenty launches in a CUDA graph."""
+    x = torch.randn(tokens, hidden, device=DEV).bfloat16()
+    gate = torch.randn(experts, hidden, device=DEV) / hidden ** 0.5
+    pieces = k.split3_bf16(gate)
+    logits = torch.empty(k.router_gemm_mma_parts(hidden), tokens, experts, device=DEV)
+    bias = torch.zeros(experts, device=DEV)
+    idx = torch.empty(tokens, top_k, dtype=torch.int32, device=DEV)
+    w = torch.empty(tokens, top_k, device=DEV)
+    t_gemm = timed_graph(lambda: k.router_gemm_mma(x, pieces, logits))
+    t_sel = timed_graph(lambda: k.router_topk(logits, bias, idx, w, True, 1.0))
+    flops = 2.0 * 3 * tokens * experts * hidden
+    return {"kernel": "router_gemm_mma + router_topk", "tokens": tokens, "hidden": hidden, "experts": experts,
+            "top_k": top_k, "gemm_us": round(t_gemm * 1e3, 1), "gemm_TFLOP/s": round(flops / t_gemm / 1e9, 1),
+            "topk_us": round(t_sel * 1e3, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["attn_decode", "attn_span", "attn_sweep"])
+    ap.add_argument("what", choices=["attn_decode", "attn_span", "attn_sweep", "router"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -98,12 +129,17 @@ def main() -> None:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--hidden", type=int, default=3072)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--top-k", type=int, default=8)
     a = ap.parse_args()
     shape = (a.q_heads, a.kv_heads, a.head_dim, a.page)
     if a.what == "attn_decode":
         print(json.dumps(attn_decode(a.batch, a.context, *shape)), flush=True)
     elif a.what == "attn_span":
         print(json.dumps(attn_span(a.tokens, a.start, *shape)), flush=True)
+    elif a.what == "router":
+        print(json.dumps(router(a.tokens, a.hidden, a.experts, a.top_k)), flush=True)
     else:
         for batch, context in [(1, 4096), (8, 4096), (64, 4096), (32, 16384), (8, 32768), (1, 131072), (4, 131072)]:
             print(json.dumps(attn_decode(batch, context, *shape)), flush=True)
