@@ -744,20 +744,20 @@ attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (raise) {
-          const float f = ex2(m_ref - m_true);              // reference -inf: 0
-          l *= f;
+        // tcgen05.ld / st / wait are .sync.aligned: the WHOLE warp runs them, whichever of its rows raise
+        // (a row that does not multiplies by exactly 1); run by some lanes only they can hang the warp
+        const float f = raise ? ex2(m_ref - m_true) : 1.f;  // reference -inf: 0
+        l *= f;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[16];
-            tmem_ld16(o_addr + (uint32_t)(c * 16), v);
-            tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[16];
+          tmem_ld16(o_addr + (uint32_t)(c * 16), v);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st16(o_addr + (uint32_t)(c * 16), v);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st16(o_addr + (uint32_t)(c * 16), v);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       if (raise) m_ref = m_true;
       const float msafe = m_ref == -INFINITY ? 0.f : m_ref;

@@ -234,6 +234,52 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
         assert torch.allclose(out.float().cpu(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("impl", ["tc", "tc_two_tiles", "mma_only"])
+def test_span_attention_maximum_grows_late_in_some_rows(impl, monkeypatch):
+    """A portion whose rows meet a key that dwarfs all earlier ones only in a LATER block of keys, and only
+    some rows of each warp do (others never, others in two blocks): the kernel that keeps O in TMEM rescales
+    it then, with instructions that the whole warp must run together whichever of its rows need it."""
+    k = K()
+    nq, nkv, hd, page = 4, 2, 128, 16
+    assert k.attn_span_tc_supported(nq, nkv, hd, page)
+    if impl != "tc":
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc2")
+    torch.manual_seed(7)
+    first, n = 300, 100                        # 200 rows a kv head: two tiles, the second not full
+    tok_pos = torch.arange(first, first + n, dtype=torch.int32)
+    tok_req = torch.zeros(n, dtype=torch.int32)
+    max_pages = -(-(first + n) // page)
+    ids = list(range(max_pages + 3))
+    random.Random(3).shuffle(ids)
+    table = torch.tensor([ids[:max_pages]], dtype=torch.int32)
+    kc = torch.randn(len(ids), nkv, page, hd, device=DEV).bfloat16()
+    vc = torch.randn(len(ids), nkv, page, hd, device=DEV).bfloat16()
+    q = torch.randn(n, nq, hd, device=DEV).bfloat16()
+    q[:, :, :2] = 0
+    # keys 200 (second block of 128) and 290 (third) stand out along dimensions 0 and 1; only the rows
+    # that look along a dimension see it
+    for key, dim in ((200, 0), (290, 1)):
+        pg, sl = int(table[0, key // page]), key % page
+        kc[pg, :, sl] = 0
+        kc[pg, :, sl, dim] = 30.0 * (dim + 1)
+    rows_a = torch.arange(n) % 3 == 0          # grows in the second block
+    rows_b = torch.arange(n) % 5 == 0          # grows in the third (again, for the rows of both)
+    q[rows_a, :, 0] = 8.0
+    q[rows_b, 1::2, 1] = 8.0                   # every other head: the two rows of a token differ
+    scale = hd ** -0.5
+    out = torch.full_like(q, float("nan"))
+    st = k.new_status(DEV)
+    G = nq // nkv
+    tiles = [[0, 0, n, x] for x in range(0, n * G, k.attn_span_rows(hd, nq, nkv, page))]
+    k.attn_span(q, kc, vc, out, tok_pos.to(DEV), table.to(DEV), torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                scale, 0, st)
+    assert int(st[0]) == 0
+    want = attention_reference(q, kc, vc, table.tolist(), tok_pos, tok_req, scale, 0)
+    assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
+    pg, sl = int(table[0, 290 // page]), 290 % page
+    assert torch.allclose(out[0, 1].float().cpu(), vc[pg, 0, sl].float().cpu(), atol=0.05)     # token 0: both subsets
+
+
 @pytest.mark.parametrize("n_dec,nq,nkv,hd,page", [(300, 4, 2, 64, 16), (70, 6, 1, 128, 8), (530, 2, 2, 32, 4)])
 def test_decode_attention_many_tokens(n_dec, nq, nkv, hd, page):
     """More single tokens than one launch of the decode kernel takes (their positions live in shared
