@@ -7,7 +7,8 @@ One JSON line on standard output.  A "step" is one decode step of the whole batc
 has the layer sizes of the baseline's third configuration (hidden 3072, 48 q / 8 kv heads of 128,
 rotary 64, 256 experts top-8 of width 1536, vocabulary 200064) with seeded random weights, 16 of the
 model's 62 layers (about 120 GB of bfloat16 weights), a batch of 8 requests that have each read a
-2,048-token prompt, and a cache sized for the 4,096-token context.
+2,048-token prompt and then decode 256 steps (the default K), and a cache sized for the 4,096-token
+context.
 
 * ``value``: decoded tokens a second, timed on the device with CUDA events around every step (the
   step function and the sampling kernel), after warm-up steps.  Each step reads tens of GB of
@@ -15,7 +16,9 @@ model's 62 layers (about 120 GB of bfloat16 weights), a batch of 8 requests that
 * ``e2e``: the same through the Python entry point (``LLM``): host token ids in, sampled ids out,
   every step with its pinned host->device copy of the step's integers and device->host read of
   the sampled ids.
-* ``prefill``: one 2,048-token prompt as one step: tokens a second, and flops / time / tensor peak.
+* ``prefill``: one 2,048-token prompt as one step: tokens a second, and flops / time / tensor peak
+  (``frac``); the step reads all 256 experts of every layer for 64 rows each, so it is bound by memory:
+  ``hbm_frac`` is its weight bytes / time / copy bandwidth.
 * ``roofline``: bytes the decode step has to read (each weight it uses once, counted from the
   experts the router really chose, plus the cache of the live requests) / time / copy bandwidth.
 * ``points``: decode at batch 1 and 64.
@@ -180,8 +183,11 @@ def run_ours(args) -> dict:
         pre_ms.append(a.elapsed_time(b))
     pre = statistics.median(pre_ms[3:])
     pf = prefill_flops(raw, layers, pf_tokens)
+    # the step reads every expert once: its bytes / time / copy bandwidth says how close to ITS bound it runs
+    pf_bytes = decode_bytes(model, raw, layers, [], [cfg.num_local_experts] * layers)
     prefill = {"value": round(pf_tokens / pre * 1e3, 1), "tokens": pf_tokens, "ms": round(pre, 3),
-               "frac": round(pf / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pf / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "hbm_frac": round(pf_bytes / (pre * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)}
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---- decode, device-timed ----
@@ -194,7 +200,7 @@ def run_ours(args) -> dict:
         kernels.LAUNCHES = 0
         ms = timed_steps(lambda i: [StepEntry(rid, [rng.randrange(V)], (0,)) for rid in rids], n_warm, n_timed, True)
         launches = kernels.LAUNCHES * n_timed // (n_warm + n_timed)
-        ctx = [eng.manager.length(rid) for rid in rids]
+        ctx = [eng.manager.length(rid) - n_timed // 2 for rid in rids]      # keys a request has in the middle timed step
         distinct = []
         for blk in model.blocks:
             ff = blk.feed_forward
@@ -257,7 +263,7 @@ def run_ours(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=16, help="layers built (the model has 62)")
@@ -278,6 +284,9 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.prompt_len + args.warmup + args.steps + 1 > args.context:
+        ap.error(f"--context {args.context} is too short for prompts of {args.prompt_len} tokens and "
+                 f"{args.warmup} + {args.steps} + 1 decoded tokens")
     out = run_ours(args)
     print(json.dumps(out))
     return 0

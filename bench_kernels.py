@@ -4,6 +4,7 @@
     python bench_kernels.py attn_span    --tokens 8192 --start 122880
     python bench_kernels.py attn_sweep                      # the cases quoted under profiles/
     python bench_kernels.py router       --tokens 2048      # router logits + selection of a prompt portion
+    python bench_kernels.py experts      --tokens 8         # routed experts of one layer: plan, gather, two products
 
 Shapes default to the M2-family attention (48 q heads, 8 kv heads of 128, pages of 16 tokens).  Caches
 are random, pages are dealt in a random order, every request of a decode case has the same context.
@@ -118,9 +119,53 @@ def router(tokens: int, hidden: int, experts: int, top_k: int) -> dict:
             "topk_us": round(t_sel * 1e3, 1)}
 
 
+def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int) -> dict:
+    """The routed experts of one layer for a step of ``tokens`` tokens (random routing, a fresh one each
+    call so that no call finds its experts in L2): expert plan, row gather and the two tcgen05 products, each
+    timed as launches in a CUDA graph.  ``GB/s`` counts the weights of the distinct experts once."""
+    w13 = torch.empty(n_experts, 2 * width, hidden, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02)
+    w2 = torch.empty(n_experts, hidden, width, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02)
+    n_pairs, st = tokens * top_k, k.new_status(DEV)
+    bm = k.expert_tile_rows(tokens, n_pairs / n_experts)
+    plan_words, max_tiles = k.moe_plan_sizes(n_pairs, n_experts, bm)
+    sets, distinct = [], []
+    for i in range(4):
+        x = torch.randn(tokens, hidden, device=DEV).bfloat16()
+        idx = torch.stack([torch.randperm(n_experts, device=DEV)[:top_k] for _ in range(tokens)]).int()
+        w = torch.rand(tokens, top_k, device=DEV)
+        plan = torch.empty(plan_words, dtype=torch.int32, device=DEV)
+        sp = torch.empty(n_pairs, dtype=torch.int32, device=DEV)
+        te, tr = (torch.empty(max_tiles, dtype=torch.int32, device=DEV) for _ in range(2))
+        xg = torch.empty(n_pairs, hidden, device=DEV, dtype=torch.bfloat16)
+        act = torch.empty(n_pairs, width, device=DEV, dtype=torch.bfloat16)
+        y = torch.empty(n_pairs, hidden, device=DEV)
+        k.moe_plan(idx, n_experts, bm, plan, sp, te, tr, st)
+        k.gather_rows(x, xg, sp, top_k)
+        sets.append((x, idx, w, plan, sp, te, tr, xg, act, y))
+        distinct.append(int(idx.unique().numel()))
+    calls = {
+        "plan": lambda s: k.moe_plan(s[1], n_experts, bm, s[3], s[4], s[5], s[6], st),
+        "gather": lambda s: k.gather_rows(s[0], s[7], s[4], top_k),
+        "up": lambda s: k.expert_gemm_tc(1, s[7], w13, s[8], s[4], s[2].view(-1), s[3], s[5], s[6], n_experts, bm, st),
+        "down": lambda s: k.expert_gemm_tc(2, s[8], w2, s[9], s[4], s[2].view(-1), s[3], s[5], s[6], n_experts, bm, st),
+    }
+    out = {"kernel": "moe_plan + gather_rows + expert_gemm_tc", "tokens": tokens, "hidden": hidden, "width": width,
+           "experts": n_experts, "top_k": top_k, "tile_rows": bm, "distinct_experts": round(sum(distinct) / 4, 1)}
+    for name, fn in calls.items():
+        def four(fn=fn):
+            for s in sets:
+                fn(s)
+        out[f"{name}_us"] = round(timed_graph(four, reps=5) / 4 * 1e3, 1)
+    gb = sum(distinct) / 4 * hidden * width * 2 / 1e9
+    out["up_GB/s"] = round(2 * gb / (out["up_us"] * 1e-6), 0)
+    out["down_GB/s"] = round(gb / (out["down_us"] * 1e-6), 0)
+    assert int(st[0]) == 0
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["attn_decode", "attn_span", "attn_sweep", "router"])
+    ap.add_argument("what", choices=["attn_decode", "attn_span", "attn_sweep", "router", "experts"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -132,12 +177,15 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=3072)
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--top-k", type=int, default=8)
+    ap.add_argument("--width", type=int, default=1536, help="inner size of an expert")
     a = ap.parse_args()
     shape = (a.q_heads, a.kv_heads, a.head_dim, a.page)
     if a.what == "attn_decode":
         print(json.dumps(attn_decode(a.batch, a.context, *shape)), flush=True)
     elif a.what == "attn_span":
         print(json.dumps(attn_span(a.tokens, a.start, *shape)), flush=True)
+    elif a.what == "experts":
+        print(json.dumps(experts(a.tokens, a.hidden, a.width, a.experts, a.top_k)), flush=True)
     elif a.what == "router":
         print(json.dumps(router(a.tokens, a.hidden, a.experts, a.top_k)), flush=True)
     else:

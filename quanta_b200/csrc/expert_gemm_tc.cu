@@ -348,7 +348,16 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   // Two blocks share an SM (shared memory is the limit), so that one block's prologue and epilogue run
   // under the other's main loop; each gets a ring of about 105 KB.
   // a tile of 256 token rows has a block to itself on its SM (its two accumulators fill the TMEM)
-  int stages = (int)((size_t)(NT > 128 ? 200 * 1024 : 105 * 1024) / stage_bytes);
+  // and so has every block of a launch of no more blocks than there are SMs (a single token's step)
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sms = 1;
+  }
+  const size_t blocks = (size_t)((N_out + EG_M - 1) / EG_M) * (size_t)max_tiles;
+  const bool alone = NT > 128 || blocks <= (size_t)sms;
+  int stages = (int)((size_t)(alone ? 200 * 1024 : 105 * 1024) / stage_bytes);
   if (stages > 8) stages = 8;
   const int k_blocks = (K + EG_BK - 1) / EG_BK;
   if (stages > k_blocks) stages = k_blocks;
