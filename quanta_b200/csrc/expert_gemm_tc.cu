@@ -133,7 +133,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
                       void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
                       const int* __restrict__ plan, const int* __restrict__ tile_expert,
                       const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
-                      int tmem_cols, int* status) {
+                      int tmem_cols, int gather_k, int* status) {
   constexpr int NM = MODE == 1 ? 2 : 1;
   extern __shared__ unsigned char smem_dyn[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
@@ -174,6 +174,10 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       s_pair[i] = pr;
       s_w[i] = i < rows ? pair_w[pr] : 0.f;
     }
+  } else if (gather_k > 0) {
+    // the token rows are fetched one by one from the step's activations: row i of the tile is the token
+    // of the i-th pair of this expert
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) s_pair[i] = sorted_pair[row0 + i] / gather_k;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -192,10 +196,19 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (!mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag)) break;
         const uint32_t full = smem_u32(&sh.full[s]);
         unsigned char* st = tiles + (size_t)s * stage_bytes;
-        mbar_expect_tx(full, stage_bytes);
+        const bool by_row = MODE == 1 && gather_k > 0;
+        mbar_expect_tx(full, by_row ? NM * a_bytes + (uint32_t)rows * EG_BK * 2 : stage_bytes);
         tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full, pol_w);
         if (MODE == 1) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + N_out, full, pol_w);
-        tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full, pol_x);
+        if (by_row) {
+          // boxes of one row: the swizzle follows the shared-memory address, so row i lands where a box of
+          // NT rows would have put it; the rows past the expert's last keep what the stage held before, and
+          // their columns of the product are never read
+          for (int i = 0; i < rows; ++i)
+            tma_load_2d(smem_u32(st + NM * a_bytes + i * (EG_BK * 2)), &tm_x, kb * EG_BK, s_pair[i], full, pol_x);
+        } else {
+          tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full, pol_x);
+        }
         armed = kb + 1;
       }
       if (*abort_flag) {
@@ -327,13 +340,15 @@ extern "C" int qb_gather_rows(const void* x, void* out, const int* sorted_pair, 
   return 0;
 }
 
-// x_rows: bf16 [n_pairs, K] in sorted order (mode 1: the gathered activations; mode 2: the act rows).
+// x_rows: bf16 [n_pairs, K] in sorted order (mode 1: the gathered activations; mode 2: the act rows); or,
+// mode 1 with gather_k > 0, the step's activations [n_rows, K] themselves: the kernel fetches the row of
+// token sorted_pair[p] / gather_k for pair p (one TMA box a row: for steps of few tokens).
 // weights: bf16 [E, (mode 1 ? 2 : 1) * N_out, K].  NT: token tile (16..256, a multiple of 16); the plan's
 // tile list must have been made with the same NT.
 extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weights, void* out, const int* sorted_pair,
                                  const float* pair_w, const int* plan, const int* tile_expert, const int* tile_row0,
-                                 int max_tiles, int n_pairs, int E, int K, int N_out, int NT, int* status,
-                                 cudaStream_t stream) {
+                                 int max_tiles, int n_pairs, int E, int K, int N_out, int NT, int gather_k, int n_rows,
+                                 int* status, cudaStream_t stream) {
   if (max_tiles <= 0 || n_pairs <= 0) return 0;
   if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
   if (mode != 1 && mode != 2) return QB_ERR_BAD_ARG;
@@ -342,7 +357,9 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   CUtensorMap tm_w, tm_x;
   int rc = make_map(&tm_w, weights, (uint64_t)E * nm * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
-  rc = make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)NT);
+  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0))) return QB_ERR_BAD_ARG;
+  rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)
+                    : make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)NT);
   if (rc) return rc;
   const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)NT * EG_BK * 2;
   // Two blocks share an SM (shared memory is the limit), so that one block's prologue and epilogue run
@@ -371,12 +388,12 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
     err = cudaFuncSetAttribute(expert_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     expert_gemm_tc_kernel<1><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
-                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, status);
+                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, gather_k, status);
   } else {
     err = cudaFuncSetAttribute(expert_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     expert_gemm_tc_kernel<2><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
-                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, status);
+                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, 0, status);
   }
   QB_LAUNCH_CHECK();
   return 0;

@@ -385,20 +385,25 @@ def gather_rows(x, out, sorted_pair, top_k: int) -> None:
 
 
 def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
-                   n_experts: int, tile_rows: int, status) -> None:
+                   n_experts: int, tile_rows: int, status, gather_top_k: int = 0) -> None:
     """Expert products on tcgen05/TMEM fed by TMA.  ``x_rows`` bf16 [pairs, K] in expert order; mode 1:
     ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32).  The plan's
-    tile list must have been made with ``bm = tile_rows``."""
-    n_pairs, K = x_rows.shape
+    tile list must have been made with ``bm = tile_rows``.  Mode 1 with ``gather_top_k`` > 0: ``x_rows`` is the
+    step's activations [T, K] and the kernel fetches the row of token ``pair // gather_top_k`` itself, one
+    TMA box a row (for steps of few tokens: it saves the gathered copy and its launch)."""
+    n_x, K = x_rows.shape
+    n_pairs = sorted_pair.numel()
     N = out.shape[1]
     want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
     if tuple(weights.shape) != want:
         raise ValueError(f"expert_gemm_tc: weights {tuple(weights.shape)} != {want}")
+    if gather_top_k == 0 and n_x != n_pairs:
+        raise ValueError(f"expert_gemm_tc: {n_x} rows for {n_pairs} pairs")
     _want(x_rows, torch.bfloat16, "x_rows"); _want(weights, torch.bfloat16, "weights")
     _want(out, torch.bfloat16 if mode == 1 else torch.float32, "out")
     _check(lib().qb_expert_gemm_tc(mode, _p(x_rows), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan),
                                    _p(tile_expert), _p(tile_row0), tile_expert.numel(), n_pairs, n_experts, K, N,
-                                   int(tile_rows), _p(status), _stream()), "expert_gemm_tc")
+                                   int(tile_rows), int(gather_top_k), n_x, _p(status), _stream()), "expert_gemm_tc")
 
 
 def sample_rows(logits, fparams, iparams, out) -> None:

@@ -73,6 +73,7 @@ class SigmoidTopKExperts(FeedForward):
     stream_max_tokens = 0
     router_mma_min_tokens = 256      # steps of fewer tokens read the float32 gate once on the CUDA cores
     fused_plan_max_tokens = 64       # steps of at most this many tokens select and plan in one launch
+    gather_in_kernel_max_tokens = 64 # and their expert products fetch the token rows without a gathered copy
 
     def path_for(self, x) -> str:
         ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
@@ -145,10 +146,15 @@ class SigmoidTopKExperts(FeedForward):
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
         if path == "tc":
             # bfloat16: TMA-fed tcgen05 products, weights as the 128-row operand, accumulators in TMEM
-            xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
-            kernels.gather_rows(x, xg, sorted_pair, self.k)
-            kernels.expert_gemm_tc(1, xg, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert, tile_row0,
-                                   self.E, bm, ctx.status)
+            if T <= self.gather_in_kernel_max_tokens:
+                # few tokens: the kernel fetches each pair's token row itself
+                kernels.expert_gemm_tc(1, x, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert,
+                                       tile_row0, self.E, bm, ctx.status, gather_top_k=self.k)
+            else:
+                xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
+                kernels.gather_rows(x, xg, sorted_pair, self.k)
+                kernels.expert_gemm_tc(1, xg, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert, tile_row0,
+                                       self.E, bm, ctx.status)
             kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                    tile_expert, tile_row0, self.E, bm, ctx.status)
         elif path == "stream":
