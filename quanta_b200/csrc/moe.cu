@@ -253,50 +253,49 @@ __global__ void moe_scatter_kernel(const int* __restrict__ idx, int n_pairs, int
 // The whole plan in one block, for steps with few pairs (decoding): counts in shared memory, the same
 // scans as above, then the scatter.  One launch instead of a memset and three kernels.
 struct PlanShared {
-  int cnt[1024], til[1024], act[1024], cur[1024];
+  int cur[1024];
+  int warp_tot[32][3];
 };
 
-// A block of 1024 threads; idx is read past L1 (another block of the same launch may have written it).
+// The plan of up to 4096 pairs by the first NTH threads of a block (NTH >= E, a multiple of 32), thread e
+// for expert e; `sync` is a barrier of exactly these threads.  Counts by shared-memory atomics, the three
+// prefix sums (rows, tiles, active experts) by warp shuffles and one pass over the warps' totals.  idx is
+// read past L1 (another block of the same launch may have written it).
+template <int NTH, typename Sync>
 __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int E, int BM, int* __restrict__ plan,
                                                 int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
                                                 int* __restrict__ tile_row0, int max_tiles, int* status,
-                                                PlanShared& sh) {
-  int* s_cnt = sh.cnt;
-  int* s_til = sh.til;
-  int* s_act = sh.act;
+                                                PlanShared& sh, Sync sync) {
   int* s_cur = sh.cur;
-  const int e = threadIdx.x;
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   s_cur[e] = 0;
-  __syncthreads();
-  for (int i = e; i < n_pairs; i += 1024) {
+  sync();
+  for (int i = e; i < n_pairs; i += NTH) {
     const int x = __ldcg(idx + i);
     if (x < 0 || x >= E) { qb_set_status(status, QB_STATUS_BAD_EXPERT, x, 4); continue; }
     atomicAdd(&s_cur[x], 1);
   }
-  __syncthreads();
+  sync();
   const int c = e < E ? s_cur[e] : 0;
   const int nt = (c + BM - 1) / BM;
-  s_cnt[e] = c;
-  s_til[e] = nt;
-  s_act[e] = c > 0;
-  __syncthreads();
-  for (int o = 1; o < 1024; o <<= 1) {
-    int a = 0, b = 0, d = 0;
-    if (e >= o) { a = s_cnt[e - o]; b = s_til[e - o]; d = s_act[e - o]; }
-    __syncthreads();
-    s_cnt[e] += a;
-    s_til[e] += b;
-    s_act[e] += d;
-    __syncthreads();
+  int sc = c, st = nt, sa = c > 0;             // inclusive sums over the experts up to e
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, sc, o), b = __shfl_up_sync(0xffffffffu, st, o),
+              d = __shfl_up_sync(0xffffffffu, sa, o);
+    if (lane >= o) { sc += a; st += b; sa += d; }
   }
-  const int off = s_cnt[e] - c, toff = s_til[e] - nt;
+  if (lane == 31) { sh.warp_tot[warp][0] = sc; sh.warp_tot[warp][1] = st; sh.warp_tot[warp][2] = sa; }
+  sync();
+  for (int w = 0; w < warp; ++w) { sc += sh.warp_tot[w][0]; st += sh.warp_tot[w][1]; sa += sh.warp_tot[w][2]; }
+  const int off = sc - c, toff = st - nt;
   int* counts = plan;
   int* offsets = plan + 2 * E;
   int* num_tiles = plan + 3 * E + 1;
   int* active = plan + 3 * E + 4;
   if (e < E) { counts[e] = c; offsets[e] = off; }
-  if (c > 0) active[s_act[e] - 1] = e;
-  if (e == E - 1) { offsets[E] = s_cnt[e]; num_tiles[0] = min(s_til[e], max_tiles); num_tiles[1] = s_act[e]; }
+  if (c > 0) active[sa - 1] = e;
+  if (e == E - 1) { offsets[E] = sc; num_tiles[0] = min(st, max_tiles); num_tiles[1] = sa; }
   for (int i = 0; i < nt; ++i) {
     if (toff + i < max_tiles) {
       tile_expert[toff + i] = e;
@@ -304,19 +303,21 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
     }
   }
   s_cur[e] = off;                     // running write position of each expert
-  __syncthreads();
-  for (int i = e; i < n_pairs; i += 1024) {
+  sync();
+  for (int i = e; i < n_pairs; i += NTH) {
     const int x = __ldcg(idx + i);
     if (x < 0 || x >= E) continue;
     sorted_pair[atomicAdd(&s_cur[x], 1)] = i;
   }
 }
 
-__global__ void moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
-                                      int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
-                                      int* __restrict__ tile_row0, int max_tiles, int* status) {
+__global__ void __launch_bounds__(1024)
+moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, int* __restrict__ plan,
+                      int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                      int* __restrict__ tile_row0, int max_tiles, int* status) {
   __shared__ PlanShared sh;
-  plan_small_body(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh);
+  plan_small_body<1024>(idx, n_pairs, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
+                        [] { __syncthreads(); });
 }
 
 // Routing and the plan of a step of few tokens in one launch: one block a token selects; the block that
@@ -342,9 +343,11 @@ router_topk_plan_kernel(const float* __restrict__ logits, int n_partials, const 
     if (s_last) *counter = 0;         // every other block has counted already
   }
   __syncthreads();
-  if (!s_last) return;
+  // the plan needs a thread an expert (at most 256 here): the block's other warps are done
+  if (!s_last || threadIdx.x >= 256) return;
   __threadfence();
-  plan_small_body(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh);
+  plan_small_body<256>(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
+                       [] { asm volatile("bar.sync 1, 256;" ::: "memory"); });
 }
 
 // counter: one int32 that is zero before the call and zero after it
