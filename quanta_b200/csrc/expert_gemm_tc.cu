@@ -168,13 +168,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
                  ::"r"(smem_u32(&sh.tmem_base)), "r"((uint32_t)tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (MODE == 2) {
-    for (int i = threadIdx.x; i < NT; i += blockDim.x) {
-      const int pr = i < rows ? sorted_pair[row0 + i] : 0;
-      s_pair[i] = pr;
-      s_w[i] = i < rows ? pair_w[pr] : 0.f;
-    }
-  } else if (gather_k > 0) {
+  if (MODE == 1 && gather_k > 0) {
     // the token rows are fetched one by one from the step's activations: row i of the tile is the token
     // of the i-th pair of this expert
     for (int i = threadIdx.x; i < rows; i += blockDim.x) s_pair[i] = sorted_pair[row0 + i] / gather_k;
@@ -253,6 +247,16 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     // ---------------- epilogue: 4 warps, one TMEM lane quadrant each ----------------
     const int quad = warp & 3;
     const int feat = j0 + quad * 32 + lane;
+    if (MODE == 2) {
+      // where each row goes and its routing weight: fetched here, under the main loop, by the warps that
+      // need them at its end (two dependent reads that the producer and the issuer do not wait for)
+      for (int i = threadIdx.x - 64; i < NT; i += 128) {
+        const int pr = i < rows ? sorted_pair[row0 + i] : 0;
+        s_pair[i] = pr;
+        s_w[i] = i < rows ? pair_w[pr] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+    }
     if (mbar_wait(smem_u32(&sh.tmem_full), 0u, abort_flag)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -374,7 +378,11 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   }
   const size_t blocks = (size_t)((N_out + EG_M - 1) / EG_M) * (size_t)max_tiles;
   const bool alone = NT > 128 || blocks <= (size_t)sms;
+  // Token tiles of at most 32 rows (decode steps of a few tokens: short blocks, one expert's 128 features
+  // each): three blocks an SM with rings of about 70 KB hide a block's prologue and epilogue better than
+  // two with 105 KB (measured at 8 tokens: 154 + 80 us against 161 + 86 us for the two products of a layer).
   int stages = (int)((size_t)(alone ? 200 * 1024 : 105 * 1024) / stage_bytes);
+  if (!alone && NT <= 32 && 72000 / stage_bytes >= 2) stages = (int)(72000 / stage_bytes);    // three blocks an SM
   if (stages > 8) stages = 8;
   const int k_blocks = (K + EG_BK - 1) / EG_BK;
   if (stages > k_blocks) stages = k_blocks;
