@@ -14,8 +14,9 @@
 //              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32).
 //   (src/quanta/minimax/moe.py:59-88; rows p sorted by expert, see the plan kernels.)
 //
-// The token rows must be contiguous in p order: MODE 1 reads a gathered copy of x (gather kernel
-// below), MODE 2 reads the act rows MODE 1 wrote.  Rows past the expert's last row compute garbage
+// The token rows are read in p order: MODE 1 reads a gathered copy of x (gather kernel below) as one box a
+// stage, or, for steps of few tokens, the rows of x themselves as one box of one row each (gather_k);
+// MODE 2 reads the act rows MODE 1 wrote.  Rows past the expert's last row compute garbage
 // that the epilogue drops; TMA zero-fills past the end of a tensor, so K need not be a multiple of 64
 // (it must be a multiple of 8: 16-byte rows).  No multicast, no clusters: every tile comes from this
 // GPU's memory through a plain per-block TMA load.
