@@ -2,9 +2,16 @@
 
 Key names, defaults and refusals follow the reference's parsers: the flat M2 schema
 (src/quanta/minimax/config.py:136-188) and, when ``text_config`` is present, the same names inside
-it with ``rotary_dim`` falling back to ``round(head_dim * partial_rotary_factor)``
-(src/quanta/minimax/config_m3.py:248-249).  eos/bos come from ``generation_config.json`` first,
-then the config, then 200020 / 200019 (config.py:154-155, 183-185).
+it with the nested parser's own defaults (src/quanta/minimax/config_m3.py:223-315): ``rotary_dim``
+falls back to ``round(head_dim * partial_rotary_factor)``, ``rope_theta`` to 5e6, ``qk_norm_type`` to
+``"per_head"``, ``hidden_act`` to ``"swigluoai"`` (which this decoder refuses, so a nested config has to
+say ``"silu"``), ``max_position_embeddings`` to 1048576.  eos/bos come from ``generation_config.json``
+first, then the config, then 200020 / 200019 (config.py:154-155, 183-185).
+
+Keys that change the layer math of the M3 checkpoints and that this decoder does not build are read
+and refused, never ignored: ``use_gemma_norm`` (gains applied as 1 + w), ``attention_output_gate``,
+dense layers (a 0 in ``moe_layer_freq``), ``n_shared_experts``, block-sparse attention
+(``sparse_attention_config.use_sparse_attention``).
 
 Every size and constant the layers use is a field here; no part reads anything else.
 """
@@ -48,6 +55,12 @@ class MiniMaxM3Config:
     routed_scaling_factor: float = 1.0
     shared_intermediate_size: int = 0
     hidden_act: str = "silu"
+    # options of the M3 checkpoints that change the math and are refused when set
+    use_gemma_norm: bool = False
+    attention_output_gate: bool = False
+    moe_layer_freq: tuple[int, ...] = ()          # 1 = routed experts; () = every layer
+    n_shared_experts: int = 0
+    use_sparse_attention: bool = False
     # norms / positions / tokens
     rms_norm_eps: float = 1e-6
     max_position_embeddings: int = 204800
@@ -84,7 +97,11 @@ class MiniMaxM3Config:
     @classmethod
     def from_dict(cls, raw: dict, generation: dict | None = None) -> "MiniMaxM3Config":
         gen = generation or {}
-        c = raw.get("text_config", raw)
+        nested = isinstance(raw.get("text_config"), dict)
+        c = raw["text_config"] if nested else raw
+        # the two parsers of the reference differ in what an absent key means
+        d_theta, d_norm, d_act, d_maxpos = (5e6, "per_head", "swigluoai", 1048576) if nested else \
+                                           (1e6, "per_layer", "silu", 204800)
         missing = [k for k in _REQUIRED if k not in c]
         if missing:
             raise ConfigError(f"config.json lacks required key(s): {', '.join(missing)}")
@@ -106,6 +123,7 @@ class MiniMaxM3Config:
         archs = tuple(raw.get("architectures") or ("MiniMaxM3ForCausalLM",))
         extra = {k: c[k] for k in ("use_mtp", "num_mtp_modules", "mtp_transformer_layers",
                                    "quantization_config") if k in c}
+        sparse = c.get("sparse_attention_config") or {}
         cfg = cls(
             vocab_size=int(c["vocab_size"]), hidden_size=int(c["hidden_size"]),
             intermediate_size=int(c["intermediate_size"]), num_hidden_layers=n_layers,
@@ -113,19 +131,24 @@ class MiniMaxM3Config:
             num_key_value_heads=int(c["num_key_value_heads"]), head_dim=head_dim,
             num_local_experts=int(c["num_local_experts"]),
             num_experts_per_tok=int(c["num_experts_per_tok"]),
-            rotary_dim=rotary_dim, rope_theta=float(c.get("rope_theta", 1e6)),
+            rotary_dim=rotary_dim, rope_theta=float(c.get("rope_theta", d_theta)),
             rope_section=None if section is None else tuple(int(x) for x in section),
             use_qk_norm=bool(c.get("use_qk_norm", False)),
-            qk_norm_type=str(c.get("qk_norm_type", "per_layer")),
+            qk_norm_type=str(c.get("qk_norm_type", d_norm)),
             attn_type_list=attn_types,
             scoring_func=str(c.get("scoring_func", "sigmoid")),
             use_routing_bias=bool(c.get("use_routing_bias", True)),
             norm_topk_prob=bool(c.get("norm_topk_prob", True)),
             routed_scaling_factor=float(c.get("routed_scaling_factor", 1.0)),
             shared_intermediate_size=int(c.get("shared_intermediate_size", 0)),
-            hidden_act=str(c.get("hidden_act", "silu")),
+            hidden_act=str(c.get("hidden_act", d_act)),
+            use_gemma_norm=bool(c.get("use_gemma_norm", False)),
+            attention_output_gate=bool(c.get("attention_output_gate", False)),
+            moe_layer_freq=tuple(int(x) for x in c.get("moe_layer_freq", ())),
+            n_shared_experts=int(c.get("n_shared_experts", 0)),
+            use_sparse_attention=bool(sparse.get("use_sparse_attention", False)),
             rms_norm_eps=float(c.get("rms_norm_eps", 1e-6)),
-            max_position_embeddings=int(c.get("max_position_embeddings", 204800)),
+            max_position_embeddings=int(c.get("max_position_embeddings", d_maxpos)),
             tie_word_embeddings=bool(c.get("tie_word_embeddings", raw.get("tie_word_embeddings", False))),
             bos_token_id=bos, eos_token_ids=eos_ids,
             torch_dtype=str(c.get("torch_dtype", raw.get("torch_dtype", "bfloat16"))),
@@ -167,6 +190,20 @@ class MiniMaxM3Config:
         if self.shared_intermediate_size != 0:
             errs.append(f"shared_intermediate_size {self.shared_intermediate_size}: this decoder has "
                         f"no shared expert")
+        if self.use_gemma_norm:
+            errs.append("use_gemma_norm: norms whose gain is stored as w and applied as 1 + w are not implemented")
+        if self.attention_output_gate:
+            errs.append("attention_output_gate: a gated attention output is not implemented")
+        if self.moe_layer_freq and len(self.moe_layer_freq) != n:
+            errs.append(f"moe_layer_freq length {len(self.moe_layer_freq)} != num_hidden_layers {n}")
+        elif any(f != 1 for f in self.moe_layer_freq):
+            bad = [i for i, f in enumerate(self.moe_layer_freq) if f != 1]
+            errs.append(f"moe_layer_freq marks layers {bad[:8]} as dense feed-forward layers "
+                        f"(only routed-expert layers are implemented)")
+        if self.n_shared_experts > 0:
+            errs.append(f"n_shared_experts {self.n_shared_experts}: this decoder has no shared expert")
+        if self.use_sparse_attention:
+            errs.append("sparse_attention_config.use_sparse_attention: block-sparse attention is not implemented")
         if self.num_experts_per_tok > self.num_local_experts:
             errs.append(f"num_experts_per_tok {self.num_experts_per_tok} > num_local_experts "
                         f"{self.num_local_experts}")
@@ -183,6 +220,16 @@ class MiniMaxM3Config:
         d["eos_token_id"] = list(eos) if len(eos) > 1 else eos[0]
         d["attn_type_list"] = list(self.attn_type_list)
         d["architectures"] = list(self.architectures)
+        for k in ("use_gemma_norm", "attention_output_gate", "n_shared_experts"):
+            if not d[k]:
+                d.pop(k)
+        d.pop("use_sparse_attention")
+        if self.use_sparse_attention:
+            d["sparse_attention_config"] = {"use_sparse_attention": True}
+        if self.moe_layer_freq:
+            d["moe_layer_freq"] = list(self.moe_layer_freq)
+        else:
+            d.pop("moe_layer_freq")
         if self.rope_section is None:
             d.pop("rope_section")
         else:

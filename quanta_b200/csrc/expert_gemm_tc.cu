@@ -258,7 +258,10 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
     }
-    if (mbar_wait(smem_u32(&sh.tmem_full), 0u, abort_flag)) {
+    // tcgen05.ld / wait::ld are .sync.aligned: the whole warp runs them or none of it does, so the lanes
+    // vote on the wait's answer (a lane may see another role's abort flag before its neighbour does)
+    const bool acc_ready = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.tmem_full), 0u, abort_flag) ? 1 : 0) != 0;
+    if (acc_ready) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
       for (int c0 = 0; c0 < NT; c0 += 16) {

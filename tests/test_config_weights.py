@@ -31,11 +31,84 @@ def test_required_keys_and_defaults():
 
 
 def test_nested_text_config_and_generation_config():
-    raw = {"architectures": ["MiniMaxM3ForCausalLM"], "text_config": dict(TINY["C"]), "eos_token_id": 5}
+    raw = {"architectures": ["MiniMaxM3ForCausalLM"], "text_config": dict(TINY["C"], hidden_act="silu"),
+           "eos_token_id": 5}
     c = MiniMaxM3Config.from_dict(raw, generation={"eos_token_id": [7, 8], "bos_token_id": 3})
     assert c.rotary_dim == 24            # round(48 * 0.5)
     assert c.eos_token_ids == (7, 8) and c.bos_token_id == 3
     assert c.rope_section == (4, 4, 4)
+
+
+def test_nested_defaults_are_the_nested_parsers():
+    """Inside ``text_config`` an absent key means what the reference's M3 parser says
+    (src/quanta/minimax/config_m3.py:280-303), not what the flat parser says."""
+    tc = dict(vocab_size=10, hidden_size=32, intermediate_size=16, num_hidden_layers=2, num_attention_heads=2,
+              num_key_value_heads=1, head_dim=16, num_local_experts=4, num_experts_per_tok=2)
+    with pytest.raises(ConfigError, match="swigluoai"):         # the nested default activation is not built
+        MiniMaxM3Config.from_dict({"text_config": dict(tc)})
+    c = MiniMaxM3Config.from_dict({"text_config": dict(tc, hidden_act="silu", use_qk_norm=True)})
+    assert c.qk_norm_type == "per_head" and c.rope_theta == 5e6 and c.max_position_embeddings == 1048576
+    flat = MiniMaxM3Config.from_dict(dict(tc, use_qk_norm=True))
+    assert flat.qk_norm_type == "per_layer" and flat.rope_theta == 1e6 and flat.max_position_embeddings == 204800
+    assert MiniMaxM3Config.from_dict(c.to_dict()) == c
+
+
+@pytest.mark.parametrize("change, word", [
+    ({"use_gemma_norm": True}, "use_gemma_norm"), ({"attention_output_gate": True}, "attention_output_gate"),
+    ({"moe_layer_freq": [0, 1]}, "dense feed-forward"), ({"moe_layer_freq": [1]}, "moe_layer_freq length"),
+    ({"n_shared_experts": 1}, "shared expert"),
+    ({"sparse_attention_config": {"use_sparse_attention": True}}, "block-sparse"),
+])
+def test_options_that_change_the_math_are_refused(change, word):
+    """Flat or nested: a key that the M3 checkpoints use to switch the layer math is never ignored."""
+    for nested in (False, True):
+        body = dict(TINY["A"], hidden_act="silu")
+        body.update(change)
+        raw = {"architectures": ["MiniMaxM3VLForConditionalGeneration"], "text_config": body} if nested else body
+        with pytest.raises(ConfigError, match=word):
+            MiniMaxM3Config.from_dict(raw)
+    ok = dict(TINY["A"], moe_layer_freq=[1, 1], n_shared_experts=0, use_gemma_norm=False,
+              sparse_attention_config={"use_sparse_attention": False})
+    c = MiniMaxM3Config.from_dict(ok)
+    assert MiniMaxM3Config.from_dict(c.to_dict()) == c
+
+
+def test_nested_config_matches_reference_m3_parser(tmp_path):
+    """Field by field against the reference's nested parser, when its sources are present."""
+    import importlib.util
+    import os
+    import pathlib
+    import sys
+    root = pathlib.Path(os.environ.get("QUANTA_REFERENCE_DIR") or pathlib.Path(__file__).resolve().parents[2] / "reference")
+    ref = root / "src" / "quanta" / "minimax" / "config_m3.py"
+    if not ref.exists():
+        pytest.skip("reference sources not present")
+    spec = importlib.util.spec_from_file_location("ref_minimax_config_m3", ref)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_minimax_config_m3"] = mod
+    try:
+        spec.loader.exec_module(mod)
+    except ImportError as e:
+        pytest.skip(f"the reference's nested parser does not import here: {e}")
+    tc = dict(vocab_size=300, hidden_size=64, intermediate_size=24, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=32, partial_rotary_factor=0.5, num_local_experts=6,
+              num_experts_per_tok=2, hidden_act="silu", use_qk_norm=True)
+    raw = {"architectures": ["MiniMaxM3VLForConditionalGeneration"], "model_type": "minimax_m3_vl", "text_config": tc}
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    theirs = mod.MiniMaxM3Config.from_pretrained(tmp_path)
+    ours = MiniMaxM3Config.from_dict(raw)
+    pairs = [("vocab_size", "vocab_size"), ("hidden_size", "hidden_size"), ("intermediate_size", "moe_intermediate_size"),
+             ("num_hidden_layers", "num_hidden_layers"), ("head_dim", "head_dim"), ("rotary_dim", "rotary_dim"),
+             ("use_qk_norm", "use_qk_norm"), ("qk_norm_type", "qk_norm_type"), ("rope_theta", "rope_theta"),
+             ("use_gemma_norm", "use_gemma_norm"), ("attention_output_gate", "attention_output_gate"),
+             ("n_shared_experts", "n_shared_experts"), ("use_sparse_attention", "use_sparse_attention"),
+             ("hidden_act", "hidden_act"), ("norm_topk_prob", "norm_topk_prob"), ("use_routing_bias", "use_routing_bias"),
+             ("routed_scaling_factor", "routed_scaling_factor"), ("rms_norm_eps", "norm_eps"),
+             ("max_position_embeddings", "max_position_embeddings"), ("eos_token_ids", "eos_token_ids"),
+             ("tie_word_embeddings", "tie_word_embeddings")]
+    for mine, their in pairs:
+        assert getattr(ours, mine) == getattr(theirs, their), mine
+    assert theirs.moe_layer_freq == (1, 1, 1) and ours.moe_layer_freq == ()     # absent: every layer routed
 
 
 @pytest.mark.parametrize("change, word", [
