@@ -20,7 +20,13 @@ from .base import FeedForward, TensorSpec, register
 
 @register("feed_forward", "sigmoid_topk_experts")
 class SigmoidTopKExperts(FeedForward):
-    graph_safe = True
+    """``trace``: a list assigned here receives, for every step, the experts each token chose (int32
+    ``[T, k]`` on the device, in choice order), for tools that follow the routing; while it is set the
+    part is not graph-safe, so an engine built then runs its decode steps kernel by kernel."""
+
+    @property
+    def graph_safe(self):
+        return self.trace is None
 
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, use_bias: bool,
                  renormalize: bool, scaling: float, names: dict):
@@ -34,6 +40,7 @@ class SigmoidTopKExperts(FeedForward):
         self.gate_w = self.bias = self.w13 = self.w2 = self.gate_pieces = None
         self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
         self._plan_counter = None    # the fused routing-and-plan kernel's counter of finished blocks (zero at rest)
+        self.trace = None
 
     def tensor_specs(self):
         n = self.names
@@ -142,6 +149,8 @@ class SigmoidTopKExperts(FeedForward):
         else:
             kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
         self.last_counts = plan[: self.E]
+        if self.trace is not None:
+            self.trace.append(idx)
         act = torch.empty((n_pairs, self.I), dtype=x.dtype, device=dev)
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
         if path == "tc":

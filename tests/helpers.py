@@ -53,7 +53,8 @@ def cut_portions(reqs: dict, sizes=(7, 2, 13, 3, 5, 2, 29, 4), seed: int = 0) ->
     return steps
 
 
-def cut_mixed(reqs: dict, max_live: int = 4, seed: int = 0, prompt_frac: float = 0.6) -> list[dict]:
+def cut_mixed(reqs: dict, max_live: int = 4, seed: int = 0, prompt_frac: float = 0.6,
+              portion_sizes=(2, 3, 5, 8, 17, 40)) -> list[dict]:
     """Up to ``max_live`` live requests; portions of some beside single tokens of others; a request
     is sometimes left out of a step.  The first ``prompt_frac`` of a request goes in portions, the
     rest token by token."""
@@ -71,7 +72,7 @@ def cut_mixed(reqs: dict, max_live: int = 4, seed: int = 0, prompt_frac: float =
             if len(live) > 1 and rng.random() < 0.2:
                 continue                      # left out of this step
             if done < prompt_len:
-                n = min(rng.choice([2, 3, 5, 8, 17, 40]), prompt_len - done)
+                n = min(rng.choice(list(portion_sizes)), prompt_len - done)
             else:
                 n = 1
             entries.append({"id": rid, "tokens": toks[done:done + n], "want": list(range(n))})
@@ -146,3 +147,9 @@ def worst_error(got: dict, want: dict):
 def first_wrong(got: dict, want: dict, tol: float):
     bad = sorted((k for k in got if float((got[k] - want[k]).abs().max()) > tol), key=lambda k: (str(k[0]), k[1]))
     return bad[0] if bad else None
+
+
+def first_wrong_place(err: dict, margins: dict, near_tie: float, tol: float):
+    """The first (request, position) whose error exceeds ``tol`` although its router margin is clear."""
+    bad = sorted((k for k, e in err.items() if e > tol and margins[k] >= near_tie), key=lambda k: (str(k[0]), k[1]))
+    return (bad[0], err[bad[0]], margins[bad[0]]) if bad else None

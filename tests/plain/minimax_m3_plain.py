@@ -1,8 +1,10 @@
 """Plain, slow implementation of the MiniMax-M3 text decoder (MiniMax-M2-family layer math).
 
-Whole sequences, no cache, one function for each part, PyTorch on the CPU.  It shares no code
-with the ``quanta_b200`` package: it reads the raw ``config.json`` dictionary and a dictionary
-of tensors by checkpoint name, and is the oracle the engine's tests compare against.
+Whole sequences, no cache, one function for each part, plain PyTorch (on the CPU; on a CUDA device
+when the tensors it is given live there, for the layer widths of the full-size model).  It shares no
+code with the ``quanta_b200`` package: it reads the raw ``config.json`` dictionary and the tensors by
+checkpoint name (a dictionary, or a function ``name -> tensor`` so that one layer's tensors can be made
+or read when the layer runs and dropped after it), and is the oracle the engine's tests compare against.
 
 This file rests on the reference's formulas (pmrjge/quanta); each function cites the file and
 lines it restates.  The reference's own model code needs ``mlx`` and cannot be imported on this
@@ -103,8 +105,8 @@ def partial_rope(x: torch.Tensor, pos: torch.Tensor, rd: int, theta: float) -> t
     (src/quanta/minimax/model_m3.py:83-96, src/quanta/minimax/attention.py:120-135).
     ``x`` ``[T, heads, hd]``; ``pos`` ``[T]`` absolute positions.  The angle is the float32
     product ``pos * inv_freq``."""
-    inv = rope_inv_freq(rd, theta)
-    ang = (pos.to(torch.float32)[:, None] * inv[None, :]).to(x.dtype)        # [T, rd/2]
+    inv = rope_inv_freq(rd, theta).to(x.device)
+    ang = (pos.to(device=x.device, dtype=torch.float32)[:, None] * inv[None, :]).to(x.dtype)        # [T, rd/2]
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x1, x2 = x[..., : rd // 2], x[..., rd // 2: rd]
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin, x[..., rd:]], dim=-1)
@@ -122,27 +124,41 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, act, com
     kr = k.repeat_interleave(rep, dim=1).transpose(0, 1)          # [nq,T,hd]
     vr = v.repeat_interleave(rep, dim=1).transpose(0, 1)
     s = (q.transpose(0, 1) @ kr.transpose(1, 2)) * (hd ** -0.5)   # [nq,T,T]
-    mask = torch.ones(T, T, dtype=torch.bool).tril()
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device).tril()
     if window:
-        mask &= ~torch.ones(T, T, dtype=torch.bool).tril(-int(window))
+        mask &= ~torch.ones(T, T, dtype=torch.bool, device=q.device).tril(-int(window))
     s = s.masked_fill(~mask, float("-inf"))
     p = _round(torch.softmax(s, dim=-1), act, compute)
     out = (p @ vr).transpose(0, 1).reshape(T, nq * hd)
     return _round(out, act, compute)
 
 
-def router(x: torch.Tensor, gate_w: torch.Tensor, bias, k: int, renorm: bool, scale: float):
+def router(x: torch.Tensor, gate_w: torch.Tensor, bias, k: int, renorm: bool, scale: float, given=None):
     """Sigmoid scores, bias for selection only, top-k, bias-free weights renormalised and scaled
     (src/quanta/minimax/moe.py:36-56).  Ties are broken towards the lower expert index.
-    Returns ``(idx [T,k] int64 sorted by choice descending, w [T,k])``."""
+    Returns ``(idx [T,k] int64 sorted by choice descending, w [T,k])``.  ``given`` ``[T,k]``: the choice
+    is taken from there instead (to follow another implementation through a near tie); the weights
+    are still this function's scores of those experts."""
     logits = x @ gate_w.to(x.dtype).T
     scores = torch.sigmoid(logits)
     choice = scores + bias.to(x.dtype)[None] if bias is not None else scores
-    idx = torch.argsort(-choice, dim=-1, stable=True)[:, :k]
+    idx = torch.argsort(-choice, dim=-1, stable=True)[:, :k] if given is None else given.to(x.device).long()
     w = torch.gather(scores, 1, idx)
     if k > 1 and renorm:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
     return idx, w * scale
+
+
+def router_margin(x: torch.Tensor, gate_w: torch.Tensor, bias, k: int) -> torch.Tensor:
+    """How far each token is from choosing other experts: the k-th largest choice score minus the
+    (k+1)-th (src/quanta/minimax/moe.py:44-52 for the scores).  A token whose margin is within the
+    rounding of the scores may choose differently in another implementation of the same arithmetic."""
+    scores = torch.sigmoid(x @ gate_w.to(x.dtype).T)
+    choice = scores + bias.to(x.dtype)[None] if bias is not None else scores
+    if k >= choice.shape[-1]:
+        return torch.full((x.shape[0],), float("inf"), dtype=x.dtype, device=x.device)
+    top = torch.topk(choice, k + 1, dim=-1).values
+    return top[:, k - 1] - top[:, k]
 
 
 def expert_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, act, compute):
@@ -154,15 +170,19 @@ def expert_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch
     return a @ w2.to(compute).T
 
 
-def moe(x: torch.Tensor, gate_w, bias, experts, k, renorm, scale, act, compute) -> torch.Tensor:
+def moe(x: torch.Tensor, gate_w, bias, experts, k, renorm, scale, act, compute, given=None, probe=None) -> torch.Tensor:
     """Routed sum of the chosen experts, weights applied after ``down``, accumulated in ``compute``;
-    no shared expert (src/quanta/minimax/moe.py:73-88).  ``experts[e] = (w1, w3, w2)``."""
-    idx, w = router(x, gate_w, bias, k, renorm, scale)
+    no shared expert (src/quanta/minimax/moe.py:73-88).  ``experts(e)`` or ``experts[e]`` ``= (w1, w3, w2)``.  The loop goes
+    over the experts, each taking the tokens that chose it (as moe.py:84-88 does with ``idx_flat``).
+    ``given``: see ``router``.  ``probe``: a dictionary that receives the choice (``idx``)."""
+    idx, w = router(x, gate_w, bias, k, renorm, scale, given)
+    if probe is not None:
+        probe["idx"] = idx
     out = torch.zeros_like(x)
-    for t in range(x.shape[0]):
-        for s in range(k):
-            e = int(idx[t, s])
-            out[t] += w[t, s] * expert_swiglu(x[t: t + 1], *experts[e], act, compute)[0]
+    for e in sorted(set(idx.reshape(-1).tolist())):
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        y = expert_swiglu(x[tok], *(experts(e) if callable(experts) else experts[e]), act, compute)
+        out.index_add_(0, tok, w[tok, slot][:, None] * y)
     return out
 
 
@@ -171,14 +191,20 @@ def moe(x: torch.Tensor, gate_w, bias, experts, k, renorm, scale, act, compute) 
 # ----------------------------------------------------------------------------------------------
 
 
-def _w(weights: dict, name: str) -> torch.Tensor:
+def _w(weights, name: str) -> torch.Tensor:
+    """``weights``: tensors by checkpoint name, or a function that returns the tensor of a name."""
+    if callable(weights):
+        return weights(name)
     if name in weights:
         return weights[name]
     return weights["language_model." + name]
 
 
-def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | None = None, window=None):
-    """``h + attn(norm(h))`` then ``h + moe(norm(h))`` (src/quanta/minimax/model.py:70-73)."""
+def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | None = None, window=None,
+          probe: dict | None = None, given=None):
+    """``h + attn(norm(h))`` then ``h + moe(norm(h))`` (src/quanta/minimax/model.py:70-73).
+    ``probe``: a dictionary that receives this layer's ``router_margin`` of every token and the experts
+    chosen (``margin``, ``idx``).  ``given``: the experts to take instead of the router's own choice."""
     c = cfg
     wl = layer if weight_layer is None else weight_layer
     p = f"model.layers.{wl}."
@@ -197,29 +223,72 @@ def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | No
     h = h + linear(a, W("self_attn.o_proj.weight"), act, compute)
     x2 = _round(rms_norm(h, W("post_attention_layernorm.weight"), c["eps"]), act, compute)
     m = p + "block_sparse_moe."
-    experts = [tuple(_w(weights, f"{m}experts.{e}.{n}.weight") for n in ("w1", "w3", "w2"))
-               for e in range(c["E"])]
+    experts = lambda e: tuple(_w(weights, f"{m}experts.{e}.{n}.weight") for n in ("w1", "w3", "w2"))  # noqa: E731
     bias = _w(weights, m + "e_score_correction_bias").to(compute) if c["bias"] else None
-    y = moe(x2, _w(weights, m + "gate.weight").to(compute), bias, experts, c["k"], c["renorm"],
-            c["scale"], act, compute)
+    gate_w = _w(weights, m + "gate.weight").to(compute)
+    if probe is not None:
+        probe["margin"] = router_margin(x2, gate_w, bias, c["k"])
+    y = moe(x2, gate_w, bias, experts, c["k"], c["renorm"], c["scale"], act, compute, given=given, probe=probe)
     return h + y
 
 
-def forward_logits(weights: dict, cfg: dict, ids, *, act=None, compute=torch.float32,
+def forward_logits(weights, cfg: dict, ids, *, act=None, compute=torch.float32,
                    schedule=None, windows=None) -> torch.Tensor:
     """Logits ``[T, V]`` of one whole sequence: embed -> blocks -> final norm -> head
     (src/quanta/minimax/model.py:86-96; head in float32, src/quanta/minimax/runtime.py:95-98).
     ``schedule`` lists the layers in the order they run (a layer may appear twice); ``windows`` maps a
     place in that order to the window of its attention (absent: every key)."""
-    ids = torch.as_tensor(ids, dtype=torch.long)
-    h = embedding(ids, _w(weights, "model.embed_tokens.weight"), compute)
-    pos = torch.arange(ids.shape[0])
+    return forward_logits_many(weights, cfg, [ids], act=act, compute=compute, schedule=schedule, windows=windows)[0]
+
+
+def forward_logits_many(weights, cfg: dict, sequences, *, rows=None, act=None, compute=torch.float32,
+                        schedule=None, windows=None, probes: list | None = None, given: dict | None = None) -> list:
+    """The same for several sequences, each whole and alone, layer by layer: a layer's tensors are
+    asked for once and serve every sequence, so ``weights`` may be a function that makes them when
+    asked (``_LayerTensors`` keeps what one layer asked for until the next begins).  ``rows[i]``:
+    the places of sequence ``i`` whose logits are returned (default: all).  The computation runs on
+    the device of the embedding table.  ``probes``: a list that receives, for each sequence, one
+    dictionary a layer with the tokens' ``router_margin`` and chosen experts.  ``given[(j, i)]``: the
+    experts sequence ``j`` takes at place ``i`` of the layer order instead of its router's choice."""
+    table = _w(weights, "model.embed_tokens.weight")
+    dev = table.device
+    seqs = [torch.as_tensor(s, dtype=torch.long, device=dev) for s in sequences]
+    hs = [embedding(s, table, compute) for s in seqs]
+    del table
     order = list(range(cfg["L"])) if schedule is None else list(schedule)
+    seen = [[] for _ in hs]
     for i, wl in enumerate(order):
-        h = block(h, pos, weights, cfg, i, act, compute, weight_layer=wl, window=(windows or {}).get(i))
-    hf = _round(rms_norm(h, _w(weights, "model.norm.weight").to(compute), cfg["eps"]), act, compute)
+        layer = _LayerTensors(weights)
+        for j, h in enumerate(hs):
+            pos = torch.arange(h.shape[0], device=dev)
+            probe = {} if probes is not None else None
+            hs[j] = block(h, pos, layer, cfg, i, act, compute, weight_layer=wl, window=(windows or {}).get(i),
+                          probe=probe, given=(given or {}).get((j, i)))
+            seen[j].append(probe)
+        del layer
+    if probes is not None:
+        probes.extend(seen)
+    norm_w = _w(weights, "model.norm.weight").to(compute)
     head = _w(weights, "model.embed_tokens.weight" if cfg["tied"] else "lm_head.weight")
-    return hf @ head.to(compute).T
+    out = []
+    for j, h in enumerate(hs):
+        if rows is not None:
+            h = h[torch.as_tensor(rows[j], dtype=torch.long, device=dev)]
+        hf = _round(rms_norm(h, norm_w, cfg["eps"]), act, compute)
+        out.append(hf @ head.to(compute).T)
+    return out
+
+
+class _LayerTensors:
+    """The tensors one layer has asked ``weights`` for, kept while the layer runs on several sequences."""
+
+    def __init__(self, weights):
+        self.weights, self.kept = weights, {}
+
+    def __call__(self, name: str) -> torch.Tensor:
+        if name not in self.kept:
+            self.kept[name] = _w(self.weights, name)
+        return self.kept[name]
 
 
 # ----------------------------------------------------------------------------------------------

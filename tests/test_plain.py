@@ -83,7 +83,9 @@ def test_causality_and_grouping(plain_models):
         ids = [3, 1, 4, 1, 5, 9, 2, 6]
         a = P.forward_logits(weights, cfg, ids)
         b = P.forward_logits(weights, cfg, ids[:5] + [7, 7, 7])
-        assert torch.equal(a[:5], b[:5])                          # a position sees only what came before
+        # a position sees only what came before (the library's products round a row differently in
+        # another batch of rows, so equality holds to rounding)
+        assert torch.allclose(a[:5], b[:5], atol=1e-6, rtol=0)
         assert not torch.allclose(a[5:], b[5:])
         assert a.shape == (8, cfg["V"])
 
