@@ -133,6 +133,7 @@ class CacheManager:
         self.slots = SlotPool(max_requests)
         self.requests: dict = {}
         self.preemptions = 0
+        self.on_free = None        # called with the slot index when a request gives its slot back
 
     # ---- requests ---------------------------------------------------------------------------------
     def has(self, rid) -> bool:
@@ -220,6 +221,8 @@ class CacheManager:
             g.pool.give_back([p for p in g.tables.pop(rid) if p >= 0])
             g.arrays.pop(rid, None)
         self.slots.give_back(rec.slot)
+        if self.on_free is not None:
+            self.on_free(rec.slot)
 
     # ---- views for a step ---------------------------------------------------------------------------
     def block_table_rows(self, group: int, rids: list) -> list[list[int]]:

@@ -24,6 +24,7 @@
 #define QB_STATUS_BAD_EXPERT 3
 #define QB_STATUS_WAIT_TIMEOUT 4
 #define QB_STATUS_SCRATCH_SMALL 5
+#define QB_STATUS_SLOT_MISMATCH 6
 
 #define QB_LAUNCH_CHECK()                        \
   do {                                           \

@@ -8,7 +8,14 @@
 // (Philox-4x32-10) keyed by the request's seed and indexed by (token, draw number): a request's
 // draws depend on nothing else in the batch.  Penalties over earlier generated tokens
 // (src/quanta/shim/omlx.py:344-363) are a separate in-place kernel.
+//
+// A row's options (temperature, top-k, top-p, min-p, seed) and the number of its draw come from the
+// state slot of its request (request_state.h); the kernel counts the draw there and leaves the token.
+// The thresholds of top-k and top-p come from histograms of integers (counts; probabilities in fixed
+// point, 2^-40 of the largest), so their sums do not depend on the order in which threads add: the
+// same row always keeps the same set.
 #include "common.cuh"
+#include "request_state.h"
 
 constexpr int SAMP_THREADS = 1024;
 
@@ -60,28 +67,48 @@ __device__ __forceinline__ ArgBest block_argmax(float v, int i, float* sv, int* 
 
 // Descending radix search over 32-bit keys.  Finds the key at which the running total (count or
 // mass, taken from the largest key downwards) first reaches `target`.  `floor_key`: only keys >=
-// floor_key take part.  Returns the key on every thread.
+// floor_key take part.  Totals are integers (MASS: exp(lg - m) * 2^40, at most 2^40 each, so 2^24
+// of them fit), added with integer atomics: exact, whatever the order.  target == 0 with MASS asks
+// for the total of all keys first (top-p of the mass that top-k left): target = frac * total.
+// Returns the key on every thread.
+constexpr double SAMP_FIXED_ONE = 1099511627776.0;      // 2^40
+
 template <bool MASS>
-__device__ uint32_t radix_threshold(const float* __restrict__ row, int V, float inv_t, float m, float target,
-                                    uint32_t floor_key, float* hist, uint32_t* s_prefix, float* s_above) {
+__device__ uint32_t radix_threshold(const float* __restrict__ row, int V, float inv_t, float m, double frac_or_count,
+                                    uint32_t floor_key, unsigned long long* hist, uint32_t* s_prefix,
+                                    unsigned long long* s_above, unsigned long long* s_target) {
   uint32_t prefix = 0;
-  float above = 0.f;
+  unsigned long long above = 0ull;
   for (int level = 0; level < 4; ++level) {
     const int shift = 24 - 8 * level;
     const uint32_t hi_mask = level == 0 ? 0u : (0xffffffffu << (shift + 8));
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0.f;
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
     __syncthreads();
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
       const float lg = row[i] * inv_t;
       const uint32_t key = order_key(lg);
       if (key < floor_key || (key & hi_mask) != prefix) continue;
-      atomicAdd(&hist[(key >> shift) & 255u], MASS ? expf(lg - m) : 1.f);
+      const unsigned long long add = MASS ? (unsigned long long)((double)expf(lg - m) * SAMP_FIXED_ONE) : 1ull;
+      atomicAdd(&hist[(key >> shift) & 255u], add);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      float run = above;
+      if (level == 0) {
+        if (MASS) {
+          unsigned long long total = 0ull;
+          for (int b = 0; b < 256; ++b) total += hist[b];
+          const unsigned long long t = (unsigned long long)(frac_or_count * (double)total);
+          *s_target = t > 0ull ? t : 1ull;              // the largest key is always kept
+        } else {
+          *s_target = (unsigned long long)frac_or_count;
+        }
+      }
+      const unsigned long long target = *s_target;
+      unsigned long long run = above;
       int pick = 0;
       for (int b = 255; b >= 0; --b) {
+        // a key is kept while the total strictly before it is below the target: the search stops at the
+        // first bin whose own total carries the sum to the target or past it
         if (run + hist[b] >= target) { pick = b; break; }
         run += hist[b];
         if (b == 0) { pick = 0; run -= hist[0]; }
@@ -97,68 +124,75 @@ __device__ uint32_t radix_threshold(const float* __restrict__ row, int V, float 
   return prefix;
 }
 
-__global__ void sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ fparams,
-                                   const int* __restrict__ iparams, int* __restrict__ out) {
+// slots: the state records (null: every row greedy, nothing recorded); row_slot[r]: the slot of row r.
+__global__ void sample_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ slots,
+                                   const int* __restrict__ row_slot, int n_slots, int* __restrict__ out) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  __shared__ float hist[256];
+  __shared__ unsigned long long hist[256];
   __shared__ uint32_t s_prefix;
-  __shared__ float s_above;
+  __shared__ unsigned long long s_above, s_target;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
-  // null parameters: every row is greedy
-  const float temperature = fparams ? fparams[r * 4 + 0] : 0.f;
-  const float top_p = fparams ? fparams[r * 4 + 1] : 1.f, min_p = fparams ? fparams[r * 4 + 2] : 0.f;
-  const int top_k = iparams ? iparams[r * 4 + 0] : 0;
-  const uint32_t k0 = iparams ? (uint32_t)iparams[r * 4 + 1] : 0u, k1 = iparams ? (uint32_t)iparams[r * 4 + 2] : 0u;
-  const uint32_t draw = iparams ? (uint32_t)iparams[r * 4 + 3] : 0u;
+  int* rec = nullptr;
+  if (slots != nullptr) {
+    const int slot = row_slot[r];
+    if (slot >= 0 && slot < n_slots) rec = slots + (size_t)slot * QB_SLOT_WORDS;
+  }
+  const float temperature = rec ? __int_as_float(rec[QB_SLOT_TEMPERATURE]) : 0.f;
+  const float top_p = rec ? __int_as_float(rec[QB_SLOT_TOP_P]) : 1.f;
+  const float min_p = rec ? __int_as_float(rec[QB_SLOT_MIN_P]) : 0.f;
+  const int top_k = rec ? rec[QB_SLOT_TOP_K] : 0;
+  const uint32_t k0 = rec ? (uint32_t)rec[QB_SLOT_SEED_LO] : 0u, k1 = rec ? (uint32_t)rec[QB_SLOT_SEED_HI] : 0u;
+  const uint32_t draw = rec ? (uint32_t)rec[QB_SLOT_DRAWN] : 0u;
+  __syncthreads();                  // every thread has read the record before thread 0 changes it
 
+  int token;
   if (temperature <= 0.f) {
     float bv = -INFINITY; int bi = -1;
     for (int i = threadIdx.x; i < V; i += blockDim.x)
       if (bi < 0 || row[i] > bv) { bv = row[i]; bi = i; }
-    const ArgBest b = block_argmax(bv, bi, sv, si);
-    if (threadIdx.x == 0) out[r] = b.i;
-    return;
-  }
-  const float inv_t = 1.f / temperature;
-  float bv = -INFINITY; int bi = -1;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float lg = row[i] * inv_t;
-    if (bi < 0 || lg > bv) { bv = lg; bi = i; }
-  }
-  const float m = block_argmax(bv, bi, sv, si).v;
-  uint32_t floor_key = 0u;
-  if (top_k > 0 && top_k < V)
-    floor_key = radix_threshold<false>(row, V, inv_t, m, (float)top_k, 0u, hist, &s_prefix, &s_above);
-  if (top_p > 0.f && top_p < 1.f) {
-    float z = 0.f;
+    token = block_argmax(bv, bi, sv, si).i;
+  } else {
+    const float inv_t = 1.f / temperature;
+    float bv = -INFINITY; int bi = -1;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
       const float lg = row[i] * inv_t;
-      if (order_key(lg) >= floor_key) z += expf(lg - m);
+      if (bi < 0 || lg > bv) { bv = lg; bi = i; }
     }
-    const float Z = qb_block_sum(z, sv);
-    __syncthreads();
-    const uint32_t kp = radix_threshold<true>(row, V, inv_t, m, top_p * Z, floor_key, hist, &s_prefix, &s_above);
-    floor_key = max(floor_key, kp);
+    const float m = block_argmax(bv, bi, sv, si).v;
+    uint32_t floor_key = 0u;
+    if (top_k > 0 && top_k < V)
+      floor_key = radix_threshold<false>(row, V, inv_t, m, (double)top_k, 0u, hist, &s_prefix, &s_above, &s_target);
+    if (top_p > 0.f && top_p < 1.f) {
+      const uint32_t kp = radix_threshold<true>(row, V, inv_t, m, (double)top_p, floor_key, hist, &s_prefix, &s_above,
+                                                &s_target);
+      floor_key = max(floor_key, kp);
+    }
+    const float min_lg = min_p > 0.f ? m + logf(min_p) : -INFINITY;
+    bv = -INFINITY; bi = -1;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float lg = row[i] * inv_t;
+      if (order_key(lg) < floor_key || lg < min_lg) continue;
+      const float v = lg + gumbel((uint32_t)i, draw, k0, k1);
+      if (bi < 0 || v > bv) { bv = v; bi = i; }
+    }
+    token = block_argmax(bv, bi, sv, si).i;
   }
-  const float min_lg = min_p > 0.f ? m + logf(min_p) : -INFINITY;
-  bv = -INFINITY; bi = -1;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float lg = row[i] * inv_t;
-    if (order_key(lg) < floor_key || lg < min_lg) continue;
-    const float v = lg + gumbel((uint32_t)i, draw, k0, k1);
-    if (bi < 0 || v > bv) { bv = v; bi = i; }
+  if (threadIdx.x == 0) {
+    out[r] = token;
+    if (rec) {
+      rec[QB_SLOT_LAST] = token;
+      rec[QB_SLOT_DRAWN] = (int)(draw + 1u);
+    }
   }
-  const ArgBest b = block_argmax(bv, bi, sv, si);
-  if (threadIdx.x == 0) out[r] = b.i;
 }
 
-// fparams [n,4]: temperature, top_p, min_p, -.  iparams [n,4]: top_k, seed low word, seed high word, draw.
-extern "C" int qb_sample_rows(const float* logits, int n, int V, const float* fparams, const int* iparams,
+extern "C" int qb_sample_rows(const float* logits, int n, int V, int* slots, const int* row_slot, int n_slots,
                               int* out, cudaStream_t stream) {
   if (n <= 0) return 0;
-  sample_rows_kernel<<<n, SAMP_THREADS, 0, stream>>>(logits, V, fparams, iparams, out);
+  if (slots != nullptr && (row_slot == nullptr || n_slots <= 0)) return QB_ERR_BAD_ARG;
+  sample_rows_kernel<<<n, SAMP_THREADS, 0, stream>>>(logits, V, slots, row_slot, n_slots, out);
   QB_LAUNCH_CHECK();
   return 0;
 }
@@ -182,6 +216,7 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, i
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int parts,
+                                    int* __restrict__ slots, const int* __restrict__ row_slot, int n_slots,
                                     int* __restrict__ out) {
   const int r = blockIdx.x;
   if (threadIdx.x != 0) return;
@@ -192,15 +227,24 @@ __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __r
     if (i >= 0 && (bi < 0 || v > bv)) { bv = v; bi = i; }
   }
   out[r] = bi;
+  if (slots != nullptr) {
+    const int slot = row_slot[r];
+    if (slot >= 0 && slot < n_slots) {
+      int* rec = slots + (size_t)slot * QB_SLOT_WORDS;
+      rec[QB_SLOT_LAST] = bi;
+      rec[QB_SLOT_DRAWN] += 1;
+    }
+  }
 }
 
-// scratch: parts floats and parts ints per row
+// Every row greedy.  scratch: parts floats and parts ints per row.  slots / row_slot as in qb_sample_rows.
 extern "C" int qb_argmax_rows(const float* logits, int n, int V, int parts, float* scratch_v, int* scratch_i,
-                              int* out, cudaStream_t stream) {
+                              int* slots, const int* row_slot, int n_slots, int* out, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (parts <= 0 || n > 65535) return QB_ERR_BAD_ARG;
+  if (slots != nullptr && (row_slot == nullptr || n_slots <= 0)) return QB_ERR_BAD_ARG;
   argmax_partial_kernel<<<dim3(parts, n), 256, 0, stream>>>(logits, V, parts, scratch_v, scratch_i);
-  argmax_final_kernel<<<n, 32, 0, stream>>>(scratch_v, scratch_i, parts, out);
+  argmax_final_kernel<<<n, 32, 0, stream>>>(scratch_v, scratch_i, parts, slots, row_slot, n_slots, out);
   QB_LAUNCH_CHECK();
   return 0;
 }
@@ -234,6 +278,34 @@ extern "C" int qb_apply_penalties(float* logits, int n, int V, const int* prev, 
                                   const float* pparams, cudaStream_t stream) {
   if (n <= 0) return 0;
   penalties_kernel<<<n, 256, 0, stream>>>(logits, V, prev, prev_off, pparams);
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+
+// The step's part in the state slots: each request's position moves to the tokens it will hold after the
+// step.  Before that the record is checked against what the host packed: the slot must be live and its
+// position must be where the step's first token of the request goes; a difference means host and device
+// disagree about a request, which is recorded in the status words (the step's writes then land where
+// the host said; the host raises when it next reads the status).
+__global__ void slots_advance_kernel(int* __restrict__ slots, int n_slots, const int* __restrict__ req_slot,
+                                     const int* __restrict__ req_start, const int* __restrict__ req_len_after, int R,
+                                     int* status) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < R; r += gridDim.x * blockDim.x) {
+    const int slot = req_slot[r];
+    if (slot < 0 || slot >= n_slots) { qb_set_status(status, QB_STATUS_SLOT_MISMATCH, slot, 8); continue; }
+    int* rec = slots + (size_t)slot * QB_SLOT_WORDS;
+    const int before = req_len_after[r] - (req_start[r + 1] - req_start[r]);
+    if (rec[QB_SLOT_LIVE] != 1 || rec[QB_SLOT_POSITION] != before) qb_set_status(status, QB_STATUS_SLOT_MISMATCH, slot, 8);
+    rec[QB_SLOT_POSITION] = req_len_after[r];
+  }
+}
+
+extern "C" int qb_slots_advance(int* slots, int n_slots, const int* req_slot, const int* req_start,
+                                const int* req_len_after, int R, int* status, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (n_slots <= 0) return QB_ERR_BAD_ARG;
+  slots_advance_kernel<<<(R + 127) / 128, 128, 0, stream>>>(slots, n_slots, req_slot, req_start, req_len_after, R, status);
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -118,15 +118,11 @@ class LLM:
         steps = steps_ahead = 0
         self.step_log = []
 
-        def launch(plan, entries, samplers, drawn_before):
+        def launch(entries, samplers):
             logits = eng.step(entries)
             handle = None
             if samplers:
-                # a replayed decode step: the ids also go to the slots' table, for a step launched ahead
-                decode_only = eng.last_decode_slots is not None and len(samplers) == len(entries)
-                scatter = (eng.slot_token, eng.last_decode_slots) if decode_only else None
-                handle = self.sampler.sample_async(logits, samplers, eng.status, drawn_before=drawn_before,
-                                                   scatter=scatter)
+                handle = self.sampler.sample_async(logits, eng.slots, eng.last_want_slots, samplers, eng.status)
             self.step_log.append({"tokens": sum(len(e.tokens) for e in entries), "sampled": len(samplers),
                                   "h2d_bytes": eng.last_h2d_bytes, "d2h_bytes": 4 * (len(samplers) + 4),
                                   "t_end": None})
@@ -140,14 +136,18 @@ class LLM:
                     break
                 entries = [StepEntry(e.request.rid, e.tokens, (e.count - 1,) if e.samples else ()) for e in plan]
                 samplers = [e.request for e in plan if e.samples]
-                handle, log = launch(plan, entries, samplers, 0)
+                for r in (e.request for e in plan if not eng.manager.has(e.request.rid)):
+                    # the request's record on the device: its options, and where its draws go on (a request
+                    # that was preempted comes back with its generated tokens as part of its prompt)
+                    eng.admit(r.rid, prompt_len=len(r.prompt), params=r.params, drawn=len(r.generated))
+                handle, log = launch(entries, samplers)
                 inflight = (plan, samplers, handle, log)
             plan, samplers, handle, log = inflight
             ahead = self._decode_ahead(sched, plan) if handle is not None else None
             nxt = None
             if ahead:
                 a_entries = [StepEntry(r.rid, [0], (0,), from_device=True) for r in ahead]
-                a_handle, a_log = launch(None, a_entries, ahead, 1)
+                a_handle, a_log = launch(a_entries, ahead)
                 nxt = (ahead, a_handle, a_log)
                 steps_ahead += 1
             sampled = {}

@@ -9,7 +9,14 @@ logits at the wanted places.  Nothing inside synchronises with the host.
 
 Steps in which every request brings exactly one token (decoding) are launch-bound when run kernel
 by kernel, so they are captured once per (batch size, context bucket) in a CUDA graph and replayed:
-the graph reads its integers from a fixed device buffer that each step overwrites.
+the graph reads its integers from a fixed device buffer that each step overwrites.  At most
+``max_graphs`` captured steps are kept; the one used longest ago goes when another is captured.
+
+Every live request has a state slot: a row of each mixer's fixed-size state and one record of the
+``slots`` array on the device (csrc/request_state.h: live flag, position, prompt length, draws so far,
+last sampled token, seed and sampling options).  The record is written when the request is admitted,
+every step moves its position (and checks it against the host's), the sampler reads and updates it,
+and it is zeroed when the request is freed.
 """
 
 from __future__ import annotations
@@ -39,9 +46,9 @@ class _DecodeGraph:
         self.graph = None
         self.seen = 0             # eager runs at this shape before the capture
         self.dev = None           # the fixed device buffer of the step's integers
-        self.host = None          # its pinned host twin
         self.logits = None
         self.launches = 0
+        self.used_at = 0          # the engine's step count when it last ran
 
 
 def _fill(host: torch.Tensor, pieces: list) -> None:
@@ -54,7 +61,7 @@ def _fill(host: torch.Tensor, pieces: list) -> None:
 
 class Engine:
     def __init__(self, model, *, num_pages: int, page_size: int = 16, max_requests: int = 64,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_graphs: int = 16):
         if not model.loaded:
             raise RuntimeError("the model has no weights yet")
         self.model = model
@@ -84,23 +91,46 @@ class Engine:
         # graphs only when every part says its step reads nothing from the host
         self.use_graphs = bool(use_graphs) and all(getattr(p, "graph_safe", False) for p in model.parts())
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self.max_graphs = max(1, int(max_graphs))
         self._graph_pool = None        # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
-        # the token last sampled for the request in each state slot: a decode step can take its ids from
-        # here, so that it can be launched before the host has read them
-        self.slot_token = torch.zeros(max_requests, dtype=torch.int32, device=self.device)
-        self.last_decode_slots = None       # device view: the slots of the rows of the last graph step
+        # one record per state slot (csrc/request_state.h).  Among other things it holds the token last
+        # sampled for the request: a decode step can take its ids from there, so that it can be launched
+        # before the host has read them
+        self.slots = torch.zeros((max_requests, kernels.SLOT_WORDS), dtype=torch.int32, device=self.device)
+        self.manager.on_free = self._slot_freed
+        self.last_want_slots = None         # device: the state slot of each row of the logits the last step returned
 
     # ---- requests -----------------------------------------------------------------------------------
-    def _admit(self, rid) -> None:
+    def admit(self, rid, *, prompt_len: int = 0, params=None, drawn: int = 0) -> int:
+        """Give ``rid`` a state slot: its mixer state rows are zeroed and its record is written (one small
+        copy).  ``params``: the request's sampling options (an object with temperature, top_k, top_p, min_p,
+        seed; None: greedy); ``drawn``: tokens it has sampled before (a request that comes back after it
+        was preempted goes on with the next draw number).  ``step`` admits requests it does not know with a
+        default record; call this first when the sampler is to read the request's options."""
         slot = self.manager.add_request(rid)
         for per_pos in self.state:
             for t in per_pos.values():
                 t[slot].zero_()
+        opts = {} if params is None else dict(seed=params.seed, temperature=params.temperature, top_k=params.top_k,
+                                                top_p=params.top_p, min_p=params.min_p)
+        rec = kernels.slot_record(prompt_len=prompt_len, drawn=drawn, **opts).pin_memory()
+        self.slots[slot].copy_(rec, non_blocking=True)
+        return slot
+
+    def _slot_freed(self, slot: int) -> None:
+        self.slots[slot].zero_()
 
     def release(self, rid) -> None:
         if self.manager.has(rid):
             self.manager.free(rid)
+
+    def stats(self) -> dict:
+        """The cache manager's figures and what the captured decode steps hold."""
+        graphs = [g for g in self._graphs.values() if g.graph is not None]
+        held = sum(g.logits.numel() * g.logits.element_size() + g.dev.numel() * 4 for g in graphs)
+        return {**self.manager.stats(), "graphs": len(graphs), "graph_output_bytes": held,
+                "graph_replays": self.graph_replays}
 
     def check(self) -> None:
         """Read the device status words (synchronises) and raise if a kernel refused an index."""
@@ -117,7 +147,7 @@ class Engine:
         slot are given back."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         mgr = self.manager
-        self.last_decode_slots = None
+        self.last_want_slots = None
         seen = set()
         for e in entries:
             if e.rid in seen:
@@ -125,8 +155,10 @@ class Engine:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: an entry must bring at least one token")
-            if e.from_device and (len(e.tokens) != 1 or not self.decode_graph_ready(len(entries), 0, entries)):
-                raise ValueError(f"request {e.rid!r}: ids from the device need a captured decode step")
+            if e.from_device and (len(e.tokens) != 1 or not self.decode_graph_ready(len(entries), 0, entries)
+                                  or not all(x.from_device for x in entries)):
+                raise ValueError(f"request {e.rid!r}: ids come from the device for every request of a captured "
+                                 f"decode step, or for none")
             if not e.from_device:
                 ids = np.asarray(e.tokens, dtype=np.int64)
                 bad = ids[(ids < 0) | (ids >= self.vocab_size)]
@@ -143,7 +175,7 @@ class Engine:
         if not mgr.can_reserve(wants):
             raise OutOfPages(f"the step needs more pages than are free: {mgr.stats()['groups']}")
         for rid in new:
-            self._admit(rid)
+            self.admit(rid)
         for rid, n in wants.items():
             mgr.reserve(rid, n)
 
@@ -167,7 +199,7 @@ class Engine:
         mgr = self.manager
         rids = [e.rid for e in entries]
         R = len(entries)
-        token_ids, tok_pos, tok_req, want_rows = [], [], [], []
+        token_ids, tok_pos, tok_req, want_rows, want_slot = [], [], [], [], []
         req_start, req_len_after, req_slot = [0], [], []
         row0 = 0
         for r, e in enumerate(entries):
@@ -177,6 +209,7 @@ class Engine:
             tok_pos.append(np.arange(base, base + n, dtype=np.int32))
             tok_req.append(np.full(n, r, dtype=np.int32))
             want_rows.extend(row0 + int(w) for w in e.want)
+            want_slot.extend([mgr.slot(e.rid)] * len(e.want))
             row0 += n
             req_start.append(row0)
             req_len_after.append(base + n)
@@ -188,7 +221,7 @@ class Engine:
         spans = [(r, req_start[r], req_start[r + 1] - req_start[r]) for r in range(R)
                  if req_start[r + 1] - req_start[r] > 1]
         pieces = [np.asarray(p, dtype=np.int32) for p in (token_ids, tok_pos, tok_req, positions, req_start,
-                                                          req_len_after, req_slot, want_rows, dec_rows)] + tables
+                                                          req_len_after, req_slot, want_rows, want_slot, dec_rows)] + tables
         info = {"req_start": req_start, "req_len_after": req_len_after, "req_slot": req_slot, "spans": spans,
                 "n_dec": len(dec_rows), "n_want": len(want_rows)}
         return pieces, info
@@ -199,8 +232,9 @@ class Engine:
         for n in sizes:
             out.append(dev[off: off + n])
             off += n
-        d_ids, d_pos, d_req, d_positions, d_start, d_len, d_slot, d_want, d_dec = out[:9]
-        d_tables = [t.view(R, max_pages) for t in out[9:]]
+        d_ids, d_pos, d_req, d_positions, d_start, d_len, d_slot, d_want, d_want_slot, d_dec = out[:10]
+        d_tables = [t.view(R, max_pages) for t in out[10:]]
+        self.last_want_slots = d_want_slot
         ctx = StepContext(
             n_tokens=T, positions=d_positions.view(T, self.n_axes), tok_pos=d_pos, tok_req=d_req, req_slot=d_slot,
             req_start=d_start, req_len_after=d_len, status=self.status, dtype=self.model.dtype,
@@ -234,6 +268,7 @@ class Engine:
         self.last_h2d_bytes = total * 4
         d_ids, d_want, ctx, caches = self._context(dev, sizes, R, T, max_pages, info, max_len_after,
                                                    max(len(e.tokens) for e in entries), with_host=True)
+        kernels.slots_advance(self.slots, ctx.req_slot, ctx.req_start, ctx.req_len_after, R, self.status)
         return self.model.forward(d_ids, ctx, caches, self.state, d_want if info["n_want"] else None)
 
     # ---- decoding through a captured graph ----------------------------------------------------------------------
@@ -279,15 +314,10 @@ class Engine:
         g.dev.copy_(host, non_blocking=True)
         self.last_h2d_bytes = total * 4
         slots_at = sum(sizes[:6])            # the req_slot piece
-        self.last_decode_slots = g.dev[slots_at: slots_at + B]
-        if any(e.from_device for e in entries):
-            # ids sampled by the step before, still on the device (rows that brought an id keep it)
-            ids = torch.index_select(self.slot_token, 0, self.last_decode_slots)
-            if all(e.from_device for e in entries):
-                g.dev[:B].copy_(ids)
-            else:
-                mask = torch.tensor([e.from_device for e in entries], device=self.device)
-                g.dev[:B].copy_(torch.where(mask, ids, g.dev[:B]))
+        row_slots = g.dev[slots_at: slots_at + B]
+        if entries[0].from_device:
+            # ids sampled by the step before, still on the device, in the requests' records
+            g.dev[:B].copy_(torch.index_select(self.slots[:, kernels.SLOT_LAST], 0, row_slots))
         if g.graph is None:
             d_ids, d_want, ctx, caches = self._context(g.dev, sizes, B, B, max_pages, info, bucket, 1, with_host=False)
             torch.cuda.synchronize()
@@ -296,16 +326,32 @@ class Engine:
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(graph, pool=self._graph_pool):
+                kernels.slots_advance(self.slots, ctx.req_slot, ctx.req_start, ctx.req_len_after, B, self.status)
                 g.logits = self.model.forward(d_ids, ctx, caches, self.state, d_want)
             g.launches = kernels.LAUNCHES - before
             g.graph = graph
+            self._drop_old_graphs(keep=key)
         else:
             kernels.LAUNCHES += g.launches
+        g.used_at = self.steps
         g.graph.replay()
         self.graph_replays += 1
         want = [r for r, e in enumerate(entries) for _ in e.want]
         if not want:
+            self.last_want_slots = None
             return None
         if want == list(range(B)):
+            self.last_want_slots = row_slots
             return g.logits
-        return g.logits[torch.tensor(want, device=self.device)]
+        picked = torch.tensor(want, device=self.device)
+        self.last_want_slots = row_slots[picked]
+        return g.logits[picked]
+
+    def _drop_old_graphs(self, keep) -> None:
+        """Every captured step keeps its logits ([batch, vocab] float32) and its nodes alive; beyond
+        ``max_graphs`` the one that ran longest ago is given up (its shape is captured again if it returns)."""
+        captured = [k for k, g in self._graphs.items() if g.graph is not None]
+        while len(captured) > self.max_graphs:
+            oldest = min((k for k in captured if k != keep), key=lambda k: self._graphs[k].used_at)
+            del self._graphs[oldest]
+            captured.remove(oldest)

@@ -21,9 +21,10 @@ NORM_NONE, NORM_PER_LAYER, NORM_PER_HEAD = 0, 1, 2
 
 _STATUS_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool (block table)",
                 3: "expert id outside the expert table", 4: "a bounded device wait ran out",
-                5: "the decode attention scratch has too few entries per row"}
+                5: "the decode attention scratch has too few entries per row",
+                6: "a request's state slot on the device is free or at another position than the host's record"}
 _KERNEL_TEXT = {1: "embedding", 2: "rope/cache write", 3: "paged attention", 4: "expert plan",
-                5: "expert product", 6: "decode attention", 7: "prefill attention"}
+                5: "expert product", 6: "decode attention", 7: "prefill attention", 8: "state slots"}
 
 
 class KernelError(RuntimeError):
@@ -406,20 +407,65 @@ def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, t
                                    int(tile_rows), int(gather_top_k), n_x, _p(status), _stream()), "expert_gemm_tc")
 
 
-def sample_rows(logits, fparams, iparams, out) -> None:
-    """``fparams``/``iparams`` None: every row is greedy (first maximum)."""
+# ---- state slots (csrc/request_state.h) ------------------------------------------------------------------
+SLOT_WORDS = 16
+SLOT_LIVE, SLOT_POSITION, SLOT_PROMPT, SLOT_DRAWN, SLOT_LAST, SLOT_SEED_LO, SLOT_SEED_HI, SLOT_TOP_K = range(8)
+SLOT_TEMPERATURE, SLOT_TOP_P, SLOT_MIN_P = 8, 9, 10
+
+
+def slot_record(*, position: int = 0, prompt_len: int = 0, drawn: int = 0, last: int = 0, seed: int = 0,
+                temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0) -> torch.Tensor:
+    """A live request's record as int32 ``[SLOT_WORDS]`` on the host (floats as their bit patterns)."""
+    import struct
+
+    def bits(x: float) -> int:
+        return struct.unpack("<i", struct.pack("<f", float(x)))[0]
+
+    def word(x: int) -> int:
+        x &= 0xFFFFFFFF
+        return x - (1 << 32) if x >= (1 << 31) else x
+
+    seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    rec = [0] * SLOT_WORDS
+    rec[SLOT_LIVE], rec[SLOT_POSITION], rec[SLOT_PROMPT], rec[SLOT_DRAWN], rec[SLOT_LAST] = 1, position, prompt_len, drawn, last
+    rec[SLOT_SEED_LO], rec[SLOT_SEED_HI], rec[SLOT_TOP_K] = word(seed), word(seed >> 32), int(top_k)
+    rec[SLOT_TEMPERATURE], rec[SLOT_TOP_P], rec[SLOT_MIN_P] = bits(temperature), bits(top_p), bits(min_p)
+    return torch.tensor(rec, dtype=torch.int32)
+
+
+def slots_advance(slots, req_slot, req_start, req_len_after, n_requests: int, status) -> None:
+    """Move each request's position in its state slot to what it holds after the step; a slot that is free
+    or at another position than the step assumes is recorded in ``status``."""
+    _want(slots, torch.int32, "slots")
+    if slots.dim() != 2 or slots.shape[1] != SLOT_WORDS:
+        raise ValueError(f"slots must be [n, {SLOT_WORDS}]")
+    _check(lib().qb_slots_advance(_p(slots), slots.shape[0], _p(req_slot), _p(req_start), _p(req_len_after),
+                                  int(n_requests), _p(status), _stream()), "slots_advance")
+
+
+def sample_rows(logits, slots, row_slot, out, all_greedy: bool = False) -> None:
+    """One token a row of float32 logits.  ``slots`` int32 ``[n_slots, SLOT_WORDS]`` and ``row_slot`` int32
+    ``[n]``: each row's options and draw number come from its slot's record, which then counts the draw and
+    holds the token.  ``slots`` None: every row is greedy (first maximum) and nothing is recorded.
+    ``all_greedy``: the caller knows every row's temperature is <= 0 (a large vocabulary is then cut over
+    many blocks)."""
     _want(logits, torch.float32, "logits"); _want(out, torch.int32, "out")
-    if fparams is not None:
-        _want(fparams, torch.float32, "fparams"); _want(iparams, torch.int32, "iparams")
     n, V = logits.shape
-    if fparams is None and V >= 4096:
+    n_slots = 0
+    if slots is not None:
+        _want(slots, torch.int32, "slots"); _want(row_slot, torch.int32, "row_slot")
+        if slots.dim() != 2 or slots.shape[1] != SLOT_WORDS or row_slot.numel() != n:
+            raise ValueError("sample_rows: slots must be [n_slots, SLOT_WORDS] and row_slot [n]")
+        n_slots = slots.shape[0]
+    if (slots is None or all_greedy) and V >= 4096:
         # all greedy: a row is cut over many blocks, then the first maximum of the chunks is taken
         parts = 32
         sv = torch.empty(n * parts, dtype=torch.float32, device=logits.device)
         si = torch.empty(n * parts, dtype=torch.int32, device=logits.device)
-        _check(lib().qb_argmax_rows(_p(logits), n, V, parts, _p(sv), _p(si), _p(out), _stream()), "argmax_rows", 2)
+        _check(lib().qb_argmax_rows(_p(logits), n, V, parts, _p(sv), _p(si), _p(slots), _p(row_slot), n_slots, _p(out),
+                                    _stream()), "argmax_rows", 2)
         return
-    _check(lib().qb_sample_rows(_p(logits), n, V, _p(fparams), _p(iparams), _p(out), _stream()), "sample_rows")
+    _check(lib().qb_sample_rows(_p(logits), n, V, _p(slots), _p(row_slot), n_slots, _p(out), _stream()), "sample_rows")
 
 
 def apply_penalties(logits, prev, prev_off, pparams) -> None:

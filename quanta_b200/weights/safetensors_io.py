@@ -107,11 +107,21 @@ class CheckpointFolder:
         self._where: dict[str, str] = {}
         index = d / "model.safetensors.index.json"
         if index.exists():
-            wm = json.loads(index.read_text())["weight_map"]
-            for name, fn in wm.items():
-                self._where[name] = fn
-            for fn in sorted(set(wm.values())):
+            wm = json.loads(index.read_text()).get("weight_map")
+            if not isinstance(wm, dict) or not wm:
+                raise ValueError(f"{index}: no weight_map")
+            shards = sorted(set(wm.values()))
+            absent = [fn for fn in shards if not (d / fn).is_file()]
+            if absent:
+                raise FileNotFoundError(f"{index.name} names {len(absent)} shard(s) that are not in {d}: "
+                                        f"{', '.join(absent[:8])}")
+            for fn in shards:
                 self._files[fn] = SafetensorsFile(d / fn)
+            astray = sorted(name for name, fn in wm.items() if name not in self._files[fn].header)
+            if astray:
+                raise ValueError(f"{index.name} places {len(astray)} tensor(s) in shards that do not hold them: "
+                                 f"{', '.join(astray[:8])}")
+            self._where.update(wm)
         else:
             single = d / "model.safetensors"
             files = [single] if single.exists() else sorted(d.glob("*.safetensors"))

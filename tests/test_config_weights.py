@@ -264,3 +264,39 @@ def test_dtypes_kept(model_dirs):
     assert model.blocks[0].mixer.w_qkv.dtype == torch.bfloat16
     assert model.blocks[0].feed_forward.gate_w.dtype == torch.float32      # stored in 32-bit, stays so
     assert model.blocks[0].mixer_norm.weight.dtype == torch.float32
+
+
+def test_sharded_folder_with_an_index(model_dirs, tmp_path):
+    """Two shards and ``model.safetensors.index.json`` (how real checkpoints come,
+    src/quanta/minimax/loader.py:96-134) load to the same tensors as the single file; an index that names
+    a shard which is not there, or a tensor its shard does not hold, is one clear error."""
+    from safetensors.torch import load_file
+    src = model_dirs["A"]
+    tensors = load_file(str(src / "model.safetensors"))
+    names = sorted(tensors)
+    halves = {"model-00001-of-00002.safetensors": names[::2], "model-00002-of-00002.safetensors": names[1::2]}
+    (tmp_path / "config.json").write_text((src / "config.json").read_text())
+    for fn, part in halves.items():
+        write_safetensors(tmp_path / fn, {n: tensors[n] for n in part})
+    index = {"metadata": {"total_size": 0}, "weight_map": {n: fn for fn, part in halves.items() for n in part}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    folder = CheckpointFolder(tmp_path)
+    assert sorted(folder.names()) == names
+    folder.close()
+    whole, _ = _cpu_model(TINY["A"])
+    whole.load(FolderSource(src))
+    sharded, _ = _cpu_model(TINY["A"])
+    sharded.load(FolderSource(tmp_path))
+    a = whole.blocks[1].feed_forward
+    b = sharded.blocks[1].feed_forward
+    assert torch.equal(a.w13, b.w13) and torch.equal(a.w2, b.w2) and torch.equal(a.gate_w, b.gate_w)
+    assert torch.equal(whole.head.weight, sharded.head.weight)
+    (tmp_path / "model-00002-of-00002.safetensors").rename(tmp_path / "elsewhere.safetensors")
+    with pytest.raises(FileNotFoundError, match="model-00002-of-00002.safetensors"):
+        FolderSource(tmp_path)
+    (tmp_path / "elsewhere.safetensors").rename(tmp_path / "model-00002-of-00002.safetensors")
+    index["weight_map"][names[0]] = "model-00002-of-00002.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    import re
+    with pytest.raises(ValueError, match=re.escape(names[0])):
+        FolderSource(tmp_path)

@@ -394,6 +394,78 @@ def test_eos_and_few_pages(model_dirs, plain_models):
     stop = want[0][4]
     cut = generate(roomy, prompts[0], max_new_tokens=12, eos_id=stop)
     assert cut == want[0][: want[0].index(stop)]
+    # sampled: a request that is preempted and recomputed goes on with the draw number it had reached,
+    # so the tokens are those of the plain implementation whether or not anything was preempted
+    kw = dict(max_new_tokens=12, temperature=0.8, seed=4321, top_k=40, eos_id=[])
+    drawn = generate(tight, prompts, **kw)
+    assert tight.last_stats["preemptions"] >= 1
+    assert drawn == generate(roomy, prompts, **kw)
+    for p, g in zip(prompts, drawn):
+        assert g == P.generate(weights, cfg, p, max_new_tokens=12, temperature=0.8, seed=4321, top_k=40)
+
+
+def test_state_slots_on_the_device(model_dirs):
+    """Every live request has a record on the device: position, prompt length, draws so far, the last
+    sampled token, seed and options.  After steps that mix prompt portions, single tokens, sampling with
+    three different option sets and a request that ends, the records say what the host's bookkeeping says,
+    the freed slot is zero, and a record that disagrees with the host is reported."""
+    import struct
+    from quanta_b200 import kernels
+    from quanta_b200.engine.model import load_model
+    from quanta_b200.engine.scheduler import SamplingParams
+    from quanta_b200.engine.step import Engine, StepEntry
+    from quanta_b200.sampling.sampler import Sampler
+
+    class Req:
+        def __init__(self, rid, prompt, params):
+            self.rid, self.prompt, self.params, self.generated = rid, prompt, params, []
+
+    model, _ = load_model(model_dirs["A"], dtype="float32")
+    eng = Engine(model, num_pages=64, page_size=4, max_requests=4)
+    sampler = Sampler(DEV)
+    reqs = {"a": Req("a", H.random_tokens(9, 512, 1), SamplingParams(temperature=0.8, seed=5, top_k=20)),
+            "b": Req("b", H.random_tokens(14, 512, 2), SamplingParams(temperature=0.0)),
+            "c": Req("c", H.random_tokens(6, 512, 3), SamplingParams(temperature=1.1, seed=2 ** 35 + 1, top_p=0.9, min_p=0.01))}
+
+    def step(parts, end=()):
+        """parts: (request, tokens, samples?)"""
+        for r, _, _ in parts:
+            if not eng.manager.has(r.rid):
+                eng.admit(r.rid, prompt_len=len(r.prompt), params=r.params, drawn=len(r.generated))
+        entries = [StepEntry(r.rid, toks, (len(toks) - 1,) if samples else ()) for r, toks, samples in parts]
+        logits = eng.step(entries, end=end)
+        who = [r for r, _, samples in parts if samples]
+        if who:
+            for r, t in zip(who, sampler.sample(logits, eng.slots, eng.last_want_slots, who, eng.status)):
+                r.generated.append(t)
+
+    a, b, c = reqs["a"], reqs["b"], reqs["c"]
+    step([(a, a.prompt, True), (b, b.prompt[:5], False)])
+    step([(a, a.generated[-1:], True), (b, b.prompt[5:], True), (c, c.prompt, True)])
+    for _ in range(5):
+        step([(r, r.generated[-1:], True) for r in (a, b, c)])      # from captured graphs after the first
+    slot_of = {r.rid: eng.manager.slot(r.rid) for r in (a, b, c)}
+    step([(a, a.generated[-1:], True), (c, c.generated[-1:], True)], end=["b"])
+    rec = eng.slots.cpu()
+    bits = lambda x: struct.unpack("<i", struct.pack("<f", x))[0]      # noqa: E731
+    for r in (a, c):
+        row = rec[slot_of[r.rid]].tolist()
+        assert row[kernels.SLOT_LIVE] == 1
+        assert row[kernels.SLOT_POSITION] == eng.manager.length(r.rid) == len(r.prompt) + len(r.generated) - 1
+        assert row[kernels.SLOT_PROMPT] == len(r.prompt) and row[kernels.SLOT_DRAWN] == len(r.generated)
+        assert row[kernels.SLOT_LAST] == r.generated[-1]
+        assert (row[kernels.SLOT_SEED_LO], row[kernels.SLOT_SEED_HI]) == (r.params.seed & 0xFFFFFFFF, r.params.seed >> 32)
+        assert row[kernels.SLOT_TOP_K] == r.params.top_k and row[kernels.SLOT_TEMPERATURE] == bits(r.params.temperature)
+        assert row[kernels.SLOT_TOP_P] == bits(r.params.top_p) and row[kernels.SLOT_MIN_P] == bits(r.params.min_p)
+    assert len(a.generated) == 8 and len(c.generated) == 7
+    assert rec[slot_of["b"]].tolist() == [0] * kernels.SLOT_WORDS
+    free = [s for s in range(4) if s not in (slot_of["a"], slot_of["c"])]
+    assert rec[free].abs().sum() == 0
+    # the device's record and the host's bookkeeping are compared at every step
+    eng.slots[slot_of["a"], kernels.SLOT_POSITION] += 1
+    eng.step([StepEntry("a", a.generated[-1:], ())])
+    with pytest.raises(kernels.KernelError, match="state slot"):
+        eng.check()
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16")])

@@ -118,6 +118,54 @@ def test_long_decoding(model_dirs, plain_models, dtype):
     _compare(got, want, tol, f"long decoding {dtype}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_decoding_across_a_graph_bucket_edge(model_dirs, plain_models, name, dtype):
+    """A prompt of 500 tokens and then 40 single tokens, from captured graphs: at 512 keys the captured step
+    of the first bucket gives way to the one of the next (a wider block table, another cut of the keys over
+    the blocks, the same shared graph memory)."""
+    toks = H.random_tokens(540, TINY[name]["vocab_size"], seed=21)
+    reqs = {"edge": toks}
+    act = None if dtype == "float32" else torch.bfloat16
+    want = H.plain_logits(plain_models[name], reqs, act=act)
+    tol = FP32_TOL if dtype == "float32" else 2.0 * max(
+        float((want[k] - v).abs().max()) for k, v in H.plain_logits(plain_models[name], reqs, act=None).items())
+    page_size = {"A": 4, "D": 16}[name]
+    eng = _engine(model_dirs, name, dtype, num_pages=-(-540 // page_size), page_size=page_size)
+    assert eng.use_graphs
+    got = H.replay(eng, H.cut_tail_decode(reqs, tail=40))
+    _compare(got, want, tol, f"{name} {dtype} across the bucket edge")
+    captured = {k for k, g in eng._graphs.items() if g.graph is not None}
+    assert captured == {(1, 512), (1, 1024)} and eng.graph_replays == 40 - 2
+    assert eng.stats()["graphs"] == 2 and eng.stats()["graph_output_bytes"] > 0
+
+
+def test_captured_steps_are_dropped_beyond_the_limit(model_dirs, plain_models):
+    """Decode batches of 1, 2 and 3 requests with room for two captured steps: the one used longest ago is
+    given up, captured again when its shape returns, and the logits stay right throughout."""
+    from quanta_b200.engine.model import load_model
+    from quanta_b200.engine.step import Engine
+    name = "A"
+    reqs = {f"g{i}": H.random_tokens(40, TINY[name]["vocab_size"], seed=60 + i) for i in range(3)}
+    want = H.plain_logits(plain_models[name], reqs)
+    model, _ = load_model(model_dirs[name], dtype="float32")
+    eng = Engine(model, num_pages=40, page_size=4, max_requests=4, max_graphs=2)
+    rids = list(reqs)
+    steps = [{"entries": [{"id": r, "tokens": reqs[r][:10], "want": []} for r in rids], "end": []}]
+    batches = [3, 3, 3, 2, 2, 2, 1, 1, 1, 3, 3, 3, 2, 2]        # the live requests of each decode step
+    fed = {r: 10 for r in rids}
+    for b in batches:
+        entries = []
+        for r in rids[:b]:
+            entries.append({"id": r, "tokens": [reqs[r][fed[r]]], "want": [0]})
+            fed[r] += 1
+        steps.append({"entries": entries, "end": []})
+    steps[-1]["end"] = rids
+    got = H.replay(eng, steps)
+    _compare(got, want, FP32_TOL, "captured steps dropped and captured again")
+    assert eng.stats()["graphs"] == 2 and eng.graph_replays >= 6
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_first_tokens(model_dirs, plain_models, name):
     """Positions 0, 1, 2 of a sequence, fed one at a time and as one portion."""
