@@ -1,13 +1,13 @@
 """The cache manager: pages, block tables, state slots.  Host-side bookkeeping only, no device code.
 
-* A **group** is a set of cache-writing schedule positions with the same need (kv heads, head size,
-  window).  Each group has its own pool of page ids and one block table per request: page ``i`` of a
+* A **group** is a set of cache-writing schedule positions with the same need (the mixer's
+  ``CacheSpec``: its streams and what it retains).  Each group has its own pool of page ids and one block table per request: page ``i`` of a
   request holds its positions ``[i*page_size, (i+1)*page_size)`` for every layer of the group.
   (The reference allocates per layer, src/quanta/paged/paged_kv_cache.py:229-238; layers with equal
   needs always move together, so here they share one table.)
 * Pages are reserved before a step for the positions it will write, given back when a request ends
-  and, in a windowed group, as soon as every position of a page is behind the window of all future
-  queries.  Freed pages are reused first-in first-out (src/quanta/paged/block_pool.py:67-106).
+  and as soon as the group's retention rule (``Retention.needed_ranges``: everything, a window, or a
+  rule of the mixer's own) says that no future query reads any position of the page.  Freed pages are reused first-in first-out (src/quanta/paged/block_pool.py:67-106).
 * A **state slot** is a row index into per-request state of fixed size (a mixer's own state, the
   sampler's counters).  Every live request holds exactly one.
 * Running out is an exception (``OutOfPages`` / ``OutOfSlots``) raised before anything is changed; it
@@ -21,7 +21,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from ..parts.base import KVCacheSpec
+from ..parts.base import CacheSpec, Retention
 
 
 class OutOfPages(RuntimeError):
@@ -93,15 +93,21 @@ class SlotPool:
 
 @dataclass
 class CacheGroup:
-    spec: KVCacheSpec
-    positions: list[int]                 # schedule positions whose K/V live in this group's pages
+    spec: CacheSpec
+    positions: list[int]                 # schedule positions whose streams live in this group's pages
     pool: PagePool
     tables: dict = field(default_factory=dict)     # request id -> list of page ids (-1: given back)
     arrays: dict = field(default_factory=dict)     # request id -> int32 array with the same entries (for packing a step)
+    # retention: request id -> [first page index not yet passed by the open range, held page indices below it]
+    passed: dict = field(default_factory=dict)
 
     @property
     def window(self):
         return self.spec.window
+
+    @property
+    def keeps_all(self) -> bool:
+        return type(self.spec.retention).needed_ranges is Retention.needed_ranges
 
 
 @dataclass
@@ -112,7 +118,7 @@ class RequestRecord:
 
 
 class CacheManager:
-    def __init__(self, needs: list[KVCacheSpec | None], page_size: int, num_pages: int, max_requests: int):
+    def __init__(self, needs: list[CacheSpec | None], page_size: int, num_pages: int, max_requests: int):
         """``needs[pos]``: what schedule position ``pos`` keeps (None: nothing).  Every group gets
         ``num_pages`` pages of ``page_size`` tokens."""
         if page_size <= 0 or num_pages <= 0 or max_requests <= 0:
@@ -120,7 +126,7 @@ class CacheManager:
         self.page_size = int(page_size)
         self.groups: list[CacheGroup] = []
         self.group_of: dict[int, int] = {}
-        by_spec: dict[KVCacheSpec, int] = {}
+        by_spec: dict[CacheSpec, int] = {}
         for pos, spec in enumerate(needs):
             if spec is None:
                 continue
@@ -147,6 +153,7 @@ class CacheManager:
         for g in self.groups:
             g.tables[rid] = []
             g.arrays[rid] = np.full(16, -1, dtype=np.int32)
+            g.passed[rid] = [0, []]
         return slot
 
     def length(self, rid) -> int:
@@ -154,12 +161,6 @@ class CacheManager:
 
     def slot(self, rid) -> int:
         return self.requests[rid].slot
-
-    def _first_needed_page(self, g: CacheGroup, length: int) -> int:
-        """Index of the first page a query at position >= ``length`` can still read."""
-        if g.window is None:
-            return 0
-        return max(0, length - g.window + 1) // self.page_size
 
     def pages_needed(self, rid, new_length: int) -> list[int]:
         """New pages each group must get so that positions ``[0, new_length)`` can be written (a
@@ -204,22 +205,40 @@ class CacheManager:
             raise RuntimeError(f"request {rid!r}: advancing to {rec.length + n_tokens} past its reservation {rec.reserved}")
         rec.length += n_tokens
         for g in self.groups:
-            if g.window is None:
-                continue
-            table = g.tables[rid]
-            first = min(self._first_needed_page(g, rec.length), len(table))
-            gone = [p for p in table[:first] if p >= 0]
-            if gone:
-                g.pool.give_back(gone)
-                for i in range(first):
-                    table[i] = -1
-                g.arrays[rid][:first] = -1
+            if not g.keeps_all:
+                self._release_unneeded(g, rid, rec.length)
+
+    def _release_unneeded(self, g: CacheGroup, rid, length: int) -> None:
+        """Give back the pages of ``rid`` that no query at a position >= ``length`` reads.  The last range
+        of the rule is open-ended and only moves forward; pages it has passed are looked at once when it
+        passes them and again only while an earlier (closed) range still holds them."""
+        ps = self.page_size
+        ranges = g.spec.retention.needed_ranges(length)
+        if not ranges or ranges[-1][1] is not None:
+            raise ValueError(f"{type(g.spec.retention).__name__}.needed_ranges must end with an open range")
+        table, state = g.tables[rid], g.passed[rid]
+        upto = min(ranges[-1][0] // ps, len(table))
+        if upto > state[0]:
+            state[1].extend(range(state[0], upto))
+            state[0] = upto
+        closed = ranges[:-1]
+        held, gone = [], []
+        for i in state[1]:
+            lo, hi = i * ps, (i + 1) * ps
+            (held if any(a < hi and b > lo for a, b in closed) else gone).append(i)
+        state[1] = held
+        if gone:
+            g.pool.give_back([table[i] for i in gone if table[i] >= 0])
+            for i in gone:
+                table[i] = -1
+            g.arrays[rid][gone] = -1
 
     def free(self, rid) -> None:
         rec = self.requests.pop(rid)
         for g in self.groups:
             g.pool.give_back([p for p in g.tables.pop(rid) if p >= 0])
             g.arrays.pop(rid, None)
+            g.passed.pop(rid, None)
         self.slots.give_back(rec.slot)
         if self.on_free is not None:
             self.on_free(rec.slot)

@@ -14,8 +14,8 @@ import torch
 
 from .. import matmul
 from ..config.registry import load_config
-from ..parts.base import KVCacheSpec, Part, TensorSpec, make
-from ..parts.block import Embedding, OutputHead
+from ..parts import block as _block  # noqa: F401  (registers the built-in block, embedding and head)
+from ..parts.base import CacheSpec, Part, TensorSpec, make
 from ..parts.spec import ModelSpec
 from ..weights.loader import FolderSource, RandomSource, open_fetch
 from ..weights.safetensors_io import write_safetensors
@@ -42,10 +42,9 @@ class Model:
         self.spec = spec
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
-        self.embedding = Embedding(spec.vocab_size, spec.hidden_size, spec.embedding_name)
+        self.embedding = make("embedding", spec.embedding)
         self.blocks = [make("block", choice) for choice in spec.layers]
-        self.head = OutputHead(spec.vocab_size, spec.hidden_size, spec.final_norm, spec.head_name,
-                               spec.embedding_name if spec.tied_head else None)
+        self.head = make("head", spec.head)
         self.schedule = list(spec.schedule)
         self.loaded = False
 
@@ -68,8 +67,14 @@ class Model:
         fetch = open_fetch(source, self.tensor_specs(), compute_dtype=self.dtype, device=self.device,
                            aliases=self.spec.name_aliases, ignored_prefixes=self.spec.ignored_prefixes,
                            ignorable=ignorable)
+        # a tensor that several parts ask for by the same name (a head tied to the embedding table) is
+        # loaded once and shared
         shared: dict[str, torch.Tensor] = {}
-        share = {self.spec.embedding_name} if self.spec.tied_head else set()
+        asked: dict[str, int] = {}
+        for p in self.parts():
+            for ts in p.tensor_specs():
+                asked[ts.name] = asked.get(ts.name, 0) + 1
+        share = {name for name, n in asked.items() if n > 1}
 
         def fetch_shared(name):
             if name in share:
@@ -84,7 +89,7 @@ class Model:
         return self
 
     # ---- what the cache manager needs to know ---------------------------------------------------
-    def cache_needs(self) -> list[KVCacheSpec | None]:
+    def cache_needs(self) -> list[CacheSpec | None]:
         """For each schedule position that writes a cache, the mixer's need (None: the mixer keeps none)."""
         return [None if e.read_cache_of is not None else self.blocks[e.layer].mixer.cache_spec()
                 for e in self.schedule]

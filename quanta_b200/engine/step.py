@@ -72,12 +72,12 @@ class Engine:
         self.page_size = int(page_size)
         needs = model.cache_needs()
         self.manager = CacheManager(needs, page_size, num_pages, max_requests)
-        self.kv: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+        # per cache-writing schedule position: the pages of every stream its mixer declared
+        self.kv: dict[int, dict[str, torch.Tensor]] = {}
         for pos, spec in enumerate(needs):
             if spec is not None:
-                shape = (num_pages, spec.n_kv_heads, page_size, spec.head_dim)
-                self.kv[pos] = (torch.zeros(shape, dtype=model.dtype, device=self.device),
-                                torch.zeros(shape, dtype=model.dtype, device=self.device))
+                self.kv[pos] = {st.name: torch.zeros((num_pages, st.heads, page_size, st.width), dtype=model.dtype,
+                                                     device=self.device) for st in spec.streams}
         self.state: list[dict[str, torch.Tensor]] = []
         for need in model.state_needs():
             self.state.append({name: torch.zeros((max_requests, *shape), dtype=dt, device=self.device)
@@ -245,8 +245,8 @@ class Engine:
         for pos, entry in enumerate(self.model.schedule):
             src = pos if entry.read_cache_of is None else entry.read_cache_of
             if src in self.kv:
-                k, v = self.kv[src]
-                caches.append(LayerCache(k, v, self.page_size, d_tables[self.manager.group_of[src]],
+                caches.append(LayerCache(streams=self.kv[src], page_size=self.page_size,
+                                         block_table=d_tables[self.manager.group_of[src]],
                                          write=entry.read_cache_of is None))
             else:
                 caches.append(None)

@@ -1,8 +1,9 @@
 """What a part is, and the registries parts are chosen from.
 
-A model is put together from parts of five kinds: ``mixer`` (attention here), ``feed_forward``
-(dense or routed experts), ``norm``, ``position`` (position encoding) and ``block`` (how a layer
-arranges the other four).  A part takes every size and constant as a constructor parameter, names
+A model is put together from parts of seven kinds: ``mixer`` (attention here), ``feed_forward``
+(dense or routed experts), ``norm``, ``position`` (position encoding), ``block`` (how a layer
+arranges the other four), ``embedding`` (token ids to the residual stream) and ``head`` (the residual
+stream to logits).  A part takes every size and constant as a constructor parameter, names
 the checkpoint tensors it needs (``tensor_specs``), receives them (``load``) and runs on the tokens
 of one step (``forward``).  No part knows which model it is in; an architecture is a function from
 its configuration to a ``ModelSpec`` that names parts and parameters layer by layer.
@@ -18,7 +19,7 @@ from typing import Any, Callable
 
 import torch
 
-KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+KINDS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
 _REGISTRY: dict[str, dict[str, type]] = {k: {} for k in KINDS}
 
 
@@ -64,26 +65,89 @@ class TensorSpec:
 
 
 @dataclass(frozen=True)
-class KVCacheSpec:
-    """A mixer's need of paged keys and values: layers with equal specs share pages and block tables."""
-    n_kv_heads: int
-    head_dim: int
-    window: int | None = None          # None: all keys are kept; W: only the last W positions
+class CacheStream:
+    """One paged tensor a mixer keeps per token: ``heads`` rows of ``width`` elements in the activation
+    dtype.  Softmax attention keeps two (keys and values); a mixer that attends over one latent vector
+    keeps one; widths need not be equal."""
+    name: str
+    heads: int
+    width: int
 
 
-@dataclass
+@dataclass(frozen=True)
+class Retention:
+    """Which cached positions a request's future queries can still read.  The cache manager gives a
+    page back as soon as no position of it is needed any more, and never asks again about a page it
+    gave back, so what is needed may only shrink as the request grows.  The base keeps everything."""
+
+    def needed_ranges(self, length: int) -> list[tuple[int, int | None]]:
+        """Half-open position ranges ``(lo, hi)`` that queries at positions ``>= length`` may read, given
+        that ``length`` tokens are cached; ``hi`` None: no upper end.  The last range must be open."""
+        return [(0, None)]
+
+
+@dataclass(frozen=True)
+class KeepAll(Retention):
+    pass
+
+
+@dataclass(frozen=True)
+class Window(Retention):
+    """A query at position p reads the keys ``p - window + 1 .. p`` only."""
+    window: int = 1
+
+    def needed_ranges(self, length):
+        return [(max(0, length - self.window + 1), None)]
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """A mixer's need of paged per-token storage: its streams and what is retained.  Layers with equal
+    specs form one group of the cache manager: they share pages ids and block tables."""
+    streams: tuple[CacheStream, ...]
+    retention: Retention = KeepAll()
+
+    @property
+    def window(self) -> int | None:
+        return getattr(self.retention, "window", None)
+
+
+def KVCacheSpec(n_kv_heads: int, head_dim: int, window: int | None = None) -> CacheSpec:
+    """Keys and values of softmax attention: two streams of ``n_kv_heads`` x ``head_dim``; ``window`` None:
+    all keys are kept, W: only the last W positions."""
+    return CacheSpec((CacheStream("k", n_kv_heads, head_dim), CacheStream("v", n_kv_heads, head_dim)),
+                     KeepAll() if window is None else Window(int(window)))
+
+
 class LayerCache:
-    """What a mixer sees of the cache in one step: its own K/V pages and its group's block table."""
-    k: torch.Tensor                    # [num_pages, n_kv, page_size, head_dim]
-    v: torch.Tensor
-    page_size: int
-    block_table: torch.Tensor          # int32 [requests in the step, pages per request]
-    write: bool = True                 # False: this layer reads a cache another layer wrote
+    """What a mixer sees of the cache in one step: its own pages of every stream it declared
+    (``streams[name]`` ``[num_pages, heads, page_size, width]``) and its group's block table (int32
+    ``[requests in the step, pages per request]``, -1 where a page was given back).  ``write`` False:
+    this layer reads a cache another layer wrote.  ``k`` / ``v`` are the streams of those names."""
+
+    def __init__(self, k=None, v=None, page_size: int = 0, block_table=None, write: bool = True, streams=None):
+        self.streams = dict(streams) if streams is not None else {"k": k, "v": v}
+        self.page_size, self.block_table, self.write = page_size, block_table, write
+
+    @property
+    def k(self):
+        return self.streams["k"]
+
+    @property
+    def v(self):
+        return self.streams["v"]
 
 
 @dataclass
 class StepContext:
-    """Per-step facts every part may read.  All tensors are on the device; ``T`` tokens in the step."""
+    """Per-step facts every part may read.  All tensors are on the device; ``T`` tokens in the step.
+
+    The tokens of request row ``r`` are the rows ``req_start[r] .. req_start[r+1]`` of every activation,
+    in position order; its per-request state (a mixer's ``state_spec``) is row ``req_slot[r]`` of each
+    state tensor.  A part that reads only these device arrays (no ``host``, no ``.item()``) may declare
+    itself ``graph_safe``; one part that is not turns captured decode steps off for the whole model.
+    ``positions`` carries one coordinate per position axis; the step function feeds every axis the
+    token's text position (a caller cannot hand a token several coordinates: image inputs are not built)."""
     n_tokens: int
     positions: torch.Tensor            # int32 [T, axes]   position fed to the position encoding
     tok_pos: torch.Tensor              # int32 [T]         index of the token in its request's cache
@@ -139,7 +203,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_spec(self) -> KVCacheSpec | None:
+    def cache_spec(self) -> CacheSpec | None:
+        """What the mixer keeps per token in pages (streams and retention); None: nothing."""
         return None
 
     def state_spec(self) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
@@ -156,6 +221,21 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Token ids to the float32 residual stream: ``forward(ids int32 [T], ctx) -> [T, hidden]``."""
+
+    def forward(self, ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The residual stream to logits: ``forward(h, pending, rows, ctx)`` adds the last layer's pending
+    contribution for the wanted token rows ``rows`` (int32) and returns float32 ``[len(rows), vocab]``."""
+
+    def forward(self, h: torch.Tensor, pending, rows: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 

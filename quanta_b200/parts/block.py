@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import Block, Part, TensorSpec, make, register
+from .base import Block, Embedding, Head, TensorSpec, make, register
 
 
 @register("block", "pre_norm")
@@ -37,7 +37,8 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(x2, ctx)
 
 
-class Embedding(Part):
+@register("embedding", "token_table")
+class TokenTable(Embedding):
     """``h = table[ids]`` into the float32 residual stream (src/quanta/minimax/model.py:91)."""
 
     graph_safe = True
@@ -58,9 +59,11 @@ class Embedding(Part):
         return h
 
 
-class OutputHead(Part):
+@register("head", "linear")
+class LinearHead(Head):
     """Final norm on the wanted rows, then ``logits = x @ head.T`` in float32
-    (src/quanta/minimax/runtime.py:95-98).  ``tied_to`` names the embedding table to reuse."""
+    (src/quanta/minimax/runtime.py:95-98).  ``tied_to`` names the embedding table to reuse (a tensor that
+    two parts ask for by the same name is loaded once and shared)."""
 
     graph_safe = True
 
@@ -74,7 +77,7 @@ class OutputHead(Part):
         return [self.norm]
 
     def tensor_specs(self):
-        return [] if self.tied_to else [TensorSpec(self.weight_name, (self.V, self.H))]
+        return [TensorSpec(self.tied_to if self.tied_to else self.weight_name, (self.V, self.H))]
 
     def load(self, fetch):
         self.weight = fetch(self.tied_to if self.tied_to else self.weight_name)

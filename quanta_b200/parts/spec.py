@@ -29,8 +29,19 @@ class ModelSpec:
     schedule: list[ScheduleEntry] = field(default_factory=list)
     ignored_prefixes: tuple[str, ...] = ()     # checkpoint tensors that are not this model's and are skipped
     name_aliases: tuple[tuple[str, str], ...] = ()   # (prefix in file, prefix in spec) rewrites
+    # ("embedding part name", params) and ("head part name", params); None: the token table and the
+    # normed linear head described by the fields above
+    embedding: tuple[str, dict] | None = None
+    head: tuple[str, dict] | None = None
 
     def __post_init__(self):
+        if self.embedding is None:
+            self.embedding = ("token_table", dict(vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                                                  weight_name=self.embedding_name))
+        if self.head is None:
+            self.head = ("linear", dict(vocab_size=self.vocab_size, hidden_size=self.hidden_size, norm=self.final_norm,
+                                        weight_name=self.head_name,
+                                        tied_to=self.embedding_name if self.tied_head else None))
         if not self.schedule:
             self.schedule = [ScheduleEntry(i) for i in range(len(self.layers))]
         for pos, e in enumerate(self.schedule):

@@ -229,3 +229,48 @@ def test_random_workloads_always_terminate_and_free_everything():
         assert all(len(r.generated) == r.params.max_new_tokens for r in reqs if r.finish_reason == "length")
         assert m.stats()["live_requests"] == 0
         assert all(g.pool.free_count == g.pool.num_pages for g in m.groups)
+
+
+def test_a_retention_rule_of_the_mixers_own():
+    """The rule is the spec's: the first six positions and a window of ten.  Pages between them go back as the
+    window passes them, the sinks' pages never do, and a page is asked about only while it is held."""
+    from dataclasses import dataclass
+    from quanta_b200.parts.base import CacheSpec, CacheStream, Retention
+
+    @dataclass(frozen=True)
+    class SinksAndWindow(Retention):
+        sinks: int = 6
+        window: int = 10
+
+        def needed_ranges(self, length):
+            return [(0, self.sinks), (max(0, length - self.window + 1), None)]
+
+    spec = CacheSpec((CacheStream("latent", 1, 24),), SinksAndWindow())
+    m = CacheManager([spec, FULL], page_size=4, num_pages=40, max_requests=2)
+    assert len(m.groups) == 2
+    g = m.groups[0]
+    m.add_request("a")
+    length = 0
+    for n in (3, 9, 1, 1, 14, 1, 1, 1, 30, 1):
+        m.reserve("a", length + n)
+        m.advance("a", n)
+        length += n
+        held = [i for i, p in enumerate(g.tables["a"]) if p >= 0]
+        first_in_window = max(0, length - 10 + 1) // 4
+        want = sorted(set(i for i in (0, 1) if i * 4 < length) | set(range(first_in_window, -(-length // 4))))
+        assert held == want, (length, held, want)
+        m.check_invariants()
+    assert g.pool.used_count == len(held) and m.groups[1].pool.used_count == -(-length // 4)
+    m.free("a")
+    assert g.pool.used_count == 0
+    m.check_invariants()
+
+    @dataclass(frozen=True)
+    class Broken(Retention):
+        def needed_ranges(self, length):
+            return [(0, 4)]
+    bad = CacheManager([CacheSpec((CacheStream("x", 1, 8),), Broken())], page_size=4, num_pages=8, max_requests=1)
+    bad.add_request("a")
+    bad.reserve("a", 5)
+    with pytest.raises(ValueError, match="open range"):
+        bad.advance("a", 5)

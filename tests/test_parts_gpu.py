@@ -57,7 +57,7 @@ def test_norm_attention_experts_alone(model_dirs, plain_models, name):
     page = 4
     n_pages = -(-T // page)
     spec = blk.mixer.cache_spec()
-    kc = torch.zeros(n_pages, spec.n_kv_heads, page, spec.head_dim, device=DEV)
+    kc = torch.zeros(n_pages, spec.streams[0].heads, page, spec.streams[0].width, device=DEV)
     cache = LayerCache(kc, torch.zeros_like(kc), page, torch.arange(n_pages, dtype=torch.int32, device=DEV).view(1, -1))
     got = blk.mixer.forward(x.to(DEV), ctx, cache, {})
     W = lambda n: weights[p + "self_attn." + n].float()     # noqa: E731
@@ -299,6 +299,167 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     for cut in (H.cut_whole(reqs), H.cut_portions(reqs), H.cut_mixed(reqs, 3, seed=2), H.cut_mixed(reqs, 2, seed=9)):
         got = H.replay(eng, cut)       # a slot is zeroed when the next request takes it
         assert H.first_wrong(got, want, 1e-4) is None
+
+
+def _register_cache_toys():
+    from dataclasses import dataclass
+    from quanta_b200.parts.base import CacheSpec, CacheStream, Embedding, Head, Mixer, Retention, TensorSpec, register
+
+    @dataclass(frozen=True)
+    class SinksAndWindow(Retention):
+        """The first ``sinks`` positions stay readable for ever, beside a window of the last ``window``."""
+        sinks: int = 4
+        window: int = 8
+
+        def needed_ranges(self, length):
+            return [(0, self.sinks), (max(0, length - self.window + 1), None)]
+
+    @register("mixer", "toy_latent_attention")
+    class LatentAttention(Mixer):
+        """Attention over ONE cached stream: each token leaves a 24-wide vector that serves as key and as
+        value (no second stream), read by later tokens at the first ``sinks`` positions and inside a window."""
+
+        def __init__(self, hidden_size, width, sinks, window, names):
+            self.H, self.W, self.sinks, self.window, self.names = hidden_size, width, sinks, window, names
+            self.down = self.q = self.up = None
+
+        def tensor_specs(self):
+            n = self.names
+            return [TensorSpec(n["down"], (self.W, self.H)), TensorSpec(n["q"], (self.W, self.H)),
+                    TensorSpec(n["up"], (self.H, self.W))]
+
+        def load(self, fetch):
+            self.down, self.q, self.up = (fetch(self.names[k]) for k in ("down", "q", "up"))
+
+        def cache_spec(self):
+            return CacheSpec((CacheStream("latent", 1, self.W),), SinksAndWindow(self.sinks, self.window))
+
+        def forward(self, x, ctx, cache, state):
+            pages, ps = cache.streams["latent"], cache.page_size         # [num_pages, 1, page_size, W]
+            c = x.float() @ self.down.float().T
+            q = x.float() @ self.q.float().T
+            out = torch.empty_like(c)
+            starts, after = ctx.host["req_start"], ctx.host["req_len_after"]
+            table = cache.block_table.cpu()
+            for r in range(len(starts) - 1):                              # a toy: plain torch, a token at a time
+                t0, n = starts[r], starts[r + 1] - starts[r]
+                first = after[r] - n
+                for i in range(n):
+                    p = first + i
+                    pages[int(table[r, p // ps]), 0, p % ps] = c[t0 + i].to(pages.dtype)
+                for i in range(n):
+                    p = first + i
+                    keys = [j for j in range(p + 1) if j < self.sinks or j > p - self.window]
+                    assert all(int(table[r, j // ps]) >= 0 for j in keys), "a page the rule needs was given back"
+                    cj = torch.stack([pages[int(table[r, j // ps]), 0, j % ps] for j in keys]).float()
+                    w = torch.softmax((cj @ q[t0 + i]) * self.W ** -0.5, 0)
+                    out[t0 + i] = w @ cj
+            return (out @ self.up.float().T).to(x.dtype)
+
+    @register("embedding", "toy_scaled_table")
+    class ScaledTable(Embedding):
+        def __init__(self, vocab_size, hidden_size, weight_name, scale):
+            self.V, self.H, self.weight_name, self.scale = vocab_size, hidden_size, weight_name, scale
+
+        def tensor_specs(self):
+            return [TensorSpec(self.weight_name, (self.V, self.H))]
+
+        def load(self, fetch):
+            self.table = fetch(self.weight_name)
+
+        def forward(self, ids, ctx):
+            return self.table[ids.long()].float() * self.scale
+
+    @register("head", "toy_scaled_head")
+    class ScaledHead(Head):
+        """Logits times a constant, from the embedding table; the pending sum and the norm in plain torch."""
+
+        def __init__(self, vocab_size, hidden_size, table_name, norm_name, eps, logit_scale):
+            self.V, self.H, self.table_name, self.norm_name = vocab_size, hidden_size, table_name, norm_name
+            self.eps, self.logit_scale = eps, logit_scale
+
+        def tensor_specs(self):
+            return [TensorSpec(self.table_name, (self.V, self.H)), TensorSpec(self.norm_name, (self.H,), "f32", "gain")]
+
+        def load(self, fetch):
+            self.table, self.gain = fetch(self.table_name), fetch(self.norm_name)
+
+        def forward(self, h, pending, rows, ctx):
+            x = h[rows.long()]
+            if pending is not None:
+                add = pending[rows.long()].float()
+                x = x + (add if add.dim() == 2 else add.sum(1))
+            x = self.gain * x * torch.rsqrt((x * x).mean(-1, keepdim=True) + self.eps)
+            return (x @ self.table.float().T) * self.logit_scale
+
+
+def _cache_toy_plain(ws, ids, cfg):
+    """Whole-sequence plain version: scaled embedding, [norm, latent attention, norm, two-way] x 2, scaled head."""
+    T = len(ids)
+    h = ws["emb"][torch.tensor(ids)].float() * cfg["emb_scale"]
+    j, p = torch.arange(T)[None, :], torch.arange(T)[:, None]
+    mask = (j <= p) & ((j < cfg["sinks"]) | (j > p - cfg["window"]))
+    for L in range(2):
+        x = P.rms_norm(h, ws[f"n{L}a"], cfg["eps"])
+        c, q = x @ ws[f"down{L}"].float().T, x @ ws[f"q{L}"].float().T
+        s = ((q @ c.T) * cfg["width"] ** -0.5).masked_fill(~mask, float("-inf"))
+        h = h + (torch.softmax(s, -1) @ c) @ ws[f"up{L}"].float().T
+        x = P.rms_norm(h, ws[f"n{L}b"], cfg["eps"])
+        pick = (x[:, :1] > 0).float()
+        h = h + x * (pick * cfg["scales"][0] + (1 - pick) * cfg["scales"][1])
+    return (P.rms_norm(h, ws["nf"], cfg["eps"]) @ ws["emb"].float().T) * cfg["logit_scale"]
+
+
+def test_toy_cache_stream_retention_rule_embedding_and_head():
+    """What a new architecture may bring without a change to the framework's files: a mixer that keeps one
+    stream of its own width instead of keys and values, a rule of its own for which positions stay readable
+    (the first four and a window; the manager gives the pages between back), an embedding and an output
+    head of its own.  Built from a specification, stepped under the four cuttings with as few pages as the
+    rule allows, against the whole-sequence plain version."""
+    from quanta_b200.engine.model import Model
+    from quanta_b200.engine.step import Engine
+    from quanta_b200.parts.spec import ModelSpec
+    from quanta_b200.weights import DictSource, RandomSource
+    _register_toys()
+    _register_cache_toys()
+    cfg = dict(eps=1e-5, sinks=4, window=9, width=24, scales=(0.5, -0.25), emb_scale=3.0, logit_scale=0.25)
+    Hd, V = 40, 97
+    norm = lambda n: ("rms_norm", dict(width=Hd, eps=cfg["eps"], weight_name=n))      # noqa: E731
+    layers = [("pre_norm", dict(hidden_size=Hd, mixer=("toy_latent_attention", dict(
+        hidden_size=Hd, width=cfg["width"], sinks=cfg["sinks"], window=cfg["window"],
+        names={"down": f"down{L}", "q": f"q{L}", "up": f"up{L}"})),
+        feed_forward=("toy_two_way_routing", dict(hidden_size=Hd, scales=cfg["scales"])),
+        mixer_norm=norm(f"n{L}a"), feed_forward_norm=norm(f"n{L}b"))) for L in range(2)]
+    spec = ModelSpec(name="cache toy", vocab_size=V, hidden_size=Hd, embedding_name="emb", layers=layers,
+                     final_norm=norm("nf"), head_name=None, tied_head=True,
+                     embedding=("toy_scaled_table", dict(vocab_size=V, hidden_size=Hd, weight_name="emb", scale=cfg["emb_scale"])),
+                     head=("toy_scaled_head", dict(vocab_size=V, hidden_size=Hd, table_name="emb", norm_name="nf",
+                                                   eps=cfg["eps"], logit_scale=cfg["logit_scale"])))
+    model = Model(spec, dtype="float32")
+    assert [s.name for s in model.tensor_specs()].count("emb") == 1            # asked for twice, loaded once
+    src = RandomSource(model.tensor_specs(), seed=4, matrix_dtype=torch.float32)
+    ws = {n: src.read(n, "cpu") for n in src.names()}
+    model.load(DictSource(ws))
+    assert model.head.table is model.embedding.table
+    reqs = {"a": H.random_tokens(61, V, 1), "b": H.random_tokens(33, V, 2), "c": H.random_tokens(47, V, 3)}
+    want = {}
+    for rid, toks in reqs.items():
+        lg = _cache_toy_plain(ws, toks, cfg)
+        want.update({(rid, i): lg[i] for i in range(len(toks))})
+    page = 4
+    for what, cut in (("whole", H.cut_whole(reqs)), ("tail", H.cut_tail_decode(reqs, 32)),
+                      ("portions", H.cut_portions(reqs)), ("mixed", H.cut_mixed(reqs, 3, seed=2))):
+        eng = Engine(model, num_pages=H.tokens_in_flight(cut, page) // page, page_size=page, max_requests=3)
+        assert not eng.use_graphs                                 # the toy reads host copies
+        (group,) = eng.manager.groups
+        assert [(s.name, s.heads, s.width) for s in group.spec.streams] == [("latent", 1, 24)]
+        assert set(eng.kv[0]) == {"latent"} and eng.kv[0]["latent"].shape[1:] == (1, page, 24)
+        got = H.replay(eng, cut)
+        eng.manager.check_invariants()
+        assert H.first_wrong(got, want, 1e-4) is None, (what, H.worst_error(got, want))
+        if what != "whole":
+            # decoding request a to 61 tokens never held more than the sinks' page, the window's and the step's
+            assert group.pool.high_water < sum(-(-len(t) // page) for t in reqs.values())
 
 
 def test_toy_position_encoding_in_the_real_attention(model_dirs):
