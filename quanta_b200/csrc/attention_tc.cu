@@ -6,9 +6,7 @@
 // swizzle, V is the MN-major operand exactly as it lies in the cache), S and O live in TMEM, and softmax
 // warps turn S into P between the two products (tcgen05.ld, float32 online softmax in the exp2 domain,
 // P as bfloat16 into the swizzled tile).  K and V come by TMA tensor loads, one box per page and 64-dim
-// slab.  Two kernels, described where they stand: two query tiles a block with O accumulated in
-// registers, and one query tile a block with O accumulated in TMEM (the one that runs unless
-// QUANTA_B200_SPAN_KERNEL=tc2).
+// slab.  One query tile a block, O accumulated in TMEM; the kernel is described where it stands.
 //
 // (src/quanta/minimax/attention.py:194-203: scores * head_dim^-0.5, causal mask, softmax in float32,
 // probabilities cast to the activation dtype, P V; q head h reads kv head h / (n_q / n_kv).)
@@ -148,363 +146,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Two query tiles per block (256 rows): the tensor pipe works for one tile while the softmax warps of
-// the other one work, two softmax warps share each scheduler, and a K/V block is read once for 256 rows.
-//
-//   warp 0: TMA producer of K blocks (two stages), warp 1: of V blocks (one stage), warp 2: MMA issuer,
-//   warp 3: idle; warps 4-7: softmax of tile A (rows 0..127), warps 8-11: of tile B (rows 128..255).
-//   TMEM: S_A, S_B, O_A, O_B, 128 columns each.  Per tile and block j a softmax thread waits for S(j),
-//   takes the row maximum, adds O(j-1) (the P V of the block before), writes P(j) and arrives; the issuer
-//   then starts P V (j) and S(j+1) of that tile and turns to the other tile.
-//   The softmax warps hold 128 accumulators a thread: the three warpgroups re-divide the registers
-//   (setmaxnreg) so that the 256 softmax threads have 224 each.
-// ------------------------------------------------------------------------------------------------
-constexpr int TC2_THREADS = 12 * 32;
-
-struct Tc2Shared {
-  uint64_t k_full[2], k_empty[2], v_full, v_empty, s_full[2], o_full[2], p_full[2];
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-__global__ void __launch_bounds__(TC2_THREADS, 1)
-attn_span_tc2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
-                     const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
-                     const int* __restrict__ tiles, int nq, int nkv, int page_size, int num_pages,
-                     float scale_log2, int window, int* status) {
-  extern __shared__ unsigned char smem_dyn[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  // Q_A, Q_B, P_A, P_B, K stage 0, K stage 1, V
-  const uint32_t q_s = smem_u32(base), p_s = q_s + 2 * TC_TILE_BYTES, k_s = p_s + 2 * TC_TILE_BYTES,
-                 v_s = k_s + 2 * TC_TILE_BYTES;
-  __shared__ Tc2Shared sh;
-  volatile int* abort_flag = &sh.abort_flag;
-
-  const int* tile = tiles + 4 * blockIdx.x;
-  const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
-  const int kvh = blockIdx.y, G = nq / nkv;
-  const int n_rows = min(2 * TC_BM, n_tok * G - row0);           // of both tiles
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int* bt = block_table + (size_t)req * bt_stride;
-  const bool has_b = n_rows > TC_BM;
-
-  const int first_tok = tok0 + row0 / G;
-  const int last_tok_a = tok0 + (row0 + min(n_rows, TC_BM) - 1) / G, last_tok = tok0 + (row0 + n_rows - 1) / G;
-  const int key_end = tok_pos[last_tok], key_end_a = tok_pos[last_tok_a];
-  const int p_first = tok_pos[first_tok];
-  const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;   // the lowest key any row reads
-  const int key_begin = lo_min / TC_BN * TC_BN;
-  const int n_blocks = (key_end - key_begin) / TC_BN + 1;          // tile B's (the later rows) or the only tile's
-  const int n_blocks_a = (key_end_a - key_begin) / TC_BN + 1;      // tile A stops here
-
-  // Q rows of both tiles into their swizzled tiles (zero past the last row); the K and V stages start as
-  // zeros, so that rows no copy covers hold zeros or older keys, never anything that is not a number
-  for (int c = tid; c < 2 * TC_BM * (TC_HD / 8); c += TC2_THREADS) {
-    const int r = c / (TC_HD / 8), ch = c % (TC_HD / 8);      // 16-byte chunk ch of row r (of 256)
-    const int R = row0 + r;
-    const bool ok = r < n_rows;
-    const __nv_bfloat16* src = q;
-    if (ok) src = q + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD + ch * 8;
-    const int rt = r & (TC_BM - 1);
-    cp_async16(q_s + (r >> 7) * TC_TILE_BYTES + (ch >> 3) * TC_SLAB_BYTES + rt * 128 + (((ch & 7) ^ (rt & 7)) << 4), src, ok);
-  }
-  asm volatile("cp.async.commit_group;\n" ::);
-  for (uint32_t i = tid; i < 3 * TC_TILE_BYTES / 16; i += TC2_THREADS)
-    reinterpret_cast<uint4*>(base + 4 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
-  if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&sh.k_full[s]), 1);
-      mbar_init(smem_u32(&sh.k_empty[s]), 1);
-      mbar_init(smem_u32(&sh.s_full[s]), 1);
-      mbar_init(smem_u32(&sh.o_full[s]), 1);
-      mbar_init(smem_u32(&sh.p_full[s]), 128);
-    }
-    mbar_init(smem_u32(&sh.v_full), 1);
-    mbar_init(smem_u32(&sh.v_empty), 1);
-    sh.abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 2) {      // the whole TMEM: S and O of both tiles, 128 columns each
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&sh.tmem_base)), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("cp.async.wait_group 0;\n" ::);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // Q and the zeros, before TMA and the MMAs
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = sh.tmem_base;
-
-  if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
-    if (warp < 2) {
-      // ---------------- TMA producers: warp 0 streams K blocks (two stages), warp 1 V blocks (one) ----------------
-      const CUtensorMap* map = warp == 0 ? &tm_k : &tm_v;
-      const int box_rows = min(page_size, TC_BN);
-      bool ok = true;
-      for (int b = 0; b < n_blocks && ok; ++b) {
-        const int slot = warp == 0 ? (b & 1) : 0;
-        const uint32_t ph = warp == 0 ? ((uint32_t)(b >> 1) & 1u) : ((uint32_t)b & 1u);
-        const uint32_t empty = warp == 0 ? smem_u32(&sh.k_empty[slot]) : smem_u32(&sh.v_empty);
-        const uint32_t bar = warp == 0 ? smem_u32(&sh.k_full[slot]) : smem_u32(&sh.v_full);
-        const uint32_t dst0 = warp == 0 ? k_s + slot * TC_TILE_BYTES : v_s;
-        ok = __all_sync(0xffffffffu, mbar_wait(empty, ph ^ 1u, abort_flag) ? 1 : 0);
-        if (!ok) break;
-        const int key0 = key_begin + b * TC_BN;
-        const int n_keys = min(TC_BN, key_end - key0 + 1);
-        const int n_req = 2 * ((n_keys + box_rows - 1) / box_rows);      // boxes: pages with visible keys x two slabs
-        // a page id outside the pool is recorded and its rows are not copied (the byte count must match);
-        // keys before every row's window are not fetched: their pages may have been given back already
-        int skipped = 0;
-        for (int i = lane; i < n_req; i += 32) {
-          const int key = key0 + (i >> 1) * box_rows;
-          if (key + box_rows - 1 < lo_min) { ++skipped; continue; }
-          const int pg = bt[key / page_size];
-          if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++skipped; }
-        }
-        skipped = __reduce_add_sync(0xffffffffu, skipped);
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_req - skipped) * (uint32_t)box_rows * 128u);
-        __syncwarp();
-        for (int i = lane; i < n_req; i += 32) {
-          const int slab = i & 1, box = i >> 1;
-          const int key = key0 + box * box_rows;
-          if (key + box_rows - 1 < lo_min) continue;
-          const int pg = bt[key / page_size];
-          if (pg < 0 || pg >= num_pages) continue;
-          const int row = (pg * nkv + kvh) * page_size + key % page_size;
-          tma_load_box(dst0 + slab * TC_SLAB_BYTES + box * box_rows * 128, map, slab * 64, row, bar);
-        }
-      }
-      if (!ok) {
-        // gave up: let the copies already issued land before the block's shared memory is given away
-        const uint64_t t0 = global_ns();
-        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
-      }
-    } else if (warp == 2 && lane == 0) {
-      // ---------------- MMA issuer ----------------
-      const uint32_t idesc_qk = umma_idesc(TC_BM, TC_BN, false), idesc_pv = umma_idesc(TC_BM, TC_HD, true);
-      bool ok = true;
-      // S_x = Q_x K_i^T (x: tile 0 or 1); the K stage must be full already
-      auto issue_qk = [&](int x, int i) {
-        const uint32_t kt = k_s + (i & 1) * TC_TILE_BYTES, qt = q_s + x * TC_TILE_BYTES;
-#pragma unroll
-        for (int k16 = 0; k16 < TC_HD / 16; ++k16) {
-          const uint32_t off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
-          umma_bf16(tmem_base + (uint32_t)(x * TC_BN), umma_desc(qt + off, 0), umma_desc(kt + off, 0), idesc_qk,
-                    k16 != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sh.s_full[x]));
-      };
-      // O_x = P_x V_j
-      auto issue_pv = [&](int x) {
-        const uint32_t pt = p_s + x * TC_TILE_BYTES;
-#pragma unroll
-        for (int k16 = 0; k16 < TC_BN / 16; ++k16) {
-          const uint32_t a_off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
-          umma_bf16(tmem_base + (uint32_t)(2 * TC_BN + x * TC_HD), umma_desc(pt + a_off, 0),
-                    umma_desc(v_s + k16 * 2048, TC_SLAB_BYTES), idesc_pv, k16 != 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sh.o_full[x]));
-      };
-      auto wait_k = [&](int i) {
-        ok = mbar_wait(smem_u32(&sh.k_full[i & 1]), (uint32_t)(i >> 1) & 1u, abort_flag);
-        if (ok) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      };
-      wait_k(0);
-      if (ok) {
-        issue_qk(0, 0);
-        if (has_b) issue_qk(1, 0);
-        umma_commit(smem_u32(&sh.k_empty[0]));
-      }
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const bool a_here = j < n_blocks_a, a_next = j + 1 < n_blocks_a, next = j + 1 < n_blocks;
-        ok = mbar_wait(smem_u32(&sh.v_full), (uint32_t)j & 1u, abort_flag);
-        if (!ok) break;
-        if (a_here) {
-          ok = mbar_wait(smem_u32(&sh.p_full[0]), (uint32_t)j & 1u, abort_flag);       // P_A(j) written, S_A(j) and O_A(j-1) read
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_pv(0);
-        }
-        if (next) {
-          wait_k(j + 1);
-          if (!ok) break;
-          if (a_next) issue_qk(0, j + 1);
-        }
-        if (has_b) {
-          ok = mbar_wait(smem_u32(&sh.p_full[1]), (uint32_t)j & 1u, abort_flag);
-          if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_pv(1);
-        }
-        umma_commit(smem_u32(&sh.v_empty));              // V(j) is free once both P V have read it
-        if (next) {
-          if (has_b) issue_qk(1, j + 1);
-          umma_commit(smem_u32(&sh.k_empty[(j + 1) & 1]));
-        }
-      }
-    }
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
-    // ---------------- softmax: one row a thread; warps 4-7 tile A, warps 8-11 tile B ----------------
-    const int x = (warp - 4) >> 2;                        // the tile
-    const int quad = warp & 3;
-    const int rt = quad * 32 + lane;                      // row within the tile
-    const int r = x * TC_BM + rt;
-    const int R = row0 + r;
-    const bool valid = r < n_rows;
-    const int my_blocks = x == 0 ? n_blocks_a : (has_b ? n_blocks : 0);
-    const int pos_r = valid ? tok_pos[tok0 + R / G] : -1;
-    const int lo_r = (window > 0 && pos_r - window + 1 > 0) ? pos_r - window + 1 : 0;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t s_addr = lane_addr + (uint32_t)(x * TC_BN), o_addr = lane_addr + (uint32_t)(2 * TC_BN + x * TC_HD);
-    const uint32_t p_row = p_s + x * TC_TILE_BYTES + rt * 128;
-    float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-    float o[TC_HD];
-#pragma unroll
-    for (int i = 0; i < TC_HD; ++i) o[i] = 0.f;
-    bool ok = true;
-    // o = o * corr + the tile's O buffer
-    auto add_block = [&](float corr) {
-      uint32_t va[16], vb[16];
-      tmem_ld16(o_addr, va);
-#pragma unroll
-      for (int c = 0; c < TC_HD / 16; c += 2) {
-        tmem_wait_ld();
-        tmem_ld16(o_addr + (uint32_t)((c + 1) * 16), vb);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[c * 16 + i] = o[c * 16 + i] * corr + __uint_as_float(va[i]);
-        tmem_wait_ld();
-        if (c + 2 < TC_HD / 16) tmem_ld16(o_addr + (uint32_t)((c + 2) * 16), va);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[(c + 1) * 16 + i] = o[(c + 1) * 16 + i] * corr + __uint_as_float(vb[i]);
-      }
-    };
-    // Iteration j: the maximum of block j, then block j-1's P V (it ran meanwhile) is added, then block
-    // j's probabilities.  One more iteration adds the last block.
-    for (int j = 0; j <= my_blocks && my_blocks > 0; ++j) {
-      const int key0 = key_begin + j * TC_BN;
-      const bool all_visible = key0 >= lo_r && key0 + TC_BN - 1 <= pos_r;
-      float msafe = 0.f, corr = 1.f, m_new = m;
-      if (j < my_blocks) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.s_full[x]), (uint32_t)j & 1u, abort_flag) ? 1 : 0);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        uint32_t va[16], vb[16];
-        auto take = [&](const uint32_t (&v)[16], int c) {
-          if (all_visible) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int key = key0 + c * 16 + i;
-              if (key >= lo_r && key <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-            }
-          }
-        };
-        tmem_ld16(s_addr, va);
-#pragma unroll 1
-        for (int c = 0; c < TC_BN / 16; c += 2) {
-          tmem_wait_ld();
-          tmem_ld16(s_addr + (uint32_t)((c + 1) * 16), vb);
-          take(va, c);
-          tmem_wait_ld();
-          if (c + 2 < TC_BN / 16) tmem_ld16(s_addr + (uint32_t)((c + 2) * 16), va);
-          take(vb, c + 1);
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-        m_new = fmaxf(m, mx);
-        msafe = m_new == -INFINITY ? 0.f : m_new;
-        corr = ex2(m - msafe);              // m = -inf: 0
-      }
-      if (j > 0) {
-        // block j-1: once its P V is done, P's tile is free as well
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full[x]), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        add_block(corr_prev);
-      }
-      if (j == my_blocks) break;
-      float sum2[2] = {0.f, 0.f};
-      {
-        uint32_t va[32], vb[32];
-        auto take = [&](const uint32_t (&v)[32], int c) {        // keys c*32 .. c*32+31
-          uint32_t pk[16];
-          if (all_visible) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
-              const float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
-              sum2[0] += p0;
-              sum2[1] += p1;
-              pk[i >> 1] = pack_bf16(p0, p1);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const int key = key0 + c * 32 + i;
-              float p0 = ex2(__uint_as_float(v[i]) * scale_log2 - msafe);
-              float p1 = ex2(__uint_as_float(v[i + 1]) * scale_log2 - msafe);
-              if (key < lo_r || key > pos_r) p0 = 0.f;
-              if (key + 1 < lo_r || key + 1 > pos_r) p1 = 0.f;
-              sum2[0] += p0;
-              sum2[1] += p1;
-              pk[i >> 1] = pack_bf16(p0, p1);
-            }
-          }
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const int chunk = (c & 1) * 4 + h;
-            const uint32_t dst = p_row + (c >> 1) * TC_SLAB_BYTES + ((chunk ^ (rt & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[h * 4]), "r"(pk[h * 4 + 1]),
-                         "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
-          }
-        };
-        tmem_ld32(s_addr, va);
-#pragma unroll 1
-        for (int c = 0; c < TC_BN / 32; c += 2) {
-          tmem_wait_ld();
-          tmem_ld32(s_addr + (uint32_t)((c + 1) * 32), vb);
-          take(va, c);
-          tmem_wait_ld();
-          if (c + 2 < TC_BN / 32) tmem_ld32(s_addr + (uint32_t)((c + 2) * 32), va);
-          take(vb, c + 1);
-        }
-      }
-      l = l * corr + (sum2[0] + sum2[1]);
-      m = m_new;
-      corr_prev = corr;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, before the MMA reads it
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&sh.p_full[x]));
-    }
-    if (ok && valid && my_blocks > 0) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + ((size_t)(tok0 + R / G) * nq + kvh * G + R % G) * TC_HD;
-#pragma unroll
-      for (int i = 0; i < TC_HD; i += 8) {
-        uint4 w;
-        w.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
-        w.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-        w.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
-        w.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = w;
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-  }
-  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
-}
-
-// ------------------------------------------------------------------------------------------------
 // One query tile per block, O accumulated in TMEM, two softmax threads per row.
 //
 //   warp 0: TMA producer of K blocks, warp 1: of V blocks (two stages each), warp 2: MMA issuer,
@@ -516,10 +157,10 @@ attn_span_tc2_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 //   never read O until the end.  Both threads of a row take the maximum over all 128 keys (the same
 //   decision without talking to each other) and the exponentials of their own 64.
 // ------------------------------------------------------------------------------------------------
-constexpr int TC3_THREADS = 11 * 32;
-constexpr float TC3_TAU = 8.0f;
+constexpr int TCS_THREADS = 11 * 32;
+constexpr float TCS_TAU = 8.0f;
 
-struct Tc3Shared {
+struct TcsShared {
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full, p_full, p_empty, fin;
   uint32_t tmem_base;
   int abort_flag;
@@ -532,8 +173,8 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 
-__global__ void __launch_bounds__(TC3_THREADS, 1)
-attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+__global__ void __launch_bounds__(TCS_THREADS, 1)
+attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                      const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                      const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
                      const int* __restrict__ tiles, int nq, int nkv, int page_size, int num_pages,
@@ -541,7 +182,7 @@ attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(base), p_s = q_s + TC_TILE_BYTES, k_s = p_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
-  __shared__ Tc3Shared sh;
+  __shared__ TcsShared sh;
   __shared__ int s_page[TC_MAX_PAGES];
   __shared__ float s_l[2][TC_BM];
   volatile int* abort_flag = &sh.abort_flag;
@@ -560,7 +201,7 @@ attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   const int key_begin = lo_min / TC_BN * TC_BN;
   const int n_blocks = (key_end - key_begin) / TC_BN + 1;
 
-  for (int c = tid; c < TC_BM * (TC_HD / 8); c += TC3_THREADS) {
+  for (int c = tid; c < TC_BM * (TC_HD / 8); c += TCS_THREADS) {
     const int r = c / (TC_HD / 8), ch = c % (TC_HD / 8);      // 16-byte chunk ch of row r
     const int R = row0 + r;
     const bool ok = r < n_rows;
@@ -569,13 +210,13 @@ attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     cp_async16(q_s + (ch >> 3) * TC_SLAB_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), src, ok);
   }
   asm volatile("cp.async.commit_group;\n" ::);
-  for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TC3_THREADS)
+  for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TCS_THREADS)
     reinterpret_cast<uint4*>(base + 2 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
   const int pi0 = key_begin / page_size;
   const int n_pi = key_end / page_size - pi0 + 1;
   const bool pages_in_smem = n_pi <= TC_MAX_PAGES;
   if (pages_in_smem)
-    for (int i = tid; i < n_pi; i += TC3_THREADS) s_page[i] = bt[pi0 + i];
+    for (int i = tid; i < n_pi; i += TCS_THREADS) s_page[i] = bt[pi0 + i];
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&sh.k_full[s]), 1);
@@ -739,7 +380,7 @@ attn_span_tc3_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       m_true = fmaxf(m_true, mx);
       // raise the reference only when the maximum has grown a lot: O and the sum are rescaled then
-      const bool raise = m_true > m_ref + TC3_TAU;          // also true while the reference is -inf and a key is visible
+      const bool raise = m_true > m_ref + TCS_TAU;          // also true while the reference is -inf and a key is visible
       if (__any_sync(0xffffffffu, raise && j > 0)) {
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.o_full), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
         if (!ok) break;
@@ -897,12 +538,8 @@ extern "C" int qb_attn_span_tc_supported(int nq, int nkv, int hd, int page_size)
   return encode_fn() != nullptr ? 1 : 0;
 }
 
-// Query rows per tile of the tcgen05 kernels: 128 (one tile a block, O in TMEM); QUANTA_B200_SPAN_KERNEL=tc2
-// runs the two-tile kernel (256), for tests and measurements.
-extern "C" int qb_attn_span_tc_rows(void) {
-  const char* want = getenv("QUANTA_B200_SPAN_KERNEL");
-  return (want != nullptr && strcmp(want, "tc2") == 0) ? 2 * TC_BM : TC_BM;
-}
+// Query rows per tile of the tcgen05 kernel.
+extern "C" int qb_attn_span_tc_rows(void) { return TC_BM; }
 
 // Same arguments as qb_attn_span; the tile list has qb_attn_span_tc_rows() rows a tile.
 extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tok_pos,
@@ -921,21 +558,12 @@ extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v
   int rc = make_kv_map(&tm_k, k_cache, rows, box_rows);
   if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, box_rows);
   if (rc) return rc;
-  if (qb_attn_span_tc_rows() == TC_BM) {
-    const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
-    cudaError_t err = cudaFuncSetAttribute(attn_span_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    attn_span_tc3_kernel<<<dim3(n_tiles, nkv), TC3_THREADS, smem, stream>>>(
-        tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
-        page_size, num_pages, scale_log2, window, status);
-  } else {
-    const size_t smem = 7 * (size_t)TC_TILE_BYTES + 1024;
-    cudaError_t err = cudaFuncSetAttribute(attn_span_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    attn_span_tc2_kernel<<<dim3(n_tiles, nkv), TC2_THREADS, smem, stream>>>(
-        tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
-        page_size, num_pages, scale_log2, window, status);
-  }
+  const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
+  cudaError_t err = cudaFuncSetAttribute(attn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return (int)err;
+  attn_span_tc_kernel<<<dim3(n_tiles, nkv), TCS_THREADS, smem, stream>>>(
+      tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
+      page_size, num_pages, scale_log2, window, status);
   QB_LAUNCH_CHECK();
   return 0;
 }

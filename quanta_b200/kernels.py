@@ -340,26 +340,10 @@ def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile
                                      tile_expert.numel(), n_experts, top_k, K, N, _stream()), "moe_grouped_simt")
 
 
-def moe_stream_supported(x: torch.Tensor, hidden: int, inner: int) -> bool:
-    """The weight-streaming tensor-core kernel takes bfloat16 and inner dimensions that are multiples
-    of 8 (16-byte rows)."""
+def expert_gemm_tc_supported(x: torch.Tensor, hidden: int, inner: int) -> bool:
+    """The tcgen05 expert kernel takes bfloat16 and inner dimensions that are multiples of 8 (16-byte rows
+    for TMA)."""
     return x.dtype == torch.bfloat16 and hidden % 8 == 0 and inner % 8 == 0
-
-
-def moe_stream(mode: int, x, weights, out, sorted_pair, pair_w, plan, n_experts: int, top_k: int,
-               max_rows: int) -> None:
-    """Same contract as ``moe_grouped_simt`` for bfloat16: weights streamed once through mma.sync with
-    the token rows as the narrow operand.  ``max_rows``: the most rows one expert can have."""
-    K = x.shape[1]
-    N = out.shape[1]
-    want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
-    if tuple(weights.shape) != want:
-        raise ValueError(f"moe_stream: weights {tuple(weights.shape)} != {want}")
-    _want(x, torch.bfloat16, "x"); _want(weights, torch.bfloat16, "weights")
-    _want(out, torch.bfloat16 if mode == 1 else torch.float32, "out")
-    n_pairs = sorted_pair.numel()
-    _check(lib().qb_moe_stream(mode, _p(x), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan), n_experts,
-                               top_k, K, N, min(n_experts, n_pairs), int(max_rows), _stream()), "moe_stream")
 
 
 def expert_tile_rows(n_tokens: int, rows_per_expert: float = 0.0) -> int:

@@ -1,4 +1,4 @@
-"""Feed-forward parts: sigmoid-routed SwiGLU experts, and a dense SwiGLU.
+"""Feed-forward part: sigmoid-routed SwiGLU experts.
 
 Routed experts (src/quanta/minimax/moe.py:36-88): router logits in float32 from a float32 gate;
 ``sigmoid`` scores; a correction bias added for the choice only; top-k (ties to the lower expert
@@ -14,7 +14,6 @@ import os
 import torch
 
 from .. import kernels
-from ..matmul import empty_rows, linear
 from .base import FeedForward, TensorSpec, register
 
 
@@ -71,25 +70,17 @@ class SigmoidTopKExperts(FeedForward):
         if dt == torch.bfloat16 and self.H % 8 == 0 and self.gate_w.is_cuda:
             self.gate_pieces = kernels.split3_bf16(self.gate_w)
 
-    # Which kernels run the expert products: "tc" (tcgen05 + TMA), "stream" (mma.sync, weights from
-    # registers), "simt" (float32 CUDA cores).  "auto": float32 and odd sizes -> simt; bfloat16 -> stream
-    # for steps of at most ``stream_max_tokens`` tokens, tc above (measured on a B200: tc is at least as
-    # fast from one token on, so the bound is 0).  Set per part, or for the whole process with
-    # QUANTA_B200_EXPERT_KERNELS (a tuning knob, for measurements).
+    # Which kernels run the expert products: "tc" (tcgen05 + TMA) for bfloat16, "simt" (float32 CUDA
+    # cores) for float32 and for widths that are no multiple of 8.  QUANTA_B200_EXPERT_KERNELS=simt forces
+    # the latter for the whole process (a knob for measurements).
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
-    stream_max_tokens = 0
     router_mma_min_tokens = 256      # steps of fewer tokens read the float32 gate once on the CUDA cores
     fused_plan_max_tokens = 64       # steps of at most this many tokens select and plan in one launch
     gather_in_kernel_max_tokens = 64 # and their expert products fetch the token rows without a gathered copy
 
     def path_for(self, x) -> str:
-        ok16 = kernels.moe_stream_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
-        choice = self.expert_kernels
-        if not ok16 or choice == "simt":
-            return "simt"
-        if choice in ("tc", "stream"):
-            return choice
-        return "stream" if x.shape[0] <= self.stream_max_tokens else "tc"
+        ok16 = kernels.expert_gemm_tc_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
+        return "tc" if ok16 and self.expert_kernels != "simt" else "simt"
 
     def router_logits(self, x):
         """float32 ``[T, E]``, or ``[chunks, T, E]`` partial sums that the selection adds in index order."""
@@ -166,42 +157,8 @@ class SigmoidTopKExperts(FeedForward):
                                        self.E, bm, ctx.status)
             kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                    tile_expert, tile_row0, self.E, bm, ctx.status)
-        elif path == "stream":
-            # bfloat16, very few rows: expert weights streamed once through mma.sync from registers
-            kernels.moe_stream(1, x, self.w13, act, sorted_pair, w.view(-1), plan, self.E, self.k, T)
-            kernels.moe_stream(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan, self.E,
-                               self.k, T)
         else:
             kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
             kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                      tile_expert, tile_row0, self.E, self.k)
         return y
-
-
-@register("feed_forward", "swiglu_dense")
-class SwiGLUDense(FeedForward):
-    """``down(silu(gate x) * up x)`` with library products and a fused activation kernel."""
-
-    graph_safe = True
-
-    def __init__(self, hidden_size: int, inner_size: int, names: dict):
-        self.H, self.I, self.names = int(hidden_size), int(inner_size), dict(names)
-        self.w_gu = self.w_down = None
-
-    def tensor_specs(self):
-        n = self.names
-        return [TensorSpec(n["gate"], (self.I, self.H)), TensorSpec(n["up"], (self.I, self.H)),
-                TensorSpec(n["down"], (self.H, self.I))]
-
-    def load(self, fetch):
-        g = fetch(self.names["gate"])
-        self.w_gu = torch.empty((2 * self.I, self.H), dtype=g.dtype, device=g.device)
-        self.w_gu[: self.I].copy_(g)
-        self.w_gu[self.I:].copy_(fetch(self.names["up"]))
-        self.w_down = fetch(self.names["down"])
-
-    def forward(self, x, ctx):
-        gu = linear(x, self.w_gu)
-        act = empty_rows(x.shape[0], self.I, dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gu, act)
-        return linear(act, self.w_down)

@@ -9,10 +9,14 @@ inputs, and writes inputs' seeds and the outputs to ``reference_oracle.json`` be
 ``tests/test_plain.py`` recomputes the same quantities with the plain implementation and compares.
 
 What this anchors: rotate-half partial rotary, the sigmoid router (selection with bias, bias-free
-weights, renormalisation, scaling), and the attention core with per-head q/k norm (the oracle applies
-``1 + w``, so it is fed ``gain - 1``).  What rests on the formulas alone: q/k norm over the
-concatenated heads, the SiLU SwiGLU expert (the oracle has only the clamped activation), and the
-expert sum without a shared expert.
+weights, renormalisation, scaling), the attention core with per-head q/k norm (the oracle applies
+``1 + w``, so it is fed ``gain - 1``), and the routed sum of SwiGLU experts (``w1`` gate, ``w3`` up,
+``w2`` down, the weight applied after ``down``, no shared term).  The oracle's expert is
+``(up + 1) * gate * sigmoid(alpha * gate)`` with both clamped at ``limit``; with ``alpha = 1`` and
+``limit = inf`` that is ``(up + 1) * silu(gate)``, and an input feature that is constant 1 whose ``w3``
+column is -1 (and whose ``w1`` column is 0) takes the ``+ 1`` away, so ``_np_moe`` computes this
+decoder's ``silu(gate) * up``; its shared expert is given zero weights.  What rests on the formulas
+alone: q/k norm over the concatenated heads (no code of the reference computes it).
 
 Run:  python tests/golden/make_golden.py /path/to/reference
 """
@@ -26,7 +30,7 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-WANTED = ("_np_sigmoid", "_np_gemma_rms", "_np_rope", "_np_attn", "_np_route")
+WANTED = ("_np_sigmoid", "_np_gemma_rms", "_np_rope", "_np_attn", "_np_route", "_np_swigluoai", "_np_moe")
 
 
 def load_oracle(ref_root: Path) -> dict:
@@ -56,7 +60,21 @@ def cases():
     gate = rng.standard_normal((10, H))
     bias = rng.uniform(-0.05, 0.05, 10)
     rope_in = rng.standard_normal((1, 3, T, 16))
-    return cfg, dict(x=x, Wq=Wq, Wk=Wk, Wv=Wv, Wo=Wo, qn=qn, kn=kn, gate=gate, bias=bias, rope_in=rope_in)
+    # routed experts: 10 experts of width 12 over the 24 features plus one that is constant 1
+    E, I = 10, 12
+    moe_w1 = rng.standard_normal((E, I, H)) * 0.3
+    moe_w3 = rng.standard_normal((E, I, H)) * 0.3
+    moe_w2 = rng.standard_normal((E, H + 1, I)) * 0.3
+    return cfg, dict(x=x, Wq=Wq, Wk=Wk, Wv=Wv, Wo=Wo, qn=qn, kn=kn, gate=gate, bias=bias, rope_in=rope_in,
+                     moe_w1=moe_w1, moe_w3=moe_w3, moe_w2=moe_w2)
+
+
+def with_constant_feature(c, up_column: float):
+    """The routed experts' inputs with a feature that is constant 1 appended: ``(x', gate', w1', w3')``.
+    The router and ``w1`` ignore the feature (zero columns); ``w3`` weighs it by ``up_column``."""
+    x = np.concatenate([c["x"], np.ones(c["x"].shape[:-1] + (1,))], axis=-1)
+    pad = lambda w, v: np.concatenate([w, np.full(w.shape[:-1] + (1,), v)], axis=-1)      # noqa: E731
+    return x, pad(c["gate"], 0.0), pad(c["moe_w1"], 0.0), pad(c["moe_w3"], up_column)
 
 
 def main():
@@ -72,6 +90,12 @@ def main():
     order = np.argsort(idx, axis=-1)
     out["route_w"] = np.take_along_axis(w, order, axis=-1).tolist()
     out["attn"] = ns["_np_attn"](c["x"], c["Wq"], c["Wk"], c["Wv"], c["Wo"], c["qn"] - 1.0, c["kn"] - 1.0, cfg).tolist()
+    # routed sum: (up' + 1) * silu(gate) with up' = up - 1 through the constant feature; no clamp; zero shared expert
+    x1, gate1, w1, w3 = with_constant_feature(c, -1.0)
+    moe_cfg = types.SimpleNamespace(**vars(cfg), swiglu_alpha=1.0, swiglu_limit=np.inf)
+    zero = np.zeros((4, x1.shape[-1]))
+    out["moe"] = ns["_np_moe"](x1, gate1, c["bias"], w1, c["moe_w2"], w3, zero, zero, np.zeros((x1.shape[-1], 4)),
+                               moe_cfg).tolist()
     # the reference's config parser on one of the tiny configurations
     sys.path.insert(0, str(ref / "src"))
     import importlib.util

@@ -154,18 +154,17 @@ def attention_reference(q, kc, vc, table, tok_pos, tok_req, scale, window):
                                                    (48, 8, 128, 16, 0), (8, 2, 128, 16, 100), (4, 2, 48, 8, 37),
                                                    (48, 1, 64, 16, 0), (72, 1, 64, 8, 0), (32, 2, 128, 32, 50),
                                                    (4, 2, 256, 16, 0), (6, 1, 192, 8, 0), (16, 2, 128, 128, 0)])
-@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only", "tc_two_tiles"])
+@pytest.mark.parametrize("impl", ["simt", "mma", "mma_only"])
 def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
     """impl: the float32 SIMT kernel; the bfloat16 tensor-core kernels as the engine picks them (tcgen05 with
-    O in TMEM for portions where the shapes allow); the same with the mma.sync kernel for every portion;
-    and with the two-tile tcgen05 kernel."""
+    O in TMEM for portions where the shapes allow); the same with the mma.sync kernel for every portion."""
     k = K()
     if impl != "simt" and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernels are the bfloat16 path")
-    if impl in ("mma_only", "tc_two_tiles"):
+    if impl == "mma_only":
         if not k.attn_span_tc_supported(nq, nkv, hd, page):
             pytest.skip("these shapes run on the mma.sync kernels anyway")
-        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc2")
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma")
     torch.manual_seed(1)
     # (first position, tokens): prompt portions beside decode tokens; a portion that starts past a split edge
     spans = [(0, 13), (70, 1), (33, 9), (129, 1), (250, 30), (600, 1)]
@@ -234,7 +233,7 @@ def test_paged_attention(dtype, nq, nkv, hd, page, window, impl, monkeypatch):
         assert torch.allclose(out.float().cpu(), want, **tol(dtype))
 
 
-@pytest.mark.parametrize("impl", ["tc", "tc_two_tiles", "mma_only"])
+@pytest.mark.parametrize("impl", ["tc", "mma_only"])
 def test_span_attention_maximum_grows_late_in_some_rows(impl, monkeypatch):
     """A portion whose rows meet a key that dwarfs all earlier ones only in a LATER block of keys, and only
     some rows of each warp do (others never, others in two blocks): the kernel that keeps O in TMEM rescales
@@ -243,7 +242,7 @@ def test_span_attention_maximum_grows_late_in_some_rows(impl, monkeypatch):
     nq, nkv, hd, page = 4, 2, 128, 16
     assert k.attn_span_tc_supported(nq, nkv, hd, page)
     if impl != "tc":
-        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma" if impl == "mma_only" else "tc2")
+        monkeypatch.setenv("QUANTA_B200_SPAN_KERNEL", "mma")
     torch.manual_seed(7)
     first, n = 300, 100                        # 200 rows a kv head: two tiles, the second not full
     tok_pos = torch.arange(first, first + n, dtype=torch.int32)
@@ -434,7 +433,7 @@ def test_router_topk_and_plan_in_one_launch(T, E, k, P, bm):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("path", ["simt", "stream", "tc"])
+@pytest.mark.parametrize("path", ["simt", "tc"])
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2),
                                        (300, 256, 136, 7, 2), (700, 64, 40, 9, 8)])
 def test_expert_products(dtype, T, H, I, E, k, path):
@@ -481,12 +480,6 @@ def test_expert_products(dtype, T, H, I, E, k, path):
         kern.expert_gemm_tc(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, bm, st)
         torch.cuda.synchronize()
         assert st.tolist()[0] == 0, f"device status {st.tolist()}"
-    else:
-        assert kern.moe_stream_supported(x, H, I)
-        kern.moe_stream(1, x, w13, act, sorted_pair, pw.view(-1), plan, E, k, T)
-        kern.moe_stream(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, E, k, T)
-        active = plan[3 * E + 4: 3 * E + 4 + int(plan[3 * E + 2])].tolist()
-        assert active == [e for e in range(E) if int(counts[e]) > 0]
     xf = x.float()
     want = torch.empty(T, k, H, device=DEV)
     for t in range(T):
@@ -498,6 +491,62 @@ def test_expert_products(dtype, T, H, I, E, k, path):
             want[t, s] = pw[t, s] * (a @ w2[e].float().T)
     assert torch.allclose(y, want, **tol(dtype))
     assert int(st[0]) == 0
+
+
+@pytest.mark.parametrize("T,in_kernel_gather", [(1, True), (8, True), (8, False), (64, True), (300, False), (2048, False)])
+def test_expert_products_at_the_full_widths(T, in_kernel_gather):
+    """Hidden 3072, experts of width 1536, 256 experts with 8 chosen: the launch geometry of the full-size
+    model (24 and 24 blocks of 128 features a tile, token tiles of 16 to 128 rows, rings of several stages),
+    with the token rows fetched by the kernel (one TMA box a row, steps of at most 64 tokens) and from a
+    gathered copy.  Against float32 products taken expert by expert."""
+    kern = K()
+    H, I, E, k = 3072, 1536, 256, 8
+    torch.manual_seed(T)
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    w13 = torch.empty(E, 2 * I, H, device=DEV, dtype=torch.bfloat16).normal_(0, H ** -0.5)
+    w2 = torch.empty(E, H, I, device=DEV, dtype=torch.bfloat16).normal_(0, I ** -0.5)
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    if T >= 300:
+        # one expert with more rows than a token tile holds: half the tokens choose expert 77 first
+        others = torch.stack([torch.randperm(E - 1, device=DEV)[: k - 1] for _ in range(T // 2)]).int()
+        idx[: T // 2, 0] = 77
+        idx[: T // 2, 1:] = others + (others >= 77).int()
+    pw = torch.rand(T, k, device=DEV)
+    n_pairs = T * k
+    bm = kern.expert_tile_rows(T, n_pairs / E)
+    words, max_tiles = kern.moe_plan_sizes(n_pairs, E, bm)
+    plan = torch.empty(words, device=DEV, dtype=torch.int32)
+    sorted_pair = torch.empty(n_pairs, device=DEV, dtype=torch.int32)
+    te = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
+    tr = torch.empty(max_tiles, device=DEV, dtype=torch.int32)
+    st = kern.new_status(DEV)
+    kern.moe_plan(idx, E, bm, plan, sorted_pair, te, tr, st)
+    act = torch.full((n_pairs, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    y = torch.full((T, k, H), float("nan"), device=DEV)
+    if in_kernel_gather:
+        kern.expert_gemm_tc(1, x, w13, act, sorted_pair, pw.view(-1), plan, te, tr, E, bm, st, gather_top_k=k)
+    else:
+        xg = torch.empty(n_pairs, H, device=DEV, dtype=torch.bfloat16)
+        kern.gather_rows(x, xg, sorted_pair, k)
+        kern.expert_gemm_tc(1, xg, w13, act, sorted_pair, pw.view(-1), plan, te, tr, E, bm, st)
+    kern.expert_gemm_tc(2, act, w2, y.view(n_pairs, H), sorted_pair, pw.view(-1), plan, te, tr, E, bm, st)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0, f"device status {st.tolist()}"
+    torch.backends.cuda.matmul.allow_tf32 = False
+    want = torch.empty(T, k, H, device=DEV)
+    want_act = torch.empty(T, k, I, device=DEV)
+    xf = x.float()
+    for e in idx.unique().tolist():
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        g = xf[tok] @ w13[e, :I].float().T
+        u = xf[tok] @ w13[e, I:].float().T
+        a = (g * torch.sigmoid(g) * u).bfloat16().float()
+        want_act[tok, slot] = a
+        want[tok, slot] = pw[tok, slot][:, None] * (a @ w2[e].float().T)
+    got_act = torch.empty_like(want_act)
+    got_act.view(n_pairs, I)[sorted_pair.long()] = act.float()
+    assert torch.allclose(got_act, want_act, **tol(torch.bfloat16))
+    assert torch.allclose(y, want, **tol(torch.bfloat16))
 
 
 def test_sampling_matches_plain():

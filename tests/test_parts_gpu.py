@@ -97,12 +97,39 @@ def test_rotary_part_with_sections_equals_the_plain_ladder():
         PartialRotary(48, 24, 1e4, sections=[4, 4])
 
 
-def test_dense_swiglu_part():
-    from quanta_b200.parts.moe import SwiGLUDense
+def test_a_dense_feed_forward_from_the_frameworks_kernels():
+    """A dense SwiGLU is no part of this architecture; as a toy defined here it shows a feed-forward built
+    from the library product and the fused activation kernel."""
+    from quanta_b200 import kernels
+    from quanta_b200.matmul import empty_rows, linear
+    from quanta_b200.parts.base import FeedForward, TensorSpec, make, register
+
+    @register("feed_forward", "toy_dense_swiglu")
+    class DenseSwiGLU(FeedForward):
+        graph_safe = True
+
+        def __init__(self, hidden_size, inner_size, names):
+            self.H, self.I, self.names = hidden_size, inner_size, names
+
+        def tensor_specs(self):
+            n = self.names
+            return [TensorSpec(n["gate"], (self.I, self.H)), TensorSpec(n["up"], (self.I, self.H)),
+                    TensorSpec(n["down"], (self.H, self.I))]
+
+        def load(self, fetch):
+            self.w_gu = torch.cat([fetch(self.names["gate"]), fetch(self.names["up"])])
+            self.w_down = fetch(self.names["down"])
+
+        def forward(self, x, ctx):
+            gu = linear(x, self.w_gu)
+            act = empty_rows(x.shape[0], self.I, dtype=x.dtype, device=x.device)
+            kernels.silu_mul(gu, act)
+            return linear(act, self.w_down)
+
     torch.manual_seed(1)
     Hd, I, T = 72, 100, 9
     ws = {"g": 0.1 * torch.randn(I, Hd), "u": 0.1 * torch.randn(I, Hd), "d": 0.1 * torch.randn(Hd, I)}
-    part = SwiGLUDense(Hd, I, {"gate": "g", "up": "u", "down": "d"})
+    part = make("feed_forward", ("toy_dense_swiglu", dict(hidden_size=Hd, inner_size=I, names={"gate": "g", "up": "u", "down": "d"})))
     part.load(lambda n: ws[n].to(DEV))
     x = torch.randn(T, Hd)
     got = part.forward(x.to(DEV), _ctx(T))

@@ -49,6 +49,21 @@ def test_attention_against_reference_oracle():
     assert torch.allclose(out, torch.tensor(GOLDEN["attn"], dtype=torch.float64)[0], atol=1e-5)
 
 
+def test_routed_sum_against_reference_oracle():
+    """``_np_moe`` of the reference (parity/minimax_m3_layer_test.py:232-245) with its clamp switched off, its
+    shared expert zero and its ``up + 1`` undone through a constant input feature (tests/golden/make_golden.py)
+    against the plain routed sum: which matrix gates, which one goes up, the weight after ``down``, the
+    sum over the chosen experts and nothing else."""
+    from tests.golden.make_golden import with_constant_feature
+    cfg, c = cases()
+    x1, gate1, w1, w3 = with_constant_feature(c, 0.0)           # this decoder's up projection ignores the feature
+    t = lambda a: torch.tensor(a, dtype=torch.float64)          # noqa: E731
+    experts = [(t(w1[e]), t(w3[e]), t(c["moe_w2"][e])) for e in range(w1.shape[0])]
+    got = P.moe(t(x1[0]), t(gate1), t(c["bias"]), experts, cfg.num_experts_per_tok, True, 1.0, None, torch.float64)
+    want = torch.tensor(GOLDEN["moe"], dtype=torch.float64)[0]
+    assert want.abs().max() > 0.1 and torch.allclose(got, want, atol=1e-10)
+
+
 def test_config_reading_against_reference_parser():
     raw, parsed = GOLDEN["config_in"], GOLDEN["config_parsed"]
     c = P.normalise_config(raw)
