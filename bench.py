@@ -21,8 +21,12 @@ context.
   ``hbm_frac`` is its weight bytes / time / copy bandwidth.
 * ``roofline``: bytes the decode step has to read (each weight it uses once, counted from the
   experts the router really chose, plus the cache of the live requests) / time / copy bandwidth.
-* ``points``: decode at batch 1 and 64.
-Peaks are read from MEASURED_PEAKS.json when the driver wrote it, else the stated fallback.
+* ``points``: decode at batch 1 and 64 (``decode_b1``, ``decode_b64``: tokens a second over at least 32
+  timed steps), each with its time a step, the bytes the step has to read counted from the experts its
+  router chose and the requests' contexts, that over time over copy bandwidth (``_frac``) and the same
+  through the Python entry point (``_e2e``); and one step of 8 prompts of 2,048 tokens
+  (``prefill_16384``), which is bound by the tensor cores: its flops / time over the sustained tensor peak.
+Peaks are read from MEASURED_PEAKS.json beside this file when it is there, else the stated fallback.
 """
 
 from __future__ import annotations
@@ -222,30 +226,62 @@ def run_ours(args) -> dict:
                 "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(need), "peaks": pk_src}
     print(f"[bench] decode b{B}: {value:.1f} tok/s, {step_ms:.3f} ms/step, roofline {roofline}", file=sys.stderr, flush=True)
 
+    def e2e_run(batch, n_timed):
+        """Decode tokens a second through ``LLM.run``: host ids in, sampled ids out, every step."""
+        n_new = args.warmup + n_timed + 1 + 8          # the prompts enter a few at a time: later ones decode fewer pure steps
+        chunk = args.prefill_chunk or prompt_len
+        llm.sched_opts["max_step_tokens"] = min(batch, 8) * chunk     # prompts advance together, then pure decode steps
+        llm.sched_opts["prefill_chunk"] = chunk
+        reqs = [Request(rid=("e", batch, i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new))
+                for i in range(batch)]
+        llm.run(reqs)
+        dec = [s for s in llm.step_log if s["tokens"] == s["sampled"] == batch][args.warmup:]
+        val = batch * (len(dec) - 1) / (dec[-1]["t_end"] - dec[0]["t_end"]) if len(dec) >= 2 else None
+        return val, (dec[-1] if dec else None)
+
     points = {}
     if args.points:
         for b in (1, 64):
-            pms, _, _, _ = decode_run(b, 3, max(4, args.steps // 4))
-            points[f"decode_b{b}"] = round(b / statistics.fmean(pms) * 1e3, 1)
-            print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
+            n_timed = max(32, args.steps // 4)
+            pms, _, pctx, pdistinct = decode_run(b, 3, n_timed)
+            p_ms = statistics.fmean(pms)
+            p_bytes = decode_bytes(model, raw, layers, pctx, pdistinct)
+            key = f"decode_b{b}"
+            points[key] = round(b / p_ms * 1e3, 1)
+            points[key + "_ms"] = round(p_ms, 4)
+            points[key + "_steps"] = n_timed
+            points[key + "_bytes"] = int(p_bytes)
+            points[key + "_experts_read"] = int(sum(pdistinct))
+            points[key + "_frac"] = round(p_bytes / (p_ms * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
+            if args.e2e:
+                val, _ = e2e_run(b, n_timed)
+                points[key + "_e2e"] = round(val, 1) if val else None
+            print(f"[bench] decode b{b}: {points[key]} tok/s, {p_ms:.3f} ms/step, {points[key + '_frac']} of the copy "
+                  f"bandwidth, e2e {points.get(key + '_e2e')}", file=sys.stderr, flush=True)
+        # one step of 8 prompts of 2,048 tokens: 64 x 8 rows an expert on average, bound by the tensor cores
+        big, big_ms = 8, []
+        for i in range(2 + 3):
+            a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            entries = [StepEntry(("pb", i, j), toks(pf_tokens), (pf_tokens - 1,)) for j in range(big)]
+            torch.cuda.synchronize()
+            a.record()
+            eng.step(entries, end=[e.rid for e in entries])
+            bb.record()
+            torch.cuda.synchronize()
+            big_ms.append(a.elapsed_time(bb))
+        bm_ = statistics.median(big_ms[2:])
+        big_flops = big * (pf - 2 * cfg.hidden_size * cfg.vocab_size) + big * 2 * cfg.hidden_size * cfg.vocab_size
+        points["prefill_16384"] = round(big * pf_tokens / bm_ * 1e3, 1)
+        points["prefill_16384_ms"] = round(bm_, 3)
+        points["prefill_16384_frac_sustained"] = round(big_flops / (bm_ * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+        print(f"[bench] prefill of {big} x {pf_tokens} tokens in one step: {bm_:.2f} ms, "
+              f"{points['prefill_16384_frac_sustained']} of the sustained tensor peak", file=sys.stderr, flush=True)
 
     # ---- end to end through the Python entry point ----
-    n_new = args.warmup + args.steps + 1
-    chunk = args.prefill_chunk or prompt_len
-    llm.sched_opts["max_step_tokens"] = B * chunk            # all prompts advance together, then pure decode steps
-    llm.sched_opts["prefill_chunk"] = chunk
-    log = []
-    if args.e2e:
-        reqs = [Request(rid=("e", i), prompt=toks(prompt_len), params=SamplingParams(max_new_tokens=n_new)) for i in range(B)]
-        llm.run(reqs)
-        log = llm.step_log
-    dec = [s for s in log if s["tokens"] == s["sampled"] == B][args.warmup:]
-    e2e_val = None
-    if len(dec) >= 2:
-        e2e_val = B * (len(dec) - 1) / (dec[-1]["t_end"] - dec[0]["t_end"])
+    e2e_val, last = e2e_run(B, args.steps) if args.e2e else (None, None)
     e2e = {"value": round(e2e_val, 1) if e2e_val else None, "unit": "tokens/s",
-           "h2d_bytes_per_step": dec[-1]["h2d_bytes"] if dec else None,
-           "d2h_bytes_per_step": dec[-1]["d2h_bytes"] if dec else None}
+           "h2d_bytes_per_step": last["h2d_bytes"] if last else None,
+           "d2h_bytes_per_step": last["d2h_bytes"] if last else None}
 
     config = {"model": "MiniMax-M3 (M2-family sizes), random weights", "weights_gb": weights_gb, "layers": layers, "layers_full": FULL_LAYERS,
               "hidden": 3072, "q_heads": 48, "kv_heads": 8, "head_dim": 128, "rotary_dim": 64, "experts": 256,

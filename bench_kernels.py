@@ -102,15 +102,14 @@ def attn_span(tokens: int, start: int, nq: int, nkv: int, hd: int, page: int) ->
 
 
 def router(tokens: int, hidden: int, experts: int, top_k: int) -> dict:
-    """Router logits (tensor cores, float32 gate in three bfloat16 pieces) and the selection of ``tokens``
-    tokens, each timed as twenty launches in a CUDA graph."""
+    """The router of a step of ``tokens`` tokens, timed as twenty launches in a CUDA graph: below 256 tokens
+    one kernel (float32 logits on the CUDA cores, selection, expert plan); from 256 on the logits on the tensor
+    cores (float32 gate in three bfloat16 pieces) and the selection."""
     x = torch.randn(tokens, hidden, device=DEV).bfloat16()
     gate = torch.randn(experts, hidden, device=DEV) / hidden ** 0.5
-    if tokens <= 64 and k.router_topk_plan_supported(tokens, experts, top_k):
-        # what a small step runs: float32 logits on the CUDA cores in fixed chunks of the inner dimension,
-        # then selection and the expert plan in one launch
-        chunk = 128
-        logits = torch.empty(-(-hidden // chunk), tokens, experts, device=DEV)
+    if tokens < 256 and k.router_small_selects(tokens, experts, top_k):
+        # what a small step runs: float32 logits on the CUDA cores, selection and the expert plan, one launch
+        logits = torch.empty(tokens, experts, device=DEV)
         bias = torch.zeros(experts, device=DEV)
         idx = torch.empty(tokens, top_k, dtype=torch.int32, device=DEV)
         w = torch.empty(tokens, top_k, device=DEV)
@@ -119,11 +118,12 @@ def router(tokens: int, hidden: int, experts: int, top_k: int) -> dict:
         plan = torch.empty(words, dtype=torch.int32, device=DEV)
         sp = torch.empty(tokens * top_k, dtype=torch.int32, device=DEV)
         te, tr = (torch.empty(max_tiles, dtype=torch.int32, device=DEV) for _ in range(2))
-        counter, st = torch.zeros(1, dtype=torch.int32, device=DEV), k.new_status(DEV)
-        t_gemm = timed_graph(lambda: k.gemm_nt_simt(x, gate, logits, k_chunk=chunk))
-        t_sel = timed_graph(lambda: k.router_topk_plan(logits, bias, idx, w, True, 1.0, counter, bm, plan, sp, te, tr, st))
-        return {"kernel": "gemm_nt_simt + router_topk_plan", "tokens": tokens, "hidden": hidden, "experts": experts,
-                "top_k": top_k, "gemm_us": round(t_gemm * 1e3, 1), "topk_plan_us": round(t_sel * 1e3, 1)}
+        counters, st = torch.zeros(1 + -(-tokens // 8), dtype=torch.int32, device=DEV), k.new_status(DEV)
+        t_logits = timed_graph(lambda: k.router_small(x, gate, bias, logits))
+        t_all = timed_graph(lambda: k.router_small(x, gate, bias, logits, idx, w, True, 1.0, counters=counters, bm=bm,
+                                                   plan=plan, sorted_pair=sp, tile_expert=te, tile_row0=tr, status=st))
+        return {"kernel": "router_small", "tokens": tokens, "hidden": hidden, "experts": experts, "top_k": top_k,
+                "logits_only_us": round(t_logits * 1e3, 1), "logits_selection_plan_us": round(t_all * 1e3, 1)}
     pieces = k.split3_bf16(gate)
     logits = torch.empty(k.router_gemm_mma_parts(hidden), tokens, experts, device=DEV)
     bias = torch.zeros(experts, device=DEV)

@@ -15,10 +15,22 @@
 // One warp selects for one token: the k largest of sigmoid(logit) (+ bias), the lower expert index first
 // among equals; the weights are the bias-free scores, renormalised and scaled.  Lane l holds experts
 // l, l + 32, ...; s_score: k floats of shared memory that belong to this warp.
+// bias: the lane's own values, bias[i] for expert lane + 32 i (zeros when the router has none).
 template <int NPL>
-__device__ __forceinline__ void select_topk(const float (&logit)[NPL], const float* __restrict__ bias,
+__device__ __forceinline__ void lane_bias(const float* __restrict__ bias, int E, float (&out)[NPL]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int e = lane + 32 * i;
+    out[i] = (bias != nullptr && e < E) ? bias[e] : 0.f;
+  }
+}
+
+// s_idx: if not null, the chosen experts are left there too (shared memory).
+template <int NPL>
+__device__ __forceinline__ void select_topk(const float (&logit)[NPL], const float (&bias)[NPL],
                                             int* __restrict__ idx_row, float* __restrict__ w_row, float* s_score,
-                                            int E, int k, int renorm, float scale) {
+                                            int E, int k, int renorm, float scale, int* s_idx = nullptr) {
   const int lane = threadIdx.x & 31;
   float choice[NPL], score[NPL];
   unsigned taken = 0u;
@@ -30,7 +42,7 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
       const float x = logit[i];
       const float s = 1.f / (1.f + expf(-x));
       score[i] = s;
-      choice[i] = bias ? s + bias[e] : s;
+      choice[i] = s + bias[i];
     } else {
       choice[i] = -INFINITY;
       taken |= 1u << i;
@@ -67,6 +79,7 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
     if (lane == 0) {
       idx_row[r] = bi;
       s_score[r] = sc;
+      if (s_idx != nullptr) s_idx[r] = bi;
     }
   }
   __syncwarp();
@@ -109,13 +122,14 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
   }
   __syncthreads();
   if (threadIdx.x >= 32) return;      // of this function: the caller's other warps go on
-  float logit[NPL];
+  float logit[NPL], b[NPL];
+  lane_bias<NPL>(bias, E, b);
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
     logit[i] = e < E ? s_logit[e] : 0.f;
   }
-  select_topk<NPL>(logit, bias, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_part, E, k, renorm, scale);
+  select_topk<NPL>(logit, b, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_part, E, k, renorm, scale);
 }
 
 template <int NPL>
@@ -143,7 +157,8 @@ router_topk_warp_kernel(const float* __restrict__ logits, int n_partials, const 
   if (t >= T) return;
   const float* lg = logits + (size_t)t * E;
   const size_t pstride = (size_t)T * E;
-  float logit[NPL];
+  float logit[NPL], b[NPL];
+  lane_bias<NPL>(bias, E, b);
 #pragma unroll
   for (int i = 0; i < NPL; ++i) {
     const int e = lane + 32 * i;
@@ -152,7 +167,7 @@ router_topk_warp_kernel(const float* __restrict__ logits, int n_partials, const 
       for (int p = 0; p < n_partials; ++p) x += lg[p * pstride + e];
     logit[i] = x;
   }
-  select_topk<NPL>(logit, bias, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_scores + (size_t)warp * k, E, k,
+  select_topk<NPL>(logit, b, idx_out + (size_t)t * k, w_out + (size_t)t * k, s_scores + (size_t)warp * k, E, k,
                    renorm, scale);
 }
 
@@ -260,8 +275,8 @@ struct PlanShared {
 // The plan of up to 4096 pairs by the first NTH threads of a block (NTH >= E, a multiple of 32), thread e
 // for expert e; `sync` is a barrier of exactly these threads.  Counts by shared-memory atomics, the three
 // prefix sums (rows, tiles, active experts) by warp shuffles and one pass over the warps' totals.  idx is
-// read past L1 (another block of the same launch may have written it).
-template <int NTH, typename Sync>
+// read past L1 (another block of the same launch may have written it), or from shared memory (IDX_SHARED).
+template <int NTH, bool IDX_SHARED = false, typename Sync>
 __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int E, int BM, int* __restrict__ plan,
                                                 int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
                                                 int* __restrict__ tile_row0, int max_tiles, int* status,
@@ -271,7 +286,7 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
   s_cur[e] = 0;
   sync();
   for (int i = e; i < n_pairs; i += NTH) {
-    const int x = __ldcg(idx + i);
+    const int x = IDX_SHARED ? idx[i] : __ldcg(idx + i);
     if (x < 0 || x >= E) { qb_set_status(status, QB_STATUS_BAD_EXPERT, x, 4); continue; }
     atomicAdd(&s_cur[x], 1);
   }
@@ -305,7 +320,7 @@ __device__ __forceinline__ void plan_small_body(const int* idx, int n_pairs, int
   s_cur[e] = off;                     // running write position of each expert
   sync();
   for (int i = e; i < n_pairs; i += NTH) {
-    const int x = __ldcg(idx + i);
+    const int x = IDX_SHARED ? idx[i] : __ldcg(idx + i);
     if (x < 0 || x >= E) continue;
     sorted_pair[atomicAdd(&s_cur[x], 1)] = i;
   }
@@ -320,51 +335,260 @@ moe_plan_small_kernel(const int* __restrict__ idx, int n_pairs, int E, int BM, i
                         [] { __syncthreads(); });
 }
 
-// Routing and the plan of a step of few tokens in one launch: one block a token selects; the block that
-// finishes last (a counter in global memory, left at zero again) lays the plan down for all of them.
-// Every block ends by itself: nothing waits.
-template <int NPL>
-__global__ void __launch_bounds__(1024)
-router_topk_plan_kernel(const float* __restrict__ logits, int n_partials, const float* __restrict__ bias,
-                        int* idx_out, float* __restrict__ w_out, int T, int E, int k, int renorm, float scale,
-                        int* counter, int BM, int* __restrict__ plan, int* __restrict__ sorted_pair,
-                        int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles, int* status) {
-  __shared__ float s_logit[1024];
-  __shared__ float s_part[1056];
-  __shared__ PlanShared sh;
-  __shared__ int s_last;
-  if ((int)blockIdx.x >= T) return;
-  route_token<NPL>(logits, n_partials, bias, idx_out, w_out, T, E, k, renorm, scale, s_logit, s_part);
-  __syncthreads();
-  if (threadIdx.x == 0) {             // the thread that wrote this token's experts
-    __threadfence();
-    const int before = atomicAdd(counter, 1);
-    s_last = before == T - 1;
-    if (s_last) *counter = 0;         // every other block has counted already
-  }
-  __syncthreads();
-  // the plan needs a thread an expert (at most 256 here): the block's other warps are done
-  if (!s_last || threadIdx.x >= 256) return;
-  __threadfence();
-  plan_small_body<256>(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
-                       [] { asm volatile("bar.sync 1, 256;" ::: "memory"); });
+// ---------------------------------------------------------------------------------------------
+// The router of steps of few tokens, whole, in one launch: float32 logits, selection, plan.
+//
+//   logits[t][e] = sum_k float(x[t][k]) * gate[e][k]        (src/quanta/minimax/moe.py:44)
+//
+// A block takes RS_TT tokens and RS_EPB experts; RS_KW warps share an expert, each a contiguous quarter of
+// the inner dimension.  The tokens' rows are staged in shared memory once; a warp's lanes walk their part of
+// the gate row in groups of 4 elements (lane l takes groups l, l + 32, ...), each lane adds its products in
+// that order, the lanes' sums are added by a butterfly and the quarters' sums in index order.  The order of
+// a logit's additions depends on the inner dimension alone: a token's logits are bit-identical whatever
+// else the step holds and however it is cut.  Few experts a block put the gate's rows on many SMs, and every
+// lane has all its loads of the row in flight at once.
+// With `select`: the block that finishes a token tile last (a counter in global memory) selects for the
+// tile's tokens, a warp a token; the block that finishes the last tile lays the expert plan down for the
+// whole step.  Every block ends by itself, nothing waits; the counters are zero again afterwards.
+// ---------------------------------------------------------------------------------------------
+constexpr int RS_TT = 8, RS_WARPS = 8, RS_QUARTERS = 4, RS_BATCH = 8;
+
+__device__ __forceinline__ float4 rs_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 rs_load4(const __nv_bfloat16* p) {      // a bfloat16 is the upper half of a float32
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                     __uint_as_float(raw.y & 0xffff0000u));
 }
 
-// counter: one int32 that is zero before the call and zero after it
-extern "C" int qb_router_topk_plan(const float* logits, int n_partials, const float* bias, int* idx_out,
-                                   float* w_out, int T, int E, int k, int renorm, float scale, int* counter, int BM,
-                                   int* plan, int* sorted_pair, int* tile_expert, int* tile_row0, int max_tiles,
-                                   int* status, cudaStream_t stream) {
+// KW: warps that share an expert (4: a quarter each, two experts a block, for steps of few tokens, whose
+// gate rows then come from many SMs at once; 1: a warp takes the four quarters in turn, eight experts a
+// block, so that a step of many tokens stages its rows in fewer blocks).  The sums are the same in both.
+template <typename TX, int NPL, bool VEC, int KW>
+__global__ void __launch_bounds__(RS_WARPS * 32)
+router_small_kernel(const TX* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ bias,
+                    float* logits, int* idx_out, float* __restrict__ w_out, int T, int E, int K, int k, int renorm,
+                    float scale, int select, int* counters, int BM, int* __restrict__ plan,
+                    int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                    int max_tiles, int* status) {
+  constexpr int EPB = RS_WARPS / KW;                            // experts a block
+  extern __shared__ __align__(16) unsigned char rs_smem[];      // [RS_TT][K] of TX: the tile's token rows
+  __shared__ PlanShared sh;
+  __shared__ float s_score[RS_WARPS][256];
+  __shared__ float s_quarter[RS_WARPS * RS_QUARTERS / KW][RS_TT];     // [expert of the block][quarter][token]
+  __shared__ int s_chosen[RS_TT * 32];                                // a single tile's choices, for its plan (k <= 32)
+  __shared__ int s_last;
+  TX* xs = reinterpret_cast<TX*>(rs_smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.y * RS_TT, nt = min(RS_TT, T - t0);
+  const int le = warp / KW, e = blockIdx.x * EPB + le;
+
+  const int units = VEC ? K / 4 : K;                       // groups of 4 elements (16 bytes), or single elements
+  const int per = (units + RS_QUARTERS - 1) / RS_QUARTERS;
+  const float* grow = gate + (size_t)(e < E ? e : 0) * K;
+  // The warp's work is a list of batches: RS_BATCH groups a lane (f, f + 32, ...) of one quarter; a warp
+  // reads 512 contiguous bytes of the gate row and of each token row at a time.  The gate values of the
+  // batch after the current one are in flight while the current one is multiplied.
+  const int q_first = warp % KW;
+  const int batches_per_q = (per + 32 * RS_BATCH - 1) / (32 * RS_BATCH);
+  const int n_batches = VEC ? ((RS_QUARTERS - q_first + KW - 1) / KW) * batches_per_q : 0;
+  auto fetch = [&](int b, float4 (&g)[RS_BATCH]) {
+    const int q = q_first + (b / batches_per_q) * KW;
+    const int u0 = q * per, u1 = min(units, u0 + per);
+    const int f0 = u0 + (b % batches_per_q) * 32 * RS_BATCH + lane;
+#pragma unroll
+    for (int u = 0; u < RS_BATCH; ++u) {
+      const int f = f0 + 32 * u;
+      if (f < u1) g[u] = *reinterpret_cast<const float4*>(grow + (size_t)f * 4);
+    }
+  };
+  float4 g0[RS_BATCH], g1[RS_BATCH], g2[RS_BATCH];
+  if (n_batches > 0) fetch(0, g0);                         // into flight before anything else
+  if (n_batches > 1) fetch(1, g1);
+
+  if (VEC) {
+    // asynchronous copies, all in flight at once (rows of K elements, K a multiple of 4: whole 8-byte words)
+    const int n8 = nt * K * (int)sizeof(TX) / 8;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(x + (size_t)t0 * K);
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs);
+    for (int i = tid; i < n8; i += RS_WARPS * 32)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 8u * (uint32_t)i), "l"(src + 8 * (size_t)i) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else {
+    for (int i = tid; i < nt * K; i += RS_WARPS * 32) xs[i] = x[(size_t)t0 * K + i];
+  }
+  __syncthreads();
+  float acc[RS_TT];
+#pragma unroll
+  for (int t = 0; t < RS_TT; ++t) acc[t] = 0.f;
+  auto multiply = [&](int b, const float4 (&g)[RS_BATCH]) {
+    const int q = q_first + (b / batches_per_q) * KW;
+    const int u0 = q * per, u1 = min(units, u0 + per);
+    const int f0 = u0 + (b % batches_per_q) * 32 * RS_BATCH + lane;
+#pragma unroll
+    for (int u = 0; u < RS_BATCH; ++u) {
+      const int f = f0 + 32 * u;
+      if (f < u1) {
+#pragma unroll
+        for (int t = 0; t < RS_TT; ++t) {
+          if (t < nt) {
+            const float4 xv = rs_load4(xs + (size_t)t * K + (size_t)f * 4);
+            acc[t] = fmaf(xv.x, g[u].x, acc[t]);
+            acc[t] = fmaf(xv.y, g[u].y, acc[t]);
+            acc[t] = fmaf(xv.z, g[u].z, acc[t]);
+            acc[t] = fmaf(xv.w, g[u].w, acc[t]);
+          }
+        }
+      }
+    }
+    if ((b + 1) % batches_per_q == 0) {                    // the quarter is done: its sums go to shared memory
+#pragma unroll
+      for (int t = 0; t < RS_TT; ++t) {
+        const float v = qb_warp_sum(acc[t]);
+        if (lane == 0) s_quarter[le * RS_QUARTERS + q][t] = v;
+        acc[t] = 0.f;
+      }
+    }
+  };
+  if (VEC) {
+    // three buffers in turn: the gate values of the next two batches are in flight while one is multiplied
+    for (int b = 0; b < n_batches; b += 3) {
+      if (b + 2 < n_batches) fetch(b + 2, g2);
+      multiply(b, g0);
+      if (b + 1 < n_batches) {
+        if (b + 3 < n_batches) fetch(b + 3, g0);
+        multiply(b + 1, g1);
+      }
+      if (b + 2 < n_batches) {
+        if (b + 4 < n_batches) fetch(b + 4, g1);
+        multiply(b + 2, g2);
+      }
+    }
+  } else {
+    for (int q = q_first; q < RS_QUARTERS; q += KW) {
+      const int u0 = q * per, u1 = min(units, u0 + per);
+      for (int kk = u0 + lane; kk < u1; kk += 32) {
+        const float gv = grow[kk];
+#pragma unroll
+        for (int t = 0; t < RS_TT; ++t)
+          if (t < nt) acc[t] = fmaf(qb_to_float<TX>(xs[(size_t)t * K + kk]), gv, acc[t]);
+      }
+#pragma unroll
+      for (int t = 0; t < RS_TT; ++t) {
+        const float v = qb_warp_sum(acc[t]);
+        if (lane == 0) s_quarter[le * RS_QUARTERS + q][t] = v;
+        acc[t] = 0.f;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < EPB * RS_TT) {
+    const int l2 = tid / RS_TT, t = tid % RS_TT, ee = blockIdx.x * EPB + l2;
+    if (ee < E && t < nt) {
+      float v = s_quarter[l2 * RS_QUARTERS][t];
+#pragma unroll
+      for (int q = 1; q < RS_QUARTERS; ++q) v += s_quarter[l2 * RS_QUARTERS + q][t];
+      __stcg(logits + (size_t)(t0 + t) * E + ee, v);
+    }
+  }
+  if (!select) return;
+  // the selecting warps will want the bias: fetched now, under the hand-over below
+  float my_bias[NPL];
+  lane_bias<NPL>(bias, E, my_bias);
+  // ---- the last block of this token tile selects ----
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const int before = atomicAdd(&counters[1 + blockIdx.y], 1);
+    s_last = before == (int)gridDim.x - 1;
+    if (s_last) counters[1 + blockIdx.y] = 0;      // every other block of the tile has counted already
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int t = warp; t < nt; t += RS_WARPS) {
+    float logit[NPL];
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int ee = lane + 32 * i;
+      logit[i] = ee < E ? __ldcg(logits + (size_t)(t0 + t) * E + ee) : 0.f;
+    }
+    select_topk<NPL>(logit, my_bias, idx_out + (size_t)(t0 + t) * k, w_out + (size_t)(t0 + t) * k, s_score[warp], E, k,
+                     renorm, scale, (gridDim.y == 1 && k <= 32) ? s_chosen + t * k : nullptr);
+  }
+  // ---- the block that finishes the last tile lays the plan down ----
+  __syncthreads();
+  if (gridDim.y > 1) {
+    if (tid == 0) {
+      __threadfence();
+      const int before = atomicAdd(&counters[0], 1);
+      s_last = before == (int)gridDim.y - 1;
+      if (s_last) counters[0] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+  }
+  if (gridDim.y == 1 && k <= 32)       // the step is this one tile: its choices are still in shared memory
+    plan_small_body<RS_WARPS * 32, true>(s_chosen, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles,
+                                         status, sh, [] { __syncthreads(); });
+  else
+    plan_small_body<RS_WARPS * 32>(idx_out, T * k, E, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status, sh,
+                                   [] { __syncthreads(); });
+}
+
+// Token rows of at most this many bytes fit the shared-memory tile.
+constexpr size_t RS_MAX_TILE_BYTES = 200 * 1024;
+
+// 1 if qb_router_small can also select and plan (select = 1) for these sizes.
+extern "C" int qb_router_small_selects(int T, int E, int k) {
+  return (E <= RS_WARPS * 32 && k <= 256 && (long long)T * k <= 4096) ? 1 : 0;
+}
+
+// x [T, K] float32 or bfloat16, gate [E, K] float32, logits [T, E] float32 (always written).  select = 1 (see
+// qb_router_small_selects): idx_out / w_out [T, k] and the expert plan as qb_moe_plan lays it down;
+// counters: 1 + ceil(T / 8) int32 that are zero before the call and zero after it.
+extern "C" int qb_router_small(const void* x, int x_dtype, const float* gate, const float* bias, float* logits,
+                               int* idx_out, float* w_out, int T, int E, int K, int k, int renorm, float scale,
+                               int select, int* counters, int BM, int* plan, int* sorted_pair, int* tile_expert,
+                               int* tile_row0, int max_tiles, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (k <= 0 || k > E || n_partials <= 0 || counter == nullptr) return QB_ERR_BAD_ARG;
-  if (E > 256 || (long long)T * k > 4096) return QB_ERR_UNSUPPORTED;
-#define QB_ROUTE(N) router_topk_plan_kernel<N><<<T, 1024, 0, stream>>>(logits, n_partials, bias, idx_out, w_out, T, E, \
-    k, renorm, scale, counter, BM, plan, sorted_pair, tile_expert, tile_row0, max_tiles, status)
-  if (E <= 32) QB_ROUTE(1);
-  else if (E <= 64) QB_ROUTE(2);
-  else if (E <= 128) QB_ROUTE(4);
-  else QB_ROUTE(8);
-#undef QB_ROUTE
+  if (E <= 0 || K <= 0) return QB_ERR_BAD_ARG;
+  if (select && (!qb_router_small_selects(T, E, k) || counters == nullptr || k <= 0 || k > E)) return QB_ERR_BAD_ARG;
+  const size_t smem = (size_t)RS_TT * K * (x_dtype == QB_F32 ? 4 : 2);
+  if (smem > RS_MAX_TILE_BYTES) return QB_ERR_UNSUPPORTED;
+  const bool vec = K % 4 == 0 && (((uintptr_t)x | (uintptr_t)gate) & 15) == 0;      // rows start on 8 (x) and 16 (gate) bytes
+  // few tokens: two experts a block (more SMs pull the gate at once); many: eight (fewer blocks stage the rows)
+  const int kw = T <= 16 ? 4 : 1;
+  const int epb = RS_WARPS / kw;
+  const dim3 grid((E + epb - 1) / epb, (T + RS_TT - 1) / RS_TT);
+  if (grid.y > 65535) return QB_ERR_UNSUPPORTED;
+  cudaError_t err = cudaSuccess;
+#define QB_RS(TX, N, V, KW_)                                                                                       \
+  do {                                                                                                             \
+    err = cudaFuncSetAttribute(router_small_kernel<TX, N, V, KW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (err != cudaSuccess) return (int)err;                                                                       \
+    router_small_kernel<TX, N, V, KW_><<<grid, RS_WARPS * 32, smem, stream>>>(                                     \
+        (const TX*)x, gate, bias, logits, idx_out, w_out, T, E, K, k, renorm, scale, select, counters, BM, plan,  \
+        sorted_pair, tile_expert, tile_row0, max_tiles, status);                                                   \
+  } while (0)
+#define QB_RS_K(TX, N, V)                                \
+  do {                                                   \
+    if (kw == 4) QB_RS(TX, N, V, 4); else QB_RS(TX, N, V, 1); \
+  } while (0)
+#define QB_RS_E(TX, V)                                   \
+  do {                                                   \
+    if (!select || E <= 32) QB_RS_K(TX, 1, V);           \
+    else if (E <= 64) QB_RS_K(TX, 2, V);                 \
+    else if (E <= 128) QB_RS_K(TX, 4, V);                \
+    else QB_RS_K(TX, 8, V);                              \
+  } while (0)
+  if (x_dtype == QB_F32) { if (vec) QB_RS_E(float, true); else QB_RS_E(float, false); }
+  else if (x_dtype == QB_BF16) { if (vec) QB_RS_E(__nv_bfloat16, true); else QB_RS_E(__nv_bfloat16, false); }
+  else return QB_ERR_BAD_ARG;
+#undef QB_RS_E
+#undef QB_RS_K
+#undef QB_RS
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -236,19 +236,6 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, dec_tok, n_dec: int, 
                                 _p(status), _stream()), "attn_decode", 2)
 
 
-def gemm_nt_simt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, k_chunk: int = 0) -> None:
-    """``out[M,N] = a[M,K] @ b[N,K].T`` in float32 on the CUDA cores, fixed summation order.  With
-    ``k_chunk`` (a multiple of 16) ``out`` is ``[ceil(K/k_chunk), M, N]``: partial products of the
-    chunks of the inner dimension, to be added in index order by the consumer."""
-    M, K = a.shape
-    N = b.shape[0]
-    want = (M, N) if not k_chunk else (-(-K // k_chunk), M, N)
-    if b.shape[1] != K or tuple(out.shape) != want:
-        raise ValueError("gemm_nt_simt: shape mismatch")
-    _check(lib().qb_gemm_nt_simt(_p(a), _code(a), _p(b), _code(b), _p(out), _code(out), M, N, K, K, K, N,
-                                 int(k_chunk), _stream()), "gemm_nt_simt")
-
-
 def split3_bf16(w: torch.Tensor) -> torch.Tensor:
     """A float32 tensor as three bfloat16 tensors ``[3, *w.shape]`` whose sum is ``w`` to float32 accuracy
     (each is the bfloat16 rounding of what the ones before leave over)."""
@@ -290,25 +277,43 @@ def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> Non
                                 ctypes.c_float(scale), _stream()), "router_topk")
 
 
-def router_topk_plan_supported(n_tokens: int, n_experts: int, top_k: int) -> bool:
-    return n_experts <= 256 and n_tokens * top_k <= 4096
+ROUTER_SMALL_MAX_TILE_BYTES = 200 * 1024          # eight token rows must fit the router's shared-memory tile
 
 
-def router_topk_plan(logits, bias, idx_out, w_out, renorm: bool, scale: float, counter, bm: int, plan, sorted_pair,
-                     tile_expert, tile_row0, status) -> None:
-    """``router_topk`` and ``moe_plan`` of a step of few tokens as one launch.  ``counter``: one int32 that
-    is zero before the call; the kernel leaves it zero."""
-    _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
-    _want(counter, torch.int32, "counter")
-    n_partials = 1 if logits.dim() == 2 else logits.shape[0]
-    T, E = logits.shape[-2:]
-    k = idx_out.shape[1]
+def router_small_selects(n_tokens: int, n_experts: int, top_k: int) -> bool:
+    """Whether ``router_small`` can select and lay the expert plan down in the same launch."""
+    return bool(lib().qb_router_small_selects(int(n_tokens), int(n_experts), int(top_k)))
+
+
+def router_small(x, gate, bias, logits, idx_out=None, w_out=None, renorm: bool = True, scale: float = 1.0, *,
+                 counters=None, bm: int = 0, plan=None, sorted_pair=None, tile_expert=None, tile_row0=None,
+                 status=None) -> None:
+    """Float32 router logits ``logits[T, E] = x[T, K] @ gate[E, K].T`` on the CUDA cores, every logit one sum in
+    an order that depends on K alone.  With ``idx_out`` / ``w_out`` / the plan tensors (and
+    ``router_small_selects``): the selection (``router_topk``) and the expert plan (``moe_plan``) in the same
+    launch; ``counters``: ``1 + ceil(T / 8)`` int32 that are zero before the call and are left zero."""
+    _want(gate, torch.float32, "gate"); _want(logits, torch.float32, "logits")
+    T, K = x.shape
+    E = gate.shape[0]
+    if gate.shape[1] != K or tuple(logits.shape) != (T, E):
+        raise ValueError("router_small: shape mismatch")
+    if 8 * K * x.element_size() > ROUTER_SMALL_MAX_TILE_BYTES:
+        raise ValueError(f"router_small: rows of {K} elements do not fit the kernel's shared-memory tile "
+                         f"(at most {ROUTER_SMALL_MAX_TILE_BYTES // (8 * x.element_size())})")
     if bias is not None:
         _want(bias, torch.float32, "bias")
-    _check(lib().qb_router_topk_plan(_p(logits), n_partials, _p(bias), _p(idx_out), _p(w_out), T, E, k, int(renorm),
-                                     ctypes.c_float(scale), _p(counter), bm, _p(plan), _p(sorted_pair),
-                                     _p(tile_expert), _p(tile_row0), tile_expert.numel(), _p(status), _stream()),
-           "router_topk_plan")
+    select = idx_out is not None
+    k = 0
+    if select:
+        _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out"); _want(counters, torch.int32, "counters")
+        k = idx_out.shape[1]
+        if not router_small_selects(T, E, k) or counters.numel() < 1 + -(-T // 8):
+            raise ValueError("router_small: sizes outside what the selecting form takes, or too few counters")
+    _check(lib().qb_router_small(_p(x), _code(x), _p(gate), _p(bias), _p(logits), _p(idx_out), _p(w_out), T, E, K, k,
+                                 int(renorm), ctypes.c_float(scale), int(select), _p(counters), int(bm), _p(plan),
+                                 _p(sorted_pair), _p(tile_expert), _p(tile_row0),
+                                 tile_expert.numel() if tile_expert is not None else 0, _p(status), _stream()),
+           "router_small")
 
 
 MOE_SIMT_BM = 32

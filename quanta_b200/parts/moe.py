@@ -38,7 +38,7 @@ class SigmoidTopKExperts(FeedForward):
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
         self.gate_w = self.bias = self.w13 = self.w2 = self.gate_pieces = None
         self.last_counts = None      # rows per expert in the last step (device tensor; for measurements)
-        self._plan_counter = None    # the fused routing-and-plan kernel's counter of finished blocks (zero at rest)
+        self._plan_counter = None    # the router kernel's counters of finished blocks (zero at rest)
         self.trace = None
 
     def tensor_specs(self):
@@ -74,28 +74,28 @@ class SigmoidTopKExperts(FeedForward):
     # cores) for float32 and for widths that are no multiple of 8.  QUANTA_B200_EXPERT_KERNELS=simt forces
     # the latter for the whole process (a knob for measurements).
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
-    router_mma_min_tokens = 256      # steps of fewer tokens read the float32 gate once on the CUDA cores
-    fused_plan_max_tokens = 64       # steps of at most this many tokens select and plan in one launch
-    gather_in_kernel_max_tokens = 64 # and their expert products fetch the token rows without a gathered copy
+    router_mma_min_tokens = 256      # steps of fewer tokens take their logits on the CUDA cores (and the float32 path always)
+    gather_in_kernel_max_tokens = 64 # steps of at most this many tokens fetch the token rows without a gathered copy
 
     def path_for(self, x) -> str:
         ok16 = kernels.expert_gemm_tc_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
         return "tc" if ok16 and self.expert_kernels != "simt" else "simt"
 
+    def _on_tensor_cores(self, x) -> bool:
+        return self.gate_pieces is not None and x.dtype == torch.bfloat16 and x.shape[0] >= self.router_mma_min_tokens
+
     def router_logits(self, x):
         """float32 ``[T, E]``, or ``[chunks, T, E]`` partial sums that the selection adds in index order."""
         T = x.shape[0]
-        if self.gate_pieces is not None and x.dtype == torch.bfloat16 and T >= self.router_mma_min_tokens:
+        if self._on_tensor_cores(x):
             # many tokens: float32-accurate logits on the tensor cores (fixed chunks of the inner dimension)
             logits = torch.empty((kernels.router_gemm_mma_parts(self.H), T, self.E), dtype=torch.float32,
                                  device=x.device)
             kernels.router_gemm_mma(x, self.gate_pieces, logits)
         else:
-            # the inner dimension is cut at fixed multiples of 128, whatever T: few rows still fill the GPU,
-            # and a token's logits do not depend on how the step is cut
-            chunk = 128
-            logits = torch.empty((-(-self.H // chunk), T, self.E), dtype=torch.float32, device=x.device)
-            kernels.gemm_nt_simt(x, self.gate_w, logits, k_chunk=chunk)
+            # a warp a (token, expert) pair: the order of a logit's additions depends on the width alone
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=x.device)
+            kernels.router_small(x, self.gate_w, self.bias, logits)
         return logits
 
     def route(self, x):
@@ -109,9 +109,8 @@ class SigmoidTopKExperts(FeedForward):
 
     def forward(self, x, ctx):
         T = x.shape[0]
-        if (x.is_cuda and T <= self.fused_plan_max_tokens
-                and kernels.router_topk_plan_supported(T, self.E, self.k)):
-            # few tokens: the block that selects last lays the plan down too
+        if x.is_cuda and not self._on_tensor_cores(x) and kernels.router_small_selects(T, self.E, self.k):
+            # logits, selection and the expert plan in one launch
             return self.experts(x, None, None, ctx)
         idx, w = self.route(x)
         return self.experts(x, idx, w, ctx)
@@ -130,13 +129,14 @@ class SigmoidTopKExperts(FeedForward):
         tile_expert = ints[plan_words + n_pairs: plan_words + n_pairs + max_tiles]
         tile_row0 = ints[plan_words + n_pairs + max_tiles:]
         if idx is None:
-            logits = self.router_logits(x)
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=dev)
             idx = torch.empty((T, self.k), dtype=torch.int32, device=dev)
             w = torch.empty((T, self.k), dtype=torch.float32, device=dev)
-            if self._plan_counter is None:
-                self._plan_counter = torch.zeros(1, dtype=torch.int32, device=dev)
-            kernels.router_topk_plan(logits, self.bias, idx, w, self.renorm, self.scaling, self._plan_counter, bm,
-                                     plan, sorted_pair, tile_expert, tile_row0, ctx.status)
+            if self._plan_counter is None or self._plan_counter.numel() < 1 + -(-T // 8):
+                self._plan_counter = torch.zeros(max(64, 1 + -(-T // 8)), dtype=torch.int32, device=dev)
+            kernels.router_small(x, self.gate_w, self.bias, logits, idx, w, self.renorm, self.scaling,
+                                 counters=self._plan_counter, bm=bm, plan=plan, sorted_pair=sorted_pair,
+                                 tile_expert=tile_expert, tile_row0=tile_row0, status=ctx.status)
         else:
             kernels.moe_plan(idx, self.E, bm, plan, sorted_pair, tile_expert, tile_row0, ctx.status)
         self.last_counts = plan[: self.E]

@@ -331,19 +331,23 @@ def test_router_gemm_mma(T, E, Kd):
     assert torch.equal(alone[:, 0], logits[:, T // 2])
 
 
-@pytest.mark.parametrize("a_dtype,b_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32)])
-def test_gemm_nt_simt(a_dtype, b_dtype):
-    M, N, K_ = 45, 257, 1003
-    a = torch.randn(M, K_, device=DEV).to(a_dtype)
-    b = torch.randn(N, K_, device=DEV).to(b_dtype)
-    out = torch.empty(M, N, device=DEV)
-    K().gemm_nt_simt(a, b, out)
-    want = a.double() @ b.double().T
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,Kd", [(45, 257, 1000), (1, 256, 3072), (9, 12, 72), (300, 33, 1003), (64, 256, 3072)])
+def test_router_small_logits(x_dtype, T, E, Kd):
+    """Float32 logits of the CUDA-core router kernel: widths that are no multiple of 8 (the scalar form),
+    more experts and tokens than one block takes; a token's logits alone are bit-identical."""
+    x = torch.randn(T, Kd, device=DEV).to(x_dtype)
+    gate = torch.randn(E, Kd, device=DEV)
+    out = torch.full((T, E), float("nan"), device=DEV)
+    K().router_small(x, gate, None, out)
+    want = x.double() @ gate.double().T
     assert torch.allclose(out.double(), want, atol=1e-3, rtol=1e-5)
-    # a row's result does not depend on the rest of the batch: bit-identical alone
-    out1 = torch.empty(1, N, device=DEV)
-    K().gemm_nt_simt(a[17:18].contiguous(), b, out1)
-    assert torch.equal(out1[0], out[17])
+    t = T // 2
+    alone = torch.empty(1, E, device=DEV)
+    K().router_small(x[t: t + 1].contiguous(), gate, None, alone)
+    assert torch.equal(alone[0], out[t])
+    with pytest.raises(ValueError, match="shared-memory tile"):
+        K().router_small(torch.zeros(2, 30000, device=DEV), torch.zeros(4, 30000, device=DEV), None, torch.empty(2, 4, device=DEV))
 
 
 @pytest.mark.parametrize("E,k,bias,renorm,scale", [(8, 2, True, True, 1.0), (100, 7, False, True, 2.5),
@@ -390,22 +394,25 @@ def _router_topk_check(parts, logits, T, E, k, bias, renorm, scale):
     assert torch.allclose(w, want_w, atol=1e-6, rtol=1e-5)
 
 
-@pytest.mark.parametrize("T,E,k,P,bm", [(1, 256, 8, 24, 16), (8, 256, 8, 24, 16), (3, 12, 3, 1, 32), (64, 200, 6, 5, 128),
-                                        (37, 16, 4, 2, 32)])
-def test_router_topk_and_plan_in_one_launch(T, E, k, P, bm):
-    """The fused kernel of small steps against the two kernels it stands for, several times over (the
-    counter of finished blocks must be back at zero after every launch)."""
+@pytest.mark.parametrize("T,E,k,Kd,bm", [(1, 256, 8, 3072, 16), (8, 256, 8, 3072, 16), (3, 12, 3, 72, 32), (64, 200, 6, 328, 128),
+                                         (37, 16, 4, 100, 32), (300, 256, 8, 256, 128)])
+def test_router_logits_selection_and_plan_in_one_launch(T, E, k, Kd, bm):
+    """The router kernel of small steps (logits, selection, expert plan in one launch) against the three
+    kernels it stands for, several times over (the counters of finished blocks must be back at zero after
+    every launch).  300 tokens: 38 token tiles, each selected by the block that finished it last."""
     kern = K()
-    assert kern.router_topk_plan_supported(T, E, k)
+    assert kern.router_small_selects(T, E, k)
     torch.manual_seed(T * 7 + E)
     bias = 0.05 * torch.randn(E, device=DEV)
-    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    gate = torch.randn(E, Kd, device=DEV) / Kd ** 0.5
+    counters = torch.zeros(1 + -(-T // 8), dtype=torch.int32, device=DEV)
     st = kern.new_status(DEV)
     plan_words, max_tiles = kern.moe_plan_sizes(T * k, E, bm)
     for rep in range(3):
-        logits = torch.randn(P, T, E, device=DEV)
-        if P == 1:
-            logits = logits[0].contiguous()
+        x = torch.randn(T, Kd, device=DEV).bfloat16()
+        logits = torch.empty(T, E, device=DEV)
+        kern.router_small(x, gate, bias, logits)
+        assert torch.allclose(logits.double(), x.double() @ gate.double().T, atol=1e-4)
         idx_a = torch.empty(T, k, device=DEV, dtype=torch.int32)
         w_a = torch.empty(T, k, device=DEV)
         kern.router_topk(logits, bias, idx_a, w_a, True, 1.5)
@@ -413,9 +420,12 @@ def test_router_topk_and_plan_in_one_launch(T, E, k, P, bm):
         kern.moe_plan(idx_a, E, bm, *a, st)
         idx_b = torch.empty_like(idx_a)
         w_b = torch.empty_like(w_a)
+        logits_b = torch.empty_like(logits)
         b = [torch.zeros(n, dtype=torch.int32, device=DEV) for n in (plan_words, T * k, max_tiles, max_tiles)]
-        kern.router_topk_plan(logits, bias, idx_b, w_b, True, 1.5, counter, bm, *b, st)
-        assert int(counter) == 0
+        kern.router_small(x, gate, bias, logits_b, idx_b, w_b, True, 1.5, counters=counters, bm=bm, plan=b[0],
+                          sorted_pair=b[1], tile_expert=b[2], tile_row0=b[3], status=st)
+        assert int(counters.abs().sum()) == 0
+        assert torch.equal(logits, logits_b)
         assert torch.equal(idx_a, idx_b) and torch.equal(w_a, w_b)
         counts, offsets = a[0][:E], a[0][2 * E: 3 * E + 1]
         assert torch.equal(counts, b[0][:E]) and torch.equal(offsets, b[0][2 * E: 3 * E + 1])
