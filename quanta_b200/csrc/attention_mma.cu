@@ -250,8 +250,11 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 // The work is the list of all 64-key tiles of all (token, kv head) pairs, token-major.  Persistent
 // blocks (one per SM) cut that list into equal contiguous ranges (a block's range may begin and end
 // inside a pair), so every SM reads the same number of bytes whatever the mix of context lengths.
-// A block is one PRODUCER warp and four CONSUMER warps around a ring of tiles in shared memory.  A tile
-// is 64 keys of one pair: its K rows, V rows and the group's Q rows.  The producer resolves 32 tiles at
+// A block is two PRODUCER warps and four CONSUMER warps around a ring of tiles in shared memory.  A tile
+// is 64 keys of one pair: its K rows, V rows and the group's Q rows.  Starting a tensor load holds the
+// issuing warp for a time that grows with the bytes, and one warp that issues all of a tile's boxes is slower
+// than the consumers and than memory; so one producer issues the Q rows and the K boxes and the other the V
+// boxes, each counting its own bytes on the tile's barrier.  Each producer resolves 32 tiles at
 // a time (pair by binary search in a prefix sum of the tokens' tile counts held in shared memory, then
 // the page ids, all lanes in parallel) and issues TMA tensor loads (one box per page) or, where the
 // shapes do not allow them, one bulk copy per row; completion is counted on the tile's mbarrier.
@@ -269,7 +272,8 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* qs, const __nv
 // (0: the output is already final).
 // ------------------------------------------------------------------------------------------------
 constexpr int AD_CONSUMERS = 4;
-constexpr int AD_THREADS = (AD_CONSUMERS + 1) * 32;
+constexpr int AD_PRODUCERS = 2;      // one issues the Q rows and the K boxes of a tile, the other its V boxes
+constexpr int AD_THREADS = (AD_CONSUMERS + AD_PRODUCERS) * 32;
 constexpr int AD_MAX_STAGES = 8;
 constexpr uint32_t AD_SPIN_LIMIT = 4u * 1000u * 1000u;
 constexpr uint64_t AD_WAIT_NS = 200ull * 1000ull * 1000ull;
@@ -395,9 +399,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   int* s_req = s_pos + AD_MAX_DEC;                                           // its block-table row
   int* s_tok = s_req + AD_MAX_DEC;                                           // its row among the step's tokens
   int* s_cum = s_tok + AD_MAX_DEC;                                           // [AD_MAX_DEC + 1] tiles of the tokens before z
-  int* s_pages = s_cum + AD_MAX_DEC + 1;                                     // [32][pages_ld] page ids of a batch
+  int* s_pages_all = s_cum + AD_MAX_DEC + 1;                                 // [producers][32][pages_ld] page ids of a batch
   __shared__ uint64_t full[AD_MAX_STAGES], empty[AD_MAX_STAGES], cbar;
-  __shared__ AdDesc s_desc[2][32];            // the tiles of a batch of 32, double-buffered
+  __shared__ AdDesc s_desc[2][32];            // the tiles of a batch of 32, double-buffered (the first producer's)
+  __shared__ AdDesc s_desc_v[2][32];          // the second producer's own copy
   __shared__ float s_ml[AD_CONSUMERS][16][2];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
@@ -417,7 +422,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&full[s]), AD_PRODUCERS);
       mbar_init(smem_u32(&empty[s]), AD_CONSUMERS);
     }
     mbar_init(smem_u32(&cbar), AD_CONSUMERS);
@@ -453,8 +458,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const int n_tiles = (int)(end - start);
 
   const uint32_t row_bytes = (uint32_t)hd * 2u;
-  if (warp == AD_CONSUMERS) {
-    // ---------------- producer ----------------
+  if (warp >= AD_CONSUMERS) {
+    // ---------------- producers: both resolve the same tiles; `which` 0 issues Q and K, 1 issues V ----------------
+    const int which = warp - AD_CONSUMERS;
+    int* s_pages = s_pages_all + which * 32 * pages_ld;
+    AdDesc (*my_desc)[32] = which == 0 ? s_desc : s_desc_v;
     bool ok = true;
     int slot = 0, q_count = 0;
     uint32_t phase = 0;
@@ -528,13 +536,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const uint32_t firsts = __ballot_sync(0xffffffffu, nd.valid && (nd.flags & AD_FIRST));
       nd.qslot = (q_count + __popc(firsts & (0xffffffffu >> (31 - lane))) + q_slots - 1) % q_slots;
       q_count = (q_count + __popc(firsts)) % q_slots;
-      s_desc[buf][lane] = nd;
+      my_desc[buf][lane] = nd;
       __syncwarp();
       const int in_batch = min(32, n_tiles - first_tile);
       if (first_tile + 32 < n_tiles) resolve(first_tile + 32);     // its loads are in flight while this batch is issued
       // ---- issue the batch ----
       for (int src = 0; src < in_batch && ok; ++src) {
-        const AdDesc d = s_desc[buf][src];
+        const AdDesc d = my_desc[buf][src];
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty[slot]), phase ^ 1u, abort_flag) ? 1 : 0);   // one answer per warp
         if (!ok) break;
         const uint32_t bar = smem_u32(&full[slot]);
@@ -549,11 +557,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           // keys before the window are not fetched (their rows keep older, finite values and are masked)
           const int key_skip = d.lo > d.key0 ? d.lo - d.key0 : 0;
           const int box_first = TMA ? key_skip >> box_shift : 0;
-          const bool new_q = (d.flags & AD_FIRST) != 0;
+          const bool new_q = which == 0 && (d.flags & AD_FIRST) != 0;
           if (lane == 0) {
-            const uint32_t kv_bytes = TMA ? (uint32_t)(2 * (n_boxes - box_first) * box_rows) * row_bytes
-                                    : (uint32_t)(2 * (n_keys - key_skip)) * row_bytes;
-            mbar_expect_tx(bar, (new_q ? (uint32_t)G * row_bytes : 0u) + kv_bytes);
+            const uint32_t my_bytes = TMA ? (uint32_t)((n_boxes - box_first) * box_rows) * row_bytes
+                                    : (uint32_t)(n_keys - key_skip) * row_bytes;
+            mbar_expect_tx(bar, (new_q ? (uint32_t)G * row_bytes : 0u) + my_bytes);
           }
           __syncwarp();
           if (new_q) {
@@ -562,8 +570,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
               bulk_copy_row(qs + (size_t)r * LD, q + ((size_t)d.tok * nq + d.kvh * G + r) * hd, row_bytes, bar);
           }
           if (TMA) {
-            for (int i = lane; i < 2 * (n_boxes - box_first); i += 32) {
-              const int which = i & 1, box = box_first + (i >> 1);
+            for (int i = lane; i < n_boxes - box_first; i += 32) {
+              const int box = box_first + i;
               const int key = d.key0 + (box << box_shift);
               const int pg = s_pages[src * pages_ld + (key >> page_shift) - d.pi0];
               const int row = ((pg * nkv + d.kvh) << page_shift) + (key & (page_size - 1));   // row of the cache [rows][hd]
@@ -575,8 +583,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
               const int key = d.key0 + r;
               const int pg = s_pages[src * pages_ld + key / page_size - d.pi0];
               const size_t off = (((size_t)pg * nkv + d.kvh) * page_size + key % page_size) * hd;
-              bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
-              bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
+              if (which == 0) bulk_copy_row(ks + (size_t)r * LD, k_cache + off, row_bytes, bar);
+              else bulk_copy_row(vs + (size_t)r * LD, v_cache + off, row_bytes, bar);
             }
           }
         }
@@ -955,9 +963,12 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 // The pairs that the blocks' ranges cut: out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over
 // the pair's segments, in index order.  The last entry of a row of part_ml holds the number of segments
 // (0: the decode kernel wrote the final output itself).
+// When the status words hold a refusal (a page id outside the pool: that tile was passed over, and if it ended
+// its pair the pair's segment count was never written) nothing is merged: the host raises at its next read.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, const int* __restrict__ dec_tok, int nq, int hd,
-                                  int n_parts) {
+                                  int n_parts, const int* __restrict__ status) {
+  if (status != nullptr && status[0] != 0) return;
   const int z = blockIdx.y, head = blockIdx.x;
   const size_t base = ((size_t)z * nq + head) * n_parts;
   int n = __float_as_int(part_ml[(base + n_parts - 1) * 2]);
@@ -1210,7 +1221,7 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
     const size_t q_bytes = (size_t)q_rows * (HDP + AT_PAD) * 2;  /* one more Q slot than tiles, 8 zero rows */ \
     const size_t stage_bytes = 2 * ad_tile_elems(HDP, TMA_) * 2 + q_bytes;                                 \
     const size_t fixed = 1024 + q_bytes + 8 * (HDP + AT_PAD) * 2 +                                         \
-                         (size_t)(4 * AD_MAX_DEC + 1 + 32 * pages_ld) * sizeof(int);                       \
+                         (size_t)(4 * AD_MAX_DEC + 1 + AD_PRODUCERS * 32 * pages_ld) * sizeof(int);        \
     const long room = (long)smem_optin - (long)fa.sharedSizeBytes - (long)fixed;                           \
     int stages = room > 0 ? (int)((size_t)room / stage_bytes) : 0;                                         \
     if (stages > AD_MAX_STAGES) stages = AD_MAX_STAGES;                                                    \
@@ -1237,7 +1248,7 @@ extern "C" int qb_attn_decode(const void* q, const void* k_cache, const void* v_
     else QB_DEC(256, false);
   }
 #undef QB_DEC
-  attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, nq, hd, n_parts);
+  attn_merge_kernel<<<dim3(nq, n_dec), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, dec_tok, nq, hd, n_parts, status);
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -24,9 +24,11 @@
  *    device current) and remembers it per device; make that first call before any stream capture
  *    begins on the device.
  *  - All calls share the one array, and it keeps the last call's contents.  Nothing in it has to
- *    start at zero: every element the merge step reads was written by the same call.  Two calls that
- *    overlap on the GPU (different streams, or the same stream from racing host threads) race on it;
- *    run them one after the other.
+ *    start at zero: every element the merge step reads was written by the same call.  The one
+ *    exception is a call that the kernel refuses in part (a page id outside the pool, recorded in the
+ *    status words): then nothing is merged at all, `out` is not valid, and the status words say so.
+ *    Two calls that overlap on the GPU (different streams, or the same stream from racing host
+ *    threads) race on the array; run them one after the other.
  */
 #pragma once
 #include <cuda_runtime.h>
