@@ -128,14 +128,18 @@ struct EgShared {
   int abort_flag;
 };
 
-template <int MODE>
+// NM: weight tiles of 128 features a block (accumulators side by side in TMEM).  MODE 1 has two by its nature
+// (gate and up rows of the same features).  MODE 2 takes two neighbouring blocks of 128 features when the
+// token tile is 256 rows (steps bound by the tensor cores): the token tile, half of what a stage holds then,
+// is fetched from L2 once for 256 features instead of once for 128.
+template <int MODE, int NM>
 __global__ void __launch_bounds__(EG_THREADS, 2)
 expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                       void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
                       const int* __restrict__ plan, const int* __restrict__ tile_expert,
                       const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
                       int tmem_cols, int gather_k, int* status) {
-  constexpr int NM = MODE == 1 ? 2 : 1;
+  constexpr int FEATS = MODE == 1 ? EG_M : NM * EG_M;      // output features a block
   extern __shared__ unsigned char smem_dyn[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -148,7 +152,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (tile >= num_tiles) return;
   const int e = tile_expert[tile], row0 = tile_row0[tile];
   const int rows = min(NT, plan[2 * E + e + 1] - row0);          // valid token rows of this tile
-  const int j0 = blockIdx.x * EG_M;
+  const int j0 = blockIdx.x * FEATS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t a_bytes = EG_M * EG_BK * 2, b_bytes = (uint32_t)NT * EG_BK * 2;
   const uint32_t stage_bytes = NM * a_bytes + b_bytes;
@@ -194,7 +198,9 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const bool by_row = MODE == 1 && gather_k > 0;
         mbar_expect_tx(full, by_row ? NM * a_bytes + (uint32_t)rows * EG_BK * 2 : stage_bytes);
         tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full, pol_w);
-        if (MODE == 1) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + N_out, full, pol_w);
+        // the second weight tile: the up rows of the same features, or the next 128 features (rows past the
+        // expert's last are another expert's and give columns that the epilogue drops)
+        if (NM == 2) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), full, pol_w);
         if (by_row) {
           // boxes of one row: the swizzle follows the shared-memory address, so row i lands where a box of
           // NT rows would have put it; the rows past the expert's last keep what the stage held before, and
@@ -220,7 +226,9 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(EG_M, NT);
+      // the MMA's N is what this tile holds, in steps of 16: an expert's last tile of a few rows costs the
+      // tensor cores a few columns, not a whole tile (the box that TMA fetches stays NT rows)
+      const uint32_t idesc = umma_idesc(EG_M, min(NT, (rows + 15) & ~15));
       bool ok = true;
       for (int kb = 0; kb < k_blocks && ok; ++kb) {
         const int s = kb % stages;
@@ -268,20 +276,27 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (c0 >= rows) break;
         uint32_t v0[16], v1[16];
         tmem_ld16(lane_addr + (uint32_t)c0, v0);
-        if (MODE == 1) tmem_ld16(lane_addr + (uint32_t)(NT + c0), v1);
+        if (NM == 2) tmem_ld16(lane_addr + (uint32_t)(NT + c0), v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (feat < N_out) {
+        if (MODE == 1) {
+          if (feat < N_out) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = c0 + i;
+              if (col >= rows) break;
+              const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
+              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(row0 + col) * N_out + feat] =
+                  __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+            }
+          }
+        } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int col = c0 + i;
             if (col >= rows) break;
-            if (MODE == 1) {
-              const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
-              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(row0 + col) * N_out + feat] =
-                  __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-            } else {
-              reinterpret_cast<float*>(out)[(size_t)s_pair[col] * N_out + feat] = s_w[col] * __uint_as_float(v0[i]);
-            }
+            float* dst = reinterpret_cast<float*>(out) + (size_t)s_pair[col] * N_out;
+            if (feat < N_out) dst[feat] = s_w[col] * __uint_as_float(v0[i]);
+            if (NM == 2 && feat + EG_M < N_out) dst[feat + EG_M] = s_w[col] * __uint_as_float(v1[i]);
           }
         }
       }
@@ -360,10 +375,13 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   if (max_tiles <= 0 || n_pairs <= 0) return 0;
   if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
   if (mode != 1 && mode != 2) return QB_ERR_BAD_ARG;
-  const int nm = mode == 1 ? 2 : 1;
+  // weight tiles a block: gate and up (mode 1); two blocks of 128 features for the down product of 256-row
+  // token tiles (see the kernel)
+  const int nm = (mode == 1 || NT >= 128) ? 2 : 1;
+  const int feats = mode == 1 ? EG_M : nm * EG_M;
   if (((uintptr_t)x_rows | (uintptr_t)weights) & 15) return QB_ERR_BAD_ARG;
   CUtensorMap tm_w, tm_x;
-  int rc = make_map(&tm_w, weights, (uint64_t)E * nm * N_out, (uint64_t)K, EG_M);
+  int rc = make_map(&tm_w, weights, (uint64_t)E * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
   if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0))) return QB_ERR_BAD_ARG;
   rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)
@@ -380,7 +398,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       sms = 1;
   }
-  const size_t blocks = (size_t)((N_out + EG_M - 1) / EG_M) * (size_t)max_tiles;
+  const size_t blocks = (size_t)((N_out + feats - 1) / feats) * (size_t)max_tiles;
   const bool alone = NT > 128 || blocks <= (size_t)sms;
   // Token tiles of at most 32 rows (decode steps of a few tokens: short blocks, one expert's 128 features
   // each): three blocks an SM with rings of about 70 KB hide a block's prologue and epilogue better than
@@ -397,19 +415,20 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   const size_t smem = stage_bytes * stages + 1024;
   int tmem_cols = 32;
   while (tmem_cols < nm * NT) tmem_cols *= 2;
-  dim3 grid((N_out + EG_M - 1) / EG_M, max_tiles);
+  dim3 grid((N_out + feats - 1) / feats, max_tiles);
   cudaError_t err;
-  if (mode == 1) {
-    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    expert_gemm_tc_kernel<1><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
-                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, gather_k, status);
-  } else {
-    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-    expert_gemm_tc_kernel<2><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert,
-                                                                tile_row0, E, K, N_out, NT, stages, tmem_cols, 0, status);
-  }
+#define QB_EG(MODE_, NM_, GK)                                                                                        \
+  do {                                                                                                             \
+    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<MODE_, NM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (err != cudaSuccess) return (int)err;                                                                       \
+    expert_gemm_tc_kernel<MODE_, NM_><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, \
+                                                                         tile_expert, tile_row0, E, K, N_out, NT,  \
+                                                                         stages, tmem_cols, GK, status);            \
+  } while (0)
+  if (mode == 1) QB_EG(1, 2, gather_k);
+  else if (nm == 2) QB_EG(2, 2, 0);
+  else QB_EG(2, 1, 0);
+#undef QB_EG
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -452,7 +452,7 @@ def test_expert_products(dtype, T, H, I, E, k, path):
         pytest.skip("the tensor-core kernels are the bfloat16 path")
     # the last case has some hundred rows an expert: the tile of 256 rows that compute-bound steps use
     bm = kern.expert_tile_rows(T, T * k / E) if path == "tc" else kern.MOE_SIMT_BM
-    assert path != "tc" or bm == (256 if T >= 700 else min(128, max(16, 1 << (T - 1).bit_length())))
+    assert path != "tc" or bm == (256 if T * k / E >= 96 else min(128, max(16, 1 << (T - 1).bit_length())))
     torch.manual_seed(3)
     x = torch.randn(T, H, device=DEV).to(dtype)
     # scaled so that outputs stay of order one at every size (the tolerance is absolute)
