@@ -62,13 +62,17 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const D* __restrict__ 
   float* hrow = h + (size_t)tok * H;
   const D* drow = delta ? delta + (size_t)tok * S * H : nullptr;
   float ss = 0.f;
+  // the gains of this thread's first chunk are asked for now: they come from memory that the layer's weights
+  // have pushed out of L2, and would else be waited for after the row's sum
+  float w_first[8];
+  if (H % 8 == 0 && out != nullptr && (int)threadIdx.x * 8 < H) QbVec8<float>::load(w + threadIdx.x * 8, w_first);
   if (H % 8 == 0) {
     // 8 elements a thread and step, vector loads; the slots of the delta are still added in index order
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float x[8];
       QbVec8<float>::load(hrow + i, x);
       if (drow) {
-#pragma unroll 4
+#pragma unroll 8
         for (int s = 0; s < S; ++s) {
           float dv[8];
           QbVec8<D>::load(drow + (size_t)s * H + i, dv);
@@ -100,7 +104,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const D* __restrict__ 
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float x[8], wv[8];
       QbVec8<float>::load(row_buf + i, x);
-      QbVec8<float>::load(w + i, wv);
+      if (i == (int)threadIdx.x * 8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) wv[e] = w_first[e];
+      } else {
+        QbVec8<float>::load(w + i, wv);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[e] = wv[e] * (x[e] * r_inv);
       QbVec8<O>::store(orow + i, x);

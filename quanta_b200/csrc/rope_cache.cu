@@ -31,9 +31,22 @@ __global__ void qknorm_rope_write_kernel(
   float* head_r = scratch + 32;
   const A* row = qkv + (size_t)t * (qn + 2 * kn);
   const int half = rd / 2;
+  // Where this token's K and V go is a chain of three dependent loads (position, request, page id), and the
+  // norm gains come from memory that the layer's expert weights have pushed out of L2: both are asked for
+  // now, so that their latency passes under the phases below instead of after them.
+  int pos = 0, page = -1;
+  if (k_cache != nullptr) {
+    pos = tok_pos[t];
+    page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+  }
+  const int n_chunks = (qn + kn) / 8;
+  float w_first[8];                  // the gains of this thread's first chunk (NORM_PER_LAYER)
+  if (norm_kind == NORM_PER_LAYER && (int)threadIdx.x < n_chunks) {
+    const int i = threadIdx.x * 8;
+    QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w_first);
+  }
 
   // 16-byte loads, all of a thread's loads issued before their first use
-  const int n_chunks = (qn + kn) / 8;
 #pragma unroll 4
   for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
     float v[8];
@@ -68,7 +81,12 @@ __global__ void qknorm_rope_write_kernel(
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
       const int i = c * 8;
       float w[8], v[8];
-      QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w);
+      if (c == (int)threadIdx.x) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = w_first[e];
+      } else {
+        QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w);
+      }
       QbVec8<float>::load(buf + i, v);
       const float r = i < qn ? rq : rk;
 #pragma unroll
@@ -111,8 +129,6 @@ __global__ void qknorm_rope_write_kernel(
   }
 
   if (k_cache == nullptr) return;
-  const int pos = tok_pos[t];
-  const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
   if (page < 0 || page >= num_pages) {
     if (threadIdx.x == 0) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 2);
     return;
