@@ -576,13 +576,8 @@ extern "C" int qb_router_small(const void* x, int x_dtype, const float* gate, co
   do {                                                   \
     if (kw == 4) QB_RS(TX, N, V, 4); else QB_RS(TX, N, V, 1); \
   } while (0)
-#define QB_RS_E(TX, V)                                   \
-  do {                                                   \
-    if (!select || E <= 32) QB_RS_K(TX, 1, V);           \
-    else if (E <= 64) QB_RS_K(TX, 2, V);                 \
-    else if (E <= 128) QB_RS_K(TX, 4, V);                \
-    else QB_RS_K(TX, 8, V);                              \
-  } while (0)
+  // the selecting warp holds eight experts a lane whatever E (at most 256 here): fewer instances to compile
+#define QB_RS_E(TX, V) QB_RS_K(TX, 8, V)
   if (x_dtype == QB_F32) { if (vec) QB_RS_E(float, true); else QB_RS_E(float, false); }
   else if (x_dtype == QB_BF16) { if (vec) QB_RS_E(__nv_bfloat16, true); else QB_RS_E(__nv_bfloat16, false); }
   else return QB_ERR_BAD_ARG;

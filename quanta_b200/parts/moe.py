@@ -33,6 +33,9 @@ class SigmoidTopKExperts(FeedForward):
             raise ValueError(f"top_k {top_k} > {n_experts} experts")
         if n_experts > 1024:
             raise ValueError(f"{n_experts} experts: the routing kernels take at most 1024")
+        if 8 * 4 * hidden_size > kernels.ROUTER_SMALL_MAX_TILE_BYTES:
+            raise ValueError(f"hidden size {hidden_size}: the router kernel stages eight float32 token rows in shared "
+                             f"memory and takes at most {kernels.ROUTER_SMALL_MAX_TILE_BYTES // 32} features")
         self.H, self.I, self.E, self.k = int(hidden_size), int(expert_size), int(n_experts), int(top_k)
         self.use_bias, self.renorm, self.scaling = bool(use_bias), bool(renormalize), float(scaling)
         self.names = dict(names)   # gate, bias, and templates w1/w2/w3 with "{e}"
@@ -74,7 +77,9 @@ class SigmoidTopKExperts(FeedForward):
     # cores) for float32 and for widths that are no multiple of 8.  QUANTA_B200_EXPERT_KERNELS=simt forces
     # the latter for the whole process (a knob for measurements).
     expert_kernels = os.environ.get("QUANTA_B200_EXPERT_KERNELS", "auto")
-    router_mma_min_tokens = 256      # steps of fewer tokens take their logits on the CUDA cores (and the float32 path always)
+    # steps of fewer tokens take their logits on the CUDA cores, in one launch with selection and plan (and the
+    # float32 path always); measured on a B200 the two ways cost the same at about a hundred tokens
+    router_mma_min_tokens = 96
     gather_in_kernel_max_tokens = 64 # steps of at most this many tokens fetch the token rows without a gathered copy
 
     def path_for(self, x) -> str:
