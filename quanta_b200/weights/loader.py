@@ -69,8 +69,11 @@ def _seed_for(seed: int, name: str) -> int:
 
 
 class RandomSource:
-    """Seeded random tensors for a list of specs; a tensor depends on (seed, its name) only, so the
-    order of generation does not matter.  ``normal``: N(0, 0.02); ``gain``: 1 + U(-0.1, 0.1); ``bias``:
+    """Seeded random tensors for a list of specs; a tensor depends on (seed, its name) and on the kind of
+    device it is drawn on (the CPU's and the GPU's generators differ, and large matrices are drawn in
+    bfloat16 directly on the GPU), so the order of generation does not matter, and the same seed on the same
+    kind of device gives the same model; a folder written by the random-weights mode (drawn on the CPU) and a
+    model drawn on the GPU from the same seed are two different models.  ``normal``: N(0, 0.02); ``gain``: 1 + U(-0.1, 0.1); ``bias``:
     U(-0.05, 0.05).  Matrices are drawn in float32 and rounded to ``matrix_dtype``."""
 
     def __init__(self, specs: Iterable[TensorSpec], seed: int, matrix_dtype=torch.bfloat16):

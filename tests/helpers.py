@@ -122,11 +122,12 @@ def replay(engine, steps: list[dict]) -> dict:
     return got
 
 
-def plain_logits(plain_model, reqs: dict, act=None, schedule=None, windows=None) -> dict:
+def plain_logits(plain_model, reqs: dict, act=None, schedule=None, windows=None, reads_cache_of=None) -> dict:
     weights, cfg = plain_model
     out = {}
     for rid, toks in reqs.items():
-        lg = P.forward_logits(weights, cfg, toks, act=act, compute=torch.float32, schedule=schedule, windows=windows)
+        lg = P.forward_logits(weights, cfg, toks, act=act, compute=torch.float32, schedule=schedule, windows=windows,
+                              reads_cache_of=reads_cache_of)
         for i in range(len(toks)):
             out[(rid, i)] = lg[i]
     return out

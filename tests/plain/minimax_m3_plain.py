@@ -201,10 +201,13 @@ def _w(weights, name: str) -> torch.Tensor:
 
 
 def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | None = None, window=None,
-          probe: dict | None = None, given=None):
+          probe: dict | None = None, given=None, kv_of: dict | None = None):
     """``h + attn(norm(h))`` then ``h + moe(norm(h))`` (src/quanta/minimax/model.py:70-73).
-    ``probe``: a dictionary that receives this layer's ``router_margin`` of every token and the experts
-    chosen (``margin``, ``idx``).  ``given``: the experts to take instead of the router's own choice."""
+    ``probe``: a dictionary that receives this layer's ``router_margin`` of every token, the experts
+    chosen and the keys and values it cached (``margin``, ``idx``, ``k``, ``v``).  ``given``: the experts to
+    take instead of the router's own choice.  ``kv_of``: another run of a block (its ``probe``): this one
+    attends over THAT run's cached keys and values with its own queries and caches none (not in the
+    reference, whose layers each keep their own; used by the tests of the run order)."""
     c = cfg
     wl = layer if weight_layer is None else weight_layer
     p = f"model.layers.{wl}."
@@ -219,6 +222,10 @@ def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | No
         k = qk_norm(k, W("self_attn.k_norm.weight"), c["nkv"], c["hd"], c["qk_norm_type"], c["eps"])
     q = _round(partial_rope(q, pos, c["rd"], c["theta"]), act, compute)
     k = _round(partial_rope(k, pos, c["rd"], c["theta"]), act, compute)
+    if kv_of is not None:
+        k, v = kv_of["k"], kv_of["v"]
+    if probe is not None:
+        probe["k"], probe["v"] = k, v
     a = causal_attention(q, k, v, act, compute, window)
     h = h + linear(a, W("self_attn.o_proj.weight"), act, compute)
     x2 = _round(rms_norm(h, W("post_attention_layernorm.weight"), c["eps"]), act, compute)
@@ -233,16 +240,19 @@ def block(h, pos, weights, cfg, layer: int, act, compute, weight_layer: int | No
 
 
 def forward_logits(weights, cfg: dict, ids, *, act=None, compute=torch.float32,
-                   schedule=None, windows=None) -> torch.Tensor:
+                   schedule=None, windows=None, reads_cache_of=None) -> torch.Tensor:
     """Logits ``[T, V]`` of one whole sequence: embed -> blocks -> final norm -> head
     (src/quanta/minimax/model.py:86-96; head in float32, src/quanta/minimax/runtime.py:95-98).
     ``schedule`` lists the layers in the order they run (a layer may appear twice); ``windows`` maps a
-    place in that order to the window of its attention (absent: every key)."""
-    return forward_logits_many(weights, cfg, [ids], act=act, compute=compute, schedule=schedule, windows=windows)[0]
+    place in that order to the window of its attention (absent: every key); ``reads_cache_of`` maps a
+    place to an earlier place whose cached keys and values it attends over instead of its own."""
+    return forward_logits_many(weights, cfg, [ids], act=act, compute=compute, schedule=schedule, windows=windows,
+                               reads_cache_of=reads_cache_of)[0]
 
 
 def forward_logits_many(weights, cfg: dict, sequences, *, rows=None, act=None, compute=torch.float32,
-                        schedule=None, windows=None, probes: list | None = None, given: dict | None = None) -> list:
+                        schedule=None, windows=None, probes: list | None = None, given: dict | None = None,
+                        reads_cache_of: dict | None = None) -> list:
     """The same for several sequences, each whole and alone, layer by layer: a layer's tensors are
     asked for once and serve every sequence, so ``weights`` may be a function that makes them when
     asked (``_LayerTensors`` keeps what one layer asked for until the next begins).  ``rows[i]``:
@@ -261,13 +271,14 @@ def forward_logits_many(weights, cfg: dict, sequences, *, rows=None, act=None, c
         layer = _LayerTensors(weights)
         for j, h in enumerate(hs):
             pos = torch.arange(h.shape[0], device=dev)
-            probe = {} if probes is not None else None
+            src = (reads_cache_of or {}).get(i)
+            probe = {} if (probes is not None or reads_cache_of) else None
             hs[j] = block(h, pos, layer, cfg, i, act, compute, weight_layer=wl, window=(windows or {}).get(i),
-                          probe=probe, given=(given or {}).get((j, i)))
+                          probe=probe, given=(given or {}).get((j, i)), kv_of=None if src is None else seen[j][src])
             seen[j].append(probe)
         del layer
     if probes is not None:
-        probes.extend(seen)
+        probes.extend([{k: v for k, v in p.items() if k not in ("k", "v")} for p in per_seq] for per_seq in seen)
     norm_w = _w(weights, "model.norm.weight").to(compute)
     head = _w(weights, "model.embed_tokens.weight" if cfg["tied"] else "lm_head.weight")
     out = []

@@ -503,12 +503,14 @@ def test_expert_products(dtype, T, H, I, E, k, path):
     assert int(st[0]) == 0
 
 
-@pytest.mark.parametrize("T,in_kernel_gather", [(1, True), (8, True), (8, False), (64, True), (300, False), (2048, False)])
+@pytest.mark.parametrize("T,in_kernel_gather", [(1, True), (8, True), (8, False), (64, True), (300, False), (2048, False),
+                                                (4096, False)])
 def test_expert_products_at_the_full_widths(T, in_kernel_gather):
     """Hidden 3072, experts of width 1536, 256 experts with 8 chosen: the launch geometry of the full-size
-    model (24 and 24 blocks of 128 features a tile, token tiles of 16 to 128 rows, rings of several stages),
-    with the token rows fetched by the kernel (one TMA box a row, steps of at most 64 tokens) and from a
-    gathered copy.  Against float32 products taken expert by expert."""
+    model (24 and 24 blocks of 128 features a tile, token tiles of 16 to 256 rows, rings of several stages; from
+    128-row tiles on the down product takes two blocks of 128 features a block), with the token rows fetched by
+    the kernel (one TMA box a row, steps of at most 64 tokens) and from a gathered copy.  4,096 tokens: 128 rows
+    an expert, tiles of 256 rows.  Against float32 products taken expert by expert."""
     kern = K()
     H, I, E, k = 3072, 1536, 256, 8
     torch.manual_seed(T)
@@ -524,6 +526,7 @@ def test_expert_products_at_the_full_widths(T, in_kernel_gather):
     pw = torch.rand(T, k, device=DEV)
     n_pairs = T * k
     bm = kern.expert_tile_rows(T, n_pairs / E)
+    assert bm == {1: 16, 8: 16, 64: 64, 300: 128, 2048: 128, 4096: 256}[T]
     words, max_tiles = kern.moe_plan_sizes(n_pairs, E, bm)
     plan = torch.empty(words, device=DEV, dtype=torch.int32)
     sorted_pair = torch.empty(n_pairs, device=DEV, dtype=torch.int32)

@@ -162,9 +162,9 @@ def test_run_order_is_data_a_layer_twice(model_dirs, plain_models):
         assert H.first_wrong(got, want, 2e-5) is None
 
 
-def test_a_layer_reads_another_layers_cache(model_dirs):
-    """Schedule entry 2 runs layer 1's weights on the K/V that entry 0 wrote (it writes none).  The
-    result must not depend on how the tokens are cut, and must differ from the unshared model."""
+def test_a_layer_reads_another_layers_cache(model_dirs, plain_models):
+    """Schedule entry 2 runs layer 1's weights on the K/V that entry 0 wrote (it writes none): against the
+    plain implementation in the same form, under three cuttings."""
     from quanta_b200.engine.model import Model
     from quanta_b200.engine.step import Engine
     from quanta_b200.parts.spec import ScheduleEntry
@@ -173,11 +173,13 @@ def test_a_layer_reads_another_layers_cache(model_dirs):
     model = Model(spec, dtype="float32").load(FolderSource(model_dirs["A"]))
     eng = Engine(model, num_pages=32, page_size=4, max_requests=4)
     assert sorted(eng.kv) == [0, 1]
-    reqs = {"a": H.random_tokens(27, 512, 3)}
-    whole = H.replay(eng, H.cut_whole(reqs))
-    for cut in (H.cut_tail_decode(reqs, 10), H.cut_portions(reqs)):
+    reqs = {"a": H.random_tokens(27, 512, 3), "b": H.random_tokens(40, 512, 4)}
+    want = H.plain_logits(plain_models["A"], reqs, schedule=[0, 1, 1], reads_cache_of={2: 0})
+    unshared = H.plain_logits(plain_models["A"], reqs, schedule=[0, 1, 1])
+    assert float((want[("a", 26)] - unshared[("a", 26)]).abs().max()) > 1e-3          # the shared cache matters
+    for cut in (H.cut_whole(reqs), H.cut_tail_decode(reqs, 10), H.cut_portions(reqs), H.cut_mixed(reqs, 2, seed=3)):
         got = H.replay(eng, cut)
-        assert H.first_wrong(got, whole, 2e-5) is None
+        assert H.first_wrong(got, want, 2e-5) is None, H.worst_error(got, want)
     with pytest.raises(ValueError, match="does not run before"):
         _spec_with_schedule("A", [ScheduleEntry(0, read_cache_of=1), ScheduleEntry(1)])
 
