@@ -404,6 +404,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   __shared__ AdDesc s_desc[2][32];            // the tiles of a batch of 32, double-buffered (the first producer's)
   __shared__ AdDesc s_desc_v[2][32];          // the second producer's own copy
   __shared__ float s_ml[AD_CONSUMERS][16][2];
+  __shared__ float s_fw[AD_CONSUMERS][16];    // segment end: the weight of each warp's part of a row
+  __shared__ float s_row[16 * AD_CONSUMERS][4];     // and the row's (max, sum, 1 / sum)
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -710,8 +712,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
       } else {
         // the warps hold key slices of the same rows: merge them through the tile's own shared memory
+        // With at most 8 q heads a kv head the four warps' rows fit the K half of the tile ([4][8][HDP] floats):
+        // what they leave there can only reach scores that the mask replaces, so the tile need not be wiped,
+        // and each warp gives the tile back when it has read what it merges.  With more heads the parts
+        // fill K and V ([4][16][HDP]) and the tile goes back as zeros (V rows that a later, shorter copy does
+        // not cover must stay finite).
+        const bool compact = RB == 1 && G <= 8 && hd == HDP;      // no padded dims: every K element of a row is copied over
+        const int sc_rows = compact ? 8 : 16;
         if (!cons_sync()) break;                         // every warp has read the tile
-        float* sc = reinterpret_cast<float*>(ks);        // [4 warps][16 rows][HDP], columns XORed by (row & 3) * 8
+        float* sc = reinterpret_cast<float*>(ks);        // [4 warps][sc_rows][HDP], columns XORed by (row & 3) * 8
         if (active) {
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
@@ -721,41 +730,60 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
             for (int i = 0; i < HDP / 8; ++i) {
               const int col = (i * 8 + qd * 2) ^ ((rr & 3) * 8);
-              *reinterpret_cast<float2*>(sc + (size_t)(warp * 16 + rr) * HDP + col) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+              *reinterpret_cast<float2*>(sc + (size_t)(warp * sc_rows + rr) * HDP + col) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
             }
           }
         }
         if (!cons_sync()) break;
         const int ctid = warp * 32 + lane;
-        for (int e = ctid; e < G * hd; e += AD_CONSUMERS * 32) {
-          const int R = e / hd, dd = e - R * hd, rb = R >> 4, rr = R & 15;
-          float M = -INFINITY;
-          for (int s = 0; s < KS; ++s) {
-            const int w = RB == 1 ? s : (rb | (s << 1));
-            M = fmaxf(M, s_ml[w][rr][0]);
-          }
-          float acc = 0.f, L = 0.f;
-          for (int s = 0; s < KS; ++s) {
-            const int w = RB == 1 ? s : (rb | (s << 1));
+        // A thread a row first: the weights of the row's parts and its (max, sum); then every thread adds the
+        // weighted parts of its columns, row after row, with nothing but independent loads in the loop (one
+        // warp a scheduler: a chain of dependent shared-memory reads and exponentials per element was 4 us).
+        if (ctid < G) {
+          const int R = ctid, rb = R >> 4, rr = R & 15;
+          float M = -INFINITY, L = 0.f;
+          for (int sl = 0; sl < KS; ++sl) M = fmaxf(M, s_ml[RB == 1 ? sl : (rb | (sl << 1))][rr][0]);
+          for (int sl = 0; sl < KS; ++sl) {
+            const int w = RB == 1 ? sl : (rb | (sl << 1));
             const float ms = s_ml[w][rr][0];
             const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            acc += f * sc[(size_t)(w * 16 + rr) * HDP + (dd ^ ((rr & 3) * 8))];
             L += f * s_ml[w][rr][1];
+            s_fw[w][rr] = f;
           }
-          const int head = d.kvh * G + R;
-          const size_t row_at = ((size_t)d.z * nq + head) * n_parts;
-          if (d.flags & AD_WHOLE) {
-            out[((size_t)d.tok * nq + head) * hd + dd] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-          } else if (fits) {
-            const size_t at = row_at + d.seg;
-            part_o[at * hd + dd] = acc;
-            if (dd == 0) { part_ml[at * 2] = M; part_ml[at * 2 + 1] = L; }
-          }
-          if (dd == 0 && (d.flags & AD_PAIR_END)) part_ml[(row_at + n_parts - 1) * 2] = __int_as_float(count);
+          s_row[R][0] = M;
+          s_row[R][1] = L;
+          s_row[R][2] = L > 0.f ? 1.f / L : 0.f;
         }
-        if (!cons_sync()) break;                         // the merged rows have been read
-        // the tile goes back as zeros: rows that the next copy does not cover must stay finite
-        for (size_t i = ctid; i < 2 * tile_elems / 8; i += AD_CONSUMERS * 32) reinterpret_cast<uint4*>(ks)[i] = make_uint4(0, 0, 0, 0);
+        if (!cons_sync()) break;
+#pragma unroll 2
+        for (int R = 0; R < G; ++R) {
+          const int rb = R >> 4, rr = R & 15, head = d.kvh * G + R;
+          const float M = s_row[R][0], L = s_row[R][1], inv_l = s_row[R][2];
+          const size_t row_at = ((size_t)d.z * nq + head) * n_parts;
+          for (int dd = ctid; dd < hd; dd += AD_CONSUMERS * 32) {
+            float acc = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl) {
+              if (sl < KS) {
+                const int w = RB == 1 ? sl : (rb | (sl << 1));
+                acc += s_fw[w][rr] * sc[(size_t)(w * sc_rows + rr) * HDP + (dd ^ ((rr & 3) * 8))];
+              }
+            }
+            if (d.flags & AD_WHOLE) {
+              out[((size_t)d.tok * nq + head) * hd + dd] = __float2bfloat16_rn(acc * inv_l);
+            } else if (fits) {
+              part_o[(row_at + d.seg) * hd + dd] = acc;
+            }
+          }
+          if (ctid == 0) {
+            if (!(d.flags & AD_WHOLE) && fits) { part_ml[(row_at + d.seg) * 2] = M; part_ml[(row_at + d.seg) * 2 + 1] = L; }
+            if (d.flags & AD_PAIR_END) part_ml[(row_at + n_parts - 1) * 2] = __int_as_float(count);
+          }
+        }
+        if (!compact) {
+          if (!cons_sync()) break;                       // the merged rows have been read
+          for (size_t i = ctid; i < 2 * tile_elems / 8; i += AD_CONSUMERS * 32) reinterpret_cast<uint4*>(ks)[i] = make_uint4(0, 0, 0, 0);
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
       __syncwarp();
