@@ -146,10 +146,11 @@ def router(tokens: int, hidden: int, experts: int, top_k: int) -> dict:
             "topk_us": round(t_sel * 1e3, 1)}
 
 
-def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int) -> dict:
+def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int, even: bool = False) -> dict:
     """The routed experts of one layer for a step of ``tokens`` tokens (random routing, a fresh one each
     call so that no call finds its experts in L2): expert plan, row gather and the two tcgen05 products, each
-    timed as launches in a CUDA graph.  ``GB/s`` counts the weights of the distinct experts once."""
+    timed as launches in a CUDA graph.  ``GB/s`` counts the weights of the distinct experts once, ``TFLOP/s``
+    the multiply-adds of the rows.  ``even``: every expert gets the same number of rows (no ragged last tiles)."""
     w13 = torch.empty(n_experts, 2 * width, hidden, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02)
     w2 = torch.empty(n_experts, hidden, width, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02)
     n_pairs, st = tokens * top_k, k.new_status(DEV)
@@ -158,7 +159,11 @@ def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int) ->
     sets, distinct = [], []
     for i in range(4):
         x = torch.randn(tokens, hidden, device=DEV).bfloat16()
-        idx = torch.stack([torch.randperm(n_experts, device=DEV)[:top_k] for _ in range(tokens)]).int()
+        if even:
+            idx = ((torch.arange(tokens, device=DEV)[:, None] * top_k + torch.arange(top_k, device=DEV)[None, :] + i)
+                   % n_experts).int()
+        else:
+            idx = torch.stack([torch.randperm(n_experts, device=DEV)[:top_k] for _ in range(tokens)]).int()
         w = torch.rand(tokens, top_k, device=DEV)
         plan = torch.empty(plan_words, dtype=torch.int32, device=DEV)
         sp = torch.empty(n_pairs, dtype=torch.int32, device=DEV)
@@ -189,6 +194,9 @@ def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int) ->
     gb = sum(distinct) / 4 * hidden * width * 2 / 1e9
     out["up_GB/s"] = round(2 * gb / (out["up_us"] * 1e-6), 0)
     out["down_GB/s"] = round(gb / (out["down_us"] * 1e-6), 0)
+    tf = 2.0 * n_pairs * hidden * width / 1e12
+    out["up_TFLOP/s"] = round(2 * tf / (out["up_us"] * 1e-6), 0)
+    out["down_TFLOP/s"] = round(tf / (out["down_us"] * 1e-6), 0)
     assert int(st[0]) == 0
     return out
 
@@ -208,6 +216,7 @@ def main() -> None:
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--width", type=int, default=1536, help="inner size of an expert")
+    ap.add_argument("--even-routing", action="store_true", help="experts: the same number of rows for every expert")
     a = ap.parse_args()
     shape = (a.q_heads, a.kv_heads, a.head_dim, a.page)
     if a.what == "attn_decode":
@@ -215,7 +224,7 @@ def main() -> None:
     elif a.what == "attn_span":
         print(json.dumps(attn_span(a.tokens, a.start, *shape)), flush=True)
     elif a.what == "experts":
-        print(json.dumps(experts(a.tokens, a.hidden, a.width, a.experts, a.top_k)), flush=True)
+        print(json.dumps(experts(a.tokens, a.hidden, a.width, a.experts, a.top_k, a.even_routing)), flush=True)
     elif a.what == "router":
         print(json.dumps(router(a.tokens, a.hidden, a.experts, a.top_k)), flush=True)
     else:

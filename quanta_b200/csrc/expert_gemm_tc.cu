@@ -70,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-// L2 policies: weights are read once per step (evict first), token tiles by every row block (evict last)
+// L2 policies: weights are read once per step by small tiles (evict first), token tiles by every row block (evict last)
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -112,6 +112,41 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ---- a pair of blocks on neighbouring SMs computing one tile (cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of the same variable in the block of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// a block's own box, its bytes counted on a barrier that may be the pair's other block's
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// arrives, once the MMAs issued so far are done, on the barrier at this offset in both blocks of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -132,14 +167,22 @@ struct EgShared {
 // (gate and up rows of the same features).  MODE 2 takes two neighbouring blocks of 128 features when the
 // token tile is 256 rows (steps bound by the tensor cores): the token tile, half of what a stage holds then,
 // is fetched from L2 once for 256 features instead of once for 128.
-template <int MODE, int NM>
-__global__ void __launch_bounds__(EG_THREADS, 2)
-expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                      void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
-                      const int* __restrict__ plan, const int* __restrict__ tile_expert,
-                      const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
-                      int tmem_cols, int gather_k, int* status) {
+//
+// PAIR: two blocks on neighbouring SMs (a cluster of two) take one tile of 256 token rows together, each
+// 128 (MODE 1) or 256 (MODE 2) of its features: tcgen05.mma.cta_group::2 with M = 256.  Each block fetches
+// its own weight tiles and HALF of the token tile, and the tensor cores of both read both halves, so a block
+// takes three quarters of the bytes from L2, and reads two thirds of the bytes from its shared memory, that
+// it would alone.  The first block of the pair issues all MMAs; every copy of either block counts on the
+// first block's barrier; a commit frees the stage in both.
+template <int MODE, int NM, bool PAIR>
+__device__ __forceinline__ void
+expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
+                    void* __restrict__ out, const int* __restrict__ sorted_pair, const float* __restrict__ pair_w,
+                    const int* __restrict__ plan, const int* __restrict__ tile_expert,
+                    const int* __restrict__ tile_row0, int E, int K, int N_out, int NT, int stages,
+                    int tmem_cols, int gather_k, int* status) {
   constexpr int FEATS = MODE == 1 ? EG_M : NM * EG_M;      // output features a block
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;     // 0: the block that issues the MMAs
   extern __shared__ unsigned char smem_dyn[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -154,7 +197,12 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int rows = min(NT, plan[2 * E + e + 1] - row0);          // valid token rows of this tile
   const int j0 = blockIdx.x * FEATS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t a_bytes = EG_M * EG_BK * 2, b_bytes = (uint32_t)NT * EG_BK * 2;
+  // the MMA's N is what this tile holds, in steps of 16: an expert's last tile of a few rows costs the
+  // tensor cores a few columns, not a whole tile (the box that TMA fetches keeps its size)
+  const int n_mma = min(NT, (rows + 15) & ~15);
+  // a pair's block holds half of the MMA's token rows: rows [rank * n_mma / 2, +n_mma / 2) of the tile, as
+  // the first rows of a box of NT / 2
+  const uint32_t a_bytes = EG_M * EG_BK * 2, b_bytes = (uint32_t)(PAIR ? NT / 2 : NT) * EG_BK * 2;
   const uint32_t stage_bytes = NM * a_bytes + b_bytes;
   const int k_blocks = (K + EG_BK - 1) / EG_BK;
   volatile int* abort_flag = &sh.abort_flag;
@@ -168,10 +216,16 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {      // one warp allocates the accumulator columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&sh.tmem_base)), "r"((uint32_t)tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {      // one warp allocates the accumulator columns (in a pair: the same warp of both blocks)
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(&sh.tmem_base)), "r"((uint32_t)tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(&sh.tmem_base)), "r"((uint32_t)tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   if (MODE == 1 && gather_k > 0) {
     // the token rows are fetched one by one from the step's activations: row i of the tile is the token
@@ -180,6 +234,7 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // both blocks' barriers exist before either counts on the other's
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = sh.tmem_base;
 
@@ -187,7 +242,9 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const int w_row = MODE == 1 ? e * 2 * N_out + j0 : e * N_out + j0;
-      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+      // weights are read once per step by tiles of few rows (evict first); the 256-row tiles of one expert run at
+      // about the same time and read the same weights, so those stay (measured: 5 % on a 16,384-token step)
+      const uint64_t pol_w = PAIR ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
       int armed = 0;
       for (int kb = 0; kb < k_blocks; ++kb) {
         const int s = kb % stages;
@@ -195,6 +252,16 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (!mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag)) break;
         const uint32_t full = smem_u32(&sh.full[s]);
         unsigned char* st = tiles + (size_t)s * stage_bytes;
+        if (PAIR) {
+          // the first block expects both blocks' bytes; the second's copies may count before that
+          const uint32_t full0 = mapa_u32(full, 0u);
+          if (rank == 0) mbar_expect_tx(full, 2u * stage_bytes);
+          tma_load_2d_pair(smem_u32(st), &tm_w, kb * EG_BK, w_row, full0, pol_w);
+          if (NM == 2) tma_load_2d_pair(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), full0, pol_w);
+          tma_load_2d_pair(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0 + (int)rank * (n_mma / 2), full0, pol_x);
+          armed = kb + 1;
+          continue;
+        }
         const bool by_row = MODE == 1 && gather_k > 0;
         mbar_expect_tx(full, by_row ? NM * a_bytes + (uint32_t)rows * EG_BK * 2 : stage_bytes);
         tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full, pol_w);
@@ -212,7 +279,11 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
         armed = kb + 1;
       }
-      if (*abort_flag) {
+      if (*abort_flag && PAIR && rank != 0) {
+        // this block's copies count on the other block's barriers, which it cannot wait on: give them time
+        const uint64_t t0 = global_ns();
+        for (uint32_t it = 0; it < EG_SPIN_LIMIT && global_ns() - t0 < 100000ull; ++it) __nanosleep(1000);
+      } else if (*abort_flag) {
         // let the copies that were issued land before this block's shared memory is given away
         for (int kb = max(0, armed - stages); kb < armed; ++kb) {
           const int s = kb % stages;
@@ -225,10 +296,8 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      // the MMA's N is what this tile holds, in steps of 16: an expert's last tile of a few rows costs the
-      // tensor cores a few columns, not a whole tile (the box that TMA fetches stays NT rows)
-      const uint32_t idesc = umma_idesc(EG_M, min(NT, (rows + 15) & ~15));
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(PAIR ? 2 * EG_M : EG_M, n_mma);
       bool ok = true;
       for (int kb = 0; kb < k_blocks && ok; ++kb) {
         const int s = kb % stages;
@@ -244,13 +313,20 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 #pragma unroll
           for (int k16 = 0; k16 < EG_BK / 16; ++k16) {
             // 16 k elements = 32 bytes further along the swizzled row: +2 in the 16-byte address field
-            umma_bf16(tmem_base + (uint32_t)(m * NT), a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc,
-                      (kb | k16) != 0 ? 1u : 0u);
+            if (PAIR)
+              umma_bf16_pair(tmem_base + (uint32_t)(m * NT), a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2),
+                             idesc, (kb | k16) != 0 ? 1u : 0u);
+            else
+              umma_bf16(tmem_base + (uint32_t)(m * NT), a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc,
+                        (kb | k16) != 0 ? 1u : 0u);
           }
         }
-        umma_commit(smem_u32(&sh.empty[s]));      // the stage is free once these MMAs have read it
+        // the stage is free once these MMAs have read it
+        if (PAIR) umma_commit_pair(smem_u32(&sh.empty[s])); else umma_commit(smem_u32(&sh.empty[s]));
       }
-      if (ok) umma_commit(smem_u32(&sh.tmem_full));
+      if (ok) {
+        if (PAIR) umma_commit_pair(smem_u32(&sh.tmem_full)); else umma_commit(smem_u32(&sh.tmem_full));
+      }
     }
   } else {
     // ---------------- epilogue: 4 warps, one TMEM lane quadrant each ----------------
@@ -304,10 +380,32 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // neither block of a pair leaves, or gives its accumulators back, while the other's MMAs may read its
+  // shared memory or its epilogue its TMEM
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
   }
   if (threadIdx.x == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, tile, 5);
+}
+
+#define QB_EG_PARAMS                                                                                              \
+  const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, void* __restrict__ out,     \
+      const int* __restrict__ sorted_pair, const float* __restrict__ pair_w, const int* __restrict__ plan,        \
+      const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, int E, int K, int N_out, int NT,    \
+      int stages, int tmem_cols, int gather_k, int* status
+#define QB_EG_ARGS tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, N_out, NT, stages, tmem_cols, gather_k, status
+
+template <int MODE, int NM>
+__global__ void __launch_bounds__(EG_THREADS, 2) expert_gemm_tc_kernel(QB_EG_PARAMS) {
+  expert_gemm_tc_body<MODE, NM, false>(QB_EG_ARGS);
+}
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(EG_THREADS, 1) expert_gemm_tc_pair_kernel(QB_EG_PARAMS) {
+  expert_gemm_tc_body<MODE, 2, true>(QB_EG_ARGS);
 }
 
 // out[p, :] = x[sorted_pair[p] / top_k, :]   (rows of 16-byte chunks)
@@ -379,15 +477,17 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   // token tiles (see the kernel)
   const int nm = (mode == 1 || NT >= 128) ? 2 : 1;
   const int feats = mode == 1 ? EG_M : nm * EG_M;
+  // tiles of 256 token rows (steps bound by the tensor cores) are taken by pairs of blocks, see the kernel
+  const bool pair = NT == 256;
   if (((uintptr_t)x_rows | (uintptr_t)weights) & 15) return QB_ERR_BAD_ARG;
   CUtensorMap tm_w, tm_x;
   int rc = make_map(&tm_w, weights, (uint64_t)E * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
-  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0))) return QB_ERR_BAD_ARG;
+  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0 || pair))) return QB_ERR_BAD_ARG;
   rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)
-                    : make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)NT);
+                    : make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)(pair ? NT / 2 : NT));
   if (rc) return rc;
-  const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)NT * EG_BK * 2;
+  const size_t stage_bytes = (size_t)nm * EG_M * EG_BK * 2 + (size_t)(pair ? NT / 2 : NT) * EG_BK * 2;
   // Two blocks share an SM (shared memory is the limit), so that one block's prologue and epilogue run
   // under the other's main loop; each gets a ring of about 105 KB.
   // a tile of 256 token rows has a block to itself on its SM (its two accumulators fill the TMEM)
@@ -398,7 +498,9 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       sms = 1;
   }
-  const size_t blocks = (size_t)((N_out + feats - 1) / feats) * (size_t)max_tiles;
+  int grid_x = (N_out + feats - 1) / feats;
+  if (pair) grid_x = (grid_x + 1) & ~1;      // a pair's second block may lie past the last feature: it drops its columns
+  const size_t blocks = (size_t)grid_x * (size_t)max_tiles;
   const bool alone = NT > 128 || blocks <= (size_t)sms;
   // Token tiles of at most 32 rows (decode steps of a few tokens: short blocks, one expert's 128 features
   // each): three blocks an SM with rings of about 70 KB hide a block's prologue and epilogue better than
@@ -415,19 +517,20 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   const size_t smem = stage_bytes * stages + 1024;
   int tmem_cols = 32;
   while (tmem_cols < nm * NT) tmem_cols *= 2;
-  dim3 grid((N_out + feats - 1) / feats, max_tiles);
+  dim3 grid(grid_x, max_tiles);
   cudaError_t err;
-#define QB_EG(MODE_, NM_, GK)                                                                                        \
+#define QB_EG(KERNEL_, GK)                                                                                         \
   do {                                                                                                             \
-    err = cudaFuncSetAttribute(expert_gemm_tc_kernel<MODE_, NM_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    err = cudaFuncSetAttribute(KERNEL_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
     if (err != cudaSuccess) return (int)err;                                                                       \
-    expert_gemm_tc_kernel<MODE_, NM_><<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, \
-                                                                         tile_expert, tile_row0, E, K, N_out, NT,  \
-                                                                         stages, tmem_cols, GK, status);            \
+    KERNEL_<<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, \
+                                               N_out, NT, stages, tmem_cols, GK, status);                          \
   } while (0)
-  if (mode == 1) QB_EG(1, 2, gather_k);
-  else if (nm == 2) QB_EG(2, 2, 0);
-  else QB_EG(2, 1, 0);
+  if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, 0);
+  else if (pair) QB_EG(expert_gemm_tc_pair_kernel<2>, 0);
+  else if (mode == 1) QB_EG((expert_gemm_tc_kernel<1, 2>), gather_k);
+  else if (nm == 2) QB_EG((expert_gemm_tc_kernel<2, 2>), 0);
+  else QB_EG((expert_gemm_tc_kernel<2, 1>), 0);
 #undef QB_EG
   QB_LAUNCH_CHECK();
   return 0;
