@@ -31,7 +31,8 @@ namespace {
 
 constexpr int EG_M = 128;            // output features per block (UMMA M)
 constexpr int EG_BK = 64;            // k elements per stage: 128 bytes, one swizzle row
-constexpr int EG_THREADS = 192;
+constexpr int EG_THREADS = 192;        // producer warp, MMA warp, four epilogue warps
+constexpr int EG_PAIR_THREADS = 320;   // a pair's blocks: eight epilogue warps
 constexpr uint32_t EG_SPIN_LIMIT = 4u * 1000u * 1000u;
 constexpr uint64_t EG_WAIT_NS = 200ull * 1000ull * 1000ull;   // no wait is longer than 0.2 s
 
@@ -154,6 +155,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
+
+// silu(g) * u.  The exponential and the quotient are the fast ones (2 ulp); the result is rounded to bfloat16.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 struct EgShared {
   uint64_t full[8];
@@ -329,18 +333,21 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
       }
     }
   } else {
-    // ---------------- epilogue: 4 warps, one TMEM lane quadrant each ----------------
-    const int quad = warp & 3;
+    // ---------------- epilogue: one TMEM lane quadrant a warp (a warp reaches the 32 lanes of its index
+    // modulo 4); a pair's blocks have two warps a quadrant that take the column chunks in turn ----------------
+    constexpr int SPLIT = PAIR ? 2 : 1;
+    constexpr int EPI_THREADS = SPLIT * 128;
+    const int quad = warp & 3, sub = (warp - 2) >> 2;
     const int feat = j0 + quad * 32 + lane;
     if (MODE == 2) {
       // where each row goes and its routing weight: fetched here, under the main loop, by the warps that
       // need them at its end (two dependent reads that the producer and the issuer do not wait for)
-      for (int i = threadIdx.x - 64; i < NT; i += 128) {
+      for (int i = threadIdx.x - 64; i < NT; i += EPI_THREADS) {
         const int pr = i < rows ? sorted_pair[row0 + i] : 0;
         s_pair[i] = pr;
         s_w[i] = i < rows ? pair_w[pr] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");      // the epilogue warps
     }
     // tcgen05.ld / wait::ld are .sync.aligned: the whole warp runs them or none of it does, so the lanes
     // vote on the wait's answer (a lane may see another role's abort flag before its neighbour does)
@@ -348,31 +355,36 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
     if (acc_ready) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      for (int c0 = 0; c0 < NT; c0 += 16) {
-        if (c0 >= rows) break;
+      for (int c0 = 16 * sub; c0 < rows; c0 += 16 * SPLIT) {
         uint32_t v0[16], v1[16];
         tmem_ld16(lane_addr + (uint32_t)c0, v0);
         if (NM == 2) tmem_ld16(lane_addr + (uint32_t)(NT + c0), v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // all 16 columns are computed (independent chains, one warp a scheduler has nothing else to hide
+        // latency with); only the stores look at the row count
         if (MODE == 1) {
-          if (feat < N_out) {
+          __nv_bfloat16 r[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = c0 + i;
-              if (col >= rows) break;
-              const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
-              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)(row0 + col) * N_out + feat] =
-                  __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
-            }
+          for (int i = 0; i < 16; ++i) {
+            const float g = __uint_as_float(v0[i]), u = __uint_as_float(v1[i]);
+            r[i] = __float2bfloat16_rn(silu_mul(g, u));
+          }
+          if (feat < N_out) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + c0) * N_out + feat;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (c0 + i < rows) dst[(size_t)i * N_out] = r[i];
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int col = c0 + i;
-            if (col >= rows) break;
-            float* dst = reinterpret_cast<float*>(out) + (size_t)s_pair[col] * N_out;
-            if (feat < N_out) dst[feat] = s_w[col] * __uint_as_float(v0[i]);
-            if (NM == 2 && feat + EG_M < N_out) dst[feat + EG_M] = s_w[col] * __uint_as_float(v1[i]);
+            if (col < rows) {
+              float* dst = reinterpret_cast<float*>(out) + (size_t)s_pair[col] * N_out;
+              const float w = s_w[col];
+              if (feat < N_out) dst[feat] = w * __uint_as_float(v0[i]);
+              if (NM == 2 && feat + EG_M < N_out) dst[feat + EG_M] = w * __uint_as_float(v1[i]);
+            }
           }
         }
       }
@@ -404,7 +416,7 @@ __global__ void __launch_bounds__(EG_THREADS, 2) expert_gemm_tc_kernel(QB_EG_PAR
   expert_gemm_tc_body<MODE, NM, false>(QB_EG_ARGS);
 }
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(EG_THREADS, 1) expert_gemm_tc_pair_kernel(QB_EG_PARAMS) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(EG_PAIR_THREADS, 1) expert_gemm_tc_pair_kernel(QB_EG_PARAMS) {
   expert_gemm_tc_body<MODE, 2, true>(QB_EG_ARGS);
 }
 
@@ -519,18 +531,18 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   while (tmem_cols < nm * NT) tmem_cols *= 2;
   dim3 grid(grid_x, max_tiles);
   cudaError_t err;
-#define QB_EG(KERNEL_, GK)                                                                                         \
+#define QB_EG(KERNEL_, GK, THREADS_)                                                                                       \
   do {                                                                                                             \
     err = cudaFuncSetAttribute(KERNEL_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
     if (err != cudaSuccess) return (int)err;                                                                       \
-    KERNEL_<<<grid, EG_THREADS, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, \
+    KERNEL_<<<grid, THREADS_, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, \
                                                N_out, NT, stages, tmem_cols, GK, status);                          \
   } while (0)
-  if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, 0);
-  else if (pair) QB_EG(expert_gemm_tc_pair_kernel<2>, 0);
-  else if (mode == 1) QB_EG((expert_gemm_tc_kernel<1, 2>), gather_k);
-  else if (nm == 2) QB_EG((expert_gemm_tc_kernel<2, 2>), 0);
-  else QB_EG((expert_gemm_tc_kernel<2, 1>), 0);
+  if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, 0, EG_PAIR_THREADS);
+  else if (pair) QB_EG(expert_gemm_tc_pair_kernel<2>, 0, EG_PAIR_THREADS);
+  else if (mode == 1) QB_EG((expert_gemm_tc_kernel<1, 2>), gather_k, EG_THREADS);
+  else if (nm == 2) QB_EG((expert_gemm_tc_kernel<2, 2>), 0, EG_THREADS);
+  else QB_EG((expert_gemm_tc_kernel<2, 1>), 0, EG_THREADS);
 #undef QB_EG
   QB_LAUNCH_CHECK();
   return 0;
