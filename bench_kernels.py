@@ -181,7 +181,7 @@ def experts(tokens: int, hidden: int, width: int, n_experts: int, top_k: int, ev
         "up": lambda s: k.expert_gemm_tc(1, s[7], w13, s[8], s[4], s[2].view(-1), s[3], s[5], s[6], n_experts, bm, st),
         "down": lambda s: k.expert_gemm_tc(2, s[8], w2, s[9], s[4], s[2].view(-1), s[3], s[5], s[6], n_experts, bm, st),
     }
-    if tokens <= 64:      # what small steps run: no gathered copy, the kernel fetches each pair's token row
+    if tokens <= 1024:    # what steps of few rows an expert run: no gathered copy, the kernel fetches each pair's token row
         calls["up_fetching_rows"] = lambda s: k.expert_gemm_tc(1, s[0], w13, s[8], s[4], s[2].view(-1), s[3], s[5], s[6],
                                                                n_experts, bm, st, gather_top_k=top_k)
     out = {"kernel": "moe_plan + gather_rows + expert_gemm_tc", "tokens": tokens, "hidden": hidden, "width": width,

@@ -827,9 +827,11 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
 
-  const int* tile = tiles + 4 * blockIdx.x;
+  // blocks are handed out in the order of blockIdx.x: all kv heads of the first tile, then of the second, so the
+  // order of the tile list (the caller puts the tiles with the most keys first) is the order of the work
+  const int* tile = tiles + 4 * (blockIdx.x / nkv);
   const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
-  const int kvh = blockIdx.y, G = nq / nkv;
+  const int kvh = blockIdx.x % nkv, G = nq / nkv;
   const int n_rows = min(BM, n_tok * G - row0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, qd = lane & 3;
   const int* bt = block_table + (size_t)req * bt_stride;
@@ -985,7 +987,7 @@ attn_span_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
   }
   __syncthreads();
-  if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
+  if (tid == 0 && abort_word) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x / nkv, 7);
 }
 
 // The pairs that the blocks' ranges cut: out[t, head, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over
@@ -1153,7 +1155,7 @@ extern "C" int qb_attn_span(const void* q, const void* k_cache, const void* v_ca
     return qb_attn_span_tc(q, k_cache, v_cache, out, tok_pos, block_table, bt_stride, tiles, n_tiles, nq, nkv, hd,
                            page_size, num_pages, scale, window, status, stream);
   const float scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(n_tiles, nkv);
+  dim3 grid((unsigned)n_tiles * (unsigned)nkv);
   const bool pow2 = (page_size & (page_size - 1)) == 0;
   const bool tma = hd % 64 == 0 && pow2 && (page_size <= AT_BN || page_size % AT_BN == 0) && encode_fn() != nullptr &&
                    (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;

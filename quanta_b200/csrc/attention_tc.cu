@@ -187,9 +187,11 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   __shared__ float s_l[2][TC_BM];
   volatile int* abort_flag = &sh.abort_flag;
 
-  const int* tile = tiles + 4 * blockIdx.x;
+  // blocks are handed out in the order of blockIdx.x: all kv heads of the first tile, then of the second, so the
+  // order of the tile list (the caller puts the tiles with the most keys first) is the order of the work
+  const int* tile = tiles + 4 * (blockIdx.x / nkv);
   const int req = tile[0], tok0 = tile[1], n_tok = tile[2], row0 = tile[3];
-  const int kvh = blockIdx.y, G = nq / nkv;
+  const int kvh = blockIdx.x % nkv, G = nq / nkv;
   const int n_rows = min(TC_BM, n_tok * G - row0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* bt = block_table + (size_t)req * bt_stride;
@@ -493,7 +495,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
-  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x, 7);
+  if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x / nkv, 7);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -561,7 +563,7 @@ extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v
   const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
   cudaError_t err = cudaFuncSetAttribute(attn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return (int)err;
-  attn_span_tc_kernel<<<dim3(n_tiles, nkv), TCS_THREADS, smem, stream>>>(
+  attn_span_tc_kernel<<<dim3((unsigned)n_tiles * (unsigned)nkv), TCS_THREADS, smem, stream>>>(
       tm_k, tm_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, tok_pos, block_table, bt_stride, tiles, nq, nkv,
       page_size, num_pages, scale_log2, window, status);
   QB_LAUNCH_CHECK();

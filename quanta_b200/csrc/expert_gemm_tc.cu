@@ -6,10 +6,11 @@
 // through shared memory exactly once per token tile:
 //
 //   warp 0   : TMA producer.  Per 64-wide k block: weight tile(s) [128 x 64] and token tile [NT x 64],
-//              bfloat16, 128-byte swizzle, into a ring of shared-memory stages (mbarrier expect_tx).
+//              bfloat16, 128-byte swizzle, into a ring of shared-memory stages (mbarrier expect_tx); lane 0
+//              fetches the boxes, all lanes share the rows where the token rows are fetched one by one.
 //   warp 1   : MMA issuer.  4 x tcgen05.mma (K = 16 each) per stage and matrix, D[128 x NT] float32 in
 //              TMEM; tcgen05.commit frees the stage and, at the end, signals the epilogue.
-//   warps 2-5: epilogue.  tcgen05.ld (one TMEM lane = one output feature per thread), then
+//   warps 2-5: epilogue (2-9 in the blocks of a pair).  tcgen05.ld (one TMEM lane = one output feature per thread), then
 //              MODE 1: act[p, j] = silu(gate) * up  (bfloat16),  gate/up = two accumulators;
 //              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32).
 //   (src/quanta/minimax/moe.py:59-88; rows p sorted by expert, see the plan kernels.)
@@ -18,8 +19,8 @@
 // stage, or, for steps of few tokens, the rows of x themselves as one box of one row each (gather_k);
 // MODE 2 reads the act rows MODE 1 wrote.  Rows past the expert's last row compute garbage
 // that the epilogue drops; TMA zero-fills past the end of a tensor, so K need not be a multiple of 64
-// (it must be a multiple of 8: 16-byte rows).  No multicast, no clusters: every tile comes from this
-// GPU's memory through a plain per-block TMA load.
+// (it must be a multiple of 8: 16-byte rows).  No multicast: every tile comes from this GPU's memory through
+// a plain per-block TMA load.  Tiles of 256 token rows are taken by two blocks together (see PAIR below).
 //
 // Every wait on an mbarrier is bounded; when one runs out the block records it in the status words,
 // lets its copies in flight land, frees its TMEM and returns.
@@ -243,46 +244,56 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
   const uint32_t tmem_base = sh.tmem_base;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      const int w_row = MODE == 1 ? e * 2 * N_out + j0 : e * N_out + j0;
-      // weights are read once per step by tiles of few rows (evict first); the 256-row tiles of one expert run at
-      // about the same time and read the same weights, so those stay (measured: 5 % on a 16,384-token step)
-      const uint64_t pol_w = PAIR ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
-      int armed = 0;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % stages;
-        const uint32_t ph = (uint32_t)(kb / stages) & 1u;
-        if (!mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag)) break;
-        const uint32_t full = smem_u32(&sh.full[s]);
-        unsigned char* st = tiles + (size_t)s * stage_bytes;
-        if (PAIR) {
-          // the first block expects both blocks' bytes; the second's copies may count before that
-          const uint32_t full0 = mapa_u32(full, 0u);
-          if (rank == 0) mbar_expect_tx(full, 2u * stage_bytes);
-          tma_load_2d_pair(smem_u32(st), &tm_w, kb * EG_BK, w_row, full0, pol_w);
-          if (NM == 2) tma_load_2d_pair(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), full0, pol_w);
-          tma_load_2d_pair(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0 + (int)rank * (n_mma / 2), full0, pol_x);
-          armed = kb + 1;
-          continue;
-        }
-        const bool by_row = MODE == 1 && gather_k > 0;
-        mbar_expect_tx(full, by_row ? NM * a_bytes + (uint32_t)rows * EG_BK * 2 : stage_bytes);
-        tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, full, pol_w);
+    // ---------------- TMA producer: lane 0 waits and fetches the boxes; where the token rows are fetched
+    // one by one, all lanes take their share of them ----------------
+    const int w_row = MODE == 1 ? e * 2 * N_out + j0 : e * N_out + j0;
+    // weights are read once per step by tiles of few rows (evict first); the 256-row tiles of one expert run at
+    // about the same time and read the same weights, so those stay (measured: 5 % on a 16,384-token step)
+    const uint64_t pol_w = PAIR ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+    const bool by_row = MODE == 1 && gather_k > 0;
+    // the tile rows this block fetches: all of them, or a pair's half
+    const int r_lo = PAIR ? (int)rank * (n_mma / 2) : 0;
+    const int r_hi = PAIR ? min(rows, r_lo + n_mma / 2) : rows;
+    int armed = 0;
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      const int s = kb % stages;
+      const uint32_t ph = (uint32_t)(kb / stages) & 1u;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, abort_flag) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      const uint32_t full = smem_u32(&sh.full[s]);
+      // a pair: every copy of either block counts on the first block's barrier, which expects both blocks'
+      // bytes (the second block's copies may count before the first has said so)
+      const uint32_t bar = PAIR ? mapa_u32(full, 0u) : full;
+      unsigned char* st = tiles + (size_t)s * stage_bytes;
+      if (lane == 0) {
+        const uint32_t x_bytes = by_row ? (uint32_t)rows * EG_BK * 2 : (PAIR ? 2u : 1u) * b_bytes;
+        if (rank == 0) mbar_expect_tx(full, (PAIR ? 2u : 1u) * NM * a_bytes + x_bytes);
         // the second weight tile: the up rows of the same features, or the next 128 features (rows past the
         // expert's last are another expert's and give columns that the epilogue drops)
-        if (NM == 2) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), full, pol_w);
-        if (by_row) {
-          // boxes of one row: the swizzle follows the shared-memory address, so row i lands where a box of
-          // NT rows would have put it; the rows past the expert's last keep what the stage held before, and
-          // their columns of the product are never read
-          for (int i = 0; i < rows; ++i)
-            tma_load_2d(smem_u32(st + NM * a_bytes + i * (EG_BK * 2)), &tm_x, kb * EG_BK, s_pair[i], full, pol_x);
+        if (PAIR) {
+          tma_load_2d_pair(smem_u32(st), &tm_w, kb * EG_BK, w_row, bar, pol_w);
+          if (NM == 2) tma_load_2d_pair(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), bar, pol_w);
+          if (!by_row) tma_load_2d_pair(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0 + r_lo, bar, pol_x);
         } else {
-          tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, full, pol_x);
+          tma_load_2d(smem_u32(st), &tm_w, kb * EG_BK, w_row, bar, pol_w);
+          if (NM == 2) tma_load_2d(smem_u32(st + a_bytes), &tm_w, kb * EG_BK, w_row + (MODE == 1 ? N_out : EG_M), bar, pol_w);
+          if (!by_row) tma_load_2d(smem_u32(st + NM * a_bytes), &tm_x, kb * EG_BK, row0, bar, pol_x);
         }
-        armed = kb + 1;
       }
+      if (by_row) {
+        // boxes of one row: the swizzle follows the shared-memory address, so a row lands where a box of
+        // many rows would have put it; the rows past the expert's last keep what the stage held before, and
+        // their columns of the product are never read
+        for (int i = r_lo + lane; i < r_hi; i += 32) {
+          const uint32_t dst = smem_u32(st + NM * a_bytes + (i - r_lo) * (EG_BK * 2));
+          if (PAIR) tma_load_2d_pair(dst, &tm_x, kb * EG_BK, s_pair[i], bar, pol_x);
+          else tma_load_2d(dst, &tm_x, kb * EG_BK, s_pair[i], bar, pol_x);
+        }
+      }
+      armed = kb + 1;
+    }
+    if (lane == 0) {
       if (*abort_flag && PAIR && rank != 0) {
         // this block's copies count on the other block's barriers, which it cannot wait on: give them time
         const uint64_t t0 = global_ns();
@@ -495,7 +506,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   CUtensorMap tm_w, tm_x;
   int rc = make_map(&tm_w, weights, (uint64_t)E * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
-  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0 || pair))) return QB_ERR_BAD_ARG;
+  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0))) return QB_ERR_BAD_ARG;
   rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)
                     : make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)(pair ? NT / 2 : NT));
   if (rc) return rc;
@@ -538,7 +549,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
     KERNEL_<<<grid, THREADS_, smem, stream>>>(tm_w, tm_x, out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E, K, \
                                                N_out, NT, stages, tmem_cols, GK, status);                          \
   } while (0)
-  if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, 0, EG_PAIR_THREADS);
+  if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, gather_k, EG_PAIR_THREADS);
   else if (pair) QB_EG(expert_gemm_tc_pair_kernel<2>, 0, EG_PAIR_THREADS);
   else if (mode == 1) QB_EG((expert_gemm_tc_kernel<1, 2>), gather_k, EG_THREADS);
   else if (nm == 2) QB_EG((expert_gemm_tc_kernel<2, 2>), 0, EG_THREADS);

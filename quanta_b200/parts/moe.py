@@ -80,7 +80,11 @@ class SigmoidTopKExperts(FeedForward):
     # steps of fewer tokens take their logits on the CUDA cores, in one launch with selection and plan (and the
     # float32 path always); measured on a B200 the two ways cost the same at about a hundred tokens
     router_mma_min_tokens = 96
-    gather_in_kernel_max_tokens = 64 # steps of at most this many tokens fetch the token rows without a gathered copy
+    # steps with at most this many rows an expert on average fetch the token rows inside the product (one TMA box a
+    # row, the producer warp's lanes sharing them) instead of from a gathered copy; measured on a B200 the box a
+    # row costs more than the copy from some 12 rows an expert on (300 tokens: 701 against 717 us a layer, 512
+    # tokens: 746 against 732 us, 2,048 tokens: 1,358 against 815 us)
+    gather_in_kernel_max_rows = 10
 
     def path_for(self, x) -> str:
         ok16 = kernels.expert_gemm_tc_supported(x, self.H, self.I) and self.w13.dtype == torch.bfloat16
@@ -151,7 +155,7 @@ class SigmoidTopKExperts(FeedForward):
         y = torch.empty((T, self.k, self.H), dtype=torch.float32, device=dev)
         if path == "tc":
             # bfloat16: TMA-fed tcgen05 products, weights as the 128-row operand, accumulators in TMEM
-            if T <= self.gather_in_kernel_max_tokens:
+            if n_pairs <= self.gather_in_kernel_max_rows * self.E:
                 # few tokens: the kernel fetches each pair's token row itself
                 kernels.expert_gemm_tc(1, x, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert,
                                        tile_row0, self.E, bm, ctx.status, gather_top_k=self.k)

@@ -503,8 +503,8 @@ def test_expert_products(dtype, T, H, I, E, k, path):
     assert int(st[0]) == 0
 
 
-@pytest.mark.parametrize("T,in_kernel_gather", [(1, True), (8, True), (8, False), (64, True), (300, False), (2048, False),
-                                                (4096, False)])
+@pytest.mark.parametrize("T,in_kernel_gather", [(1, True), (8, True), (8, False), (64, True), (300, False), (300, True),
+                                                (2048, False), (2048, True), (4096, False), (4096, True)])
 def test_expert_products_at_the_full_widths(T, in_kernel_gather):
     """Hidden 3072, experts of width 1536, 256 experts with 8 chosen: the launch geometry of the full-size
     model (24 and 24 blocks of 128 features a tile, token tiles of 16 to 256 rows, rings of several stages; from
