@@ -445,12 +445,15 @@ def test_router_logits_selection_and_plan_in_one_launch(T, E, k, Kd, bm):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("path", ["simt", "tc"])
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 72, 40, 12, 3), (37, 96, 48, 16, 4), (130, 328, 200, 9, 2), (9, 1024, 520, 6, 2),
-                                       (300, 256, 136, 7, 2), (700, 64, 40, 9, 8)])
+                                       (300, 256, 136, 7, 2), (700, 64, 40, 9, 8), (600, 328, 200, 7, 4),
+                                       (1100, 136, 264, 7, 4)])
 def test_expert_products(dtype, T, H, I, E, k, path):
     kern = K()
     if path != "simt" and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernels are the bfloat16 path")
-    # the last case has some hundred rows an expert: the tile of 256 rows that compute-bound steps use
+    # the last three cases have some hundred rows an expert: tiles of 256 rows, taken by pairs of blocks (inner
+    # sizes that are no multiple of the 64-wide k block, feature counts that end inside a block's 128 or leave
+    # the pair's second block without any, experts of three tiles with a ragged last one)
     bm = kern.expert_tile_rows(T, T * k / E) if path == "tc" else kern.MOE_SIMT_BM
     assert path != "tc" or bm == (256 if T * k / E >= 96 else min(128, max(16, 1 << (T - 1).bit_length())))
     torch.manual_seed(3)
