@@ -162,6 +162,7 @@ constexpr float TCS_TAU = 8.0f;
 
 struct TcsShared {
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full, p_full, p_empty, fin;
+  uint64_t mx_full[4];      // the two warps of a lane quadrant have both written their maxima of a block
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -185,6 +186,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   __shared__ TcsShared sh;
   __shared__ int s_page[TC_MAX_PAGES];
   __shared__ float s_l[2][TC_BM];
+  __shared__ float s_mx[2][2][TC_BM];      // [block parity][half][row]
   volatile int* abort_flag = &sh.abort_flag;
 
   // blocks are handed out in the order of blockIdx.x: all kv heads of the first tile, then of the second, so the
@@ -231,6 +233,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     mbar_init(smem_u32(&sh.p_full), 256);
     mbar_init(smem_u32(&sh.p_empty), 1);
     mbar_init(smem_u32(&sh.fin), 256);
+    for (int q4 = 0; q4 < 4; ++q4) mbar_init(smem_u32(&sh.mx_full[q4]), 64);
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -351,35 +354,38 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       const int key0 = key_begin + j * TC_BN;
       const bool all_visible = key0 >= lo_r && key0 + TC_BN - 1 <= pos_r;
       const uint32_t s_addr = lane_addr + (uint32_t)(slot * TC_BN);
-      // pass 1: the row's maximum over all 128 keys of the block (three-operand max, 32 keys a load)
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // this thread's 64 keys of the block, read once and kept; the row's maximum over all 128 keys is the larger
+      // of this thread's and its partner's (the same lane of the warp four further on), handed over through
+      // shared memory and a barrier of the two warps
+      const int kbase = key0 + half * 64;
+      uint32_t va[32], vb[32];
       {
-        uint32_t va[32], vb[32];
-        auto take = [&](const uint32_t (&v)[32], int c) {
-          if (all_visible) {
+        const uint32_t mine = s_addr + (uint32_t)(half * 64);
+        tmem_ld32(mine, va);
+        tmem_ld32(mine + 32u, vb);
+        tmem_wait_ld();
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (all_visible) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2)
-              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-          } else {
+        for (int i = 0; i < 32; i += 2) {
+          mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+          mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+        }
+      } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + c * 32 + i;
-              if (key >= lo_r && key <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-            }
-          }
-        };
-        tmem_ld32(s_addr, va);
-#pragma unroll 1
-        for (int c = 0; c < TC_BN / 32; c += 2) {
-          tmem_wait_ld();
-          tmem_ld32(s_addr + (uint32_t)((c + 1) * 32), vb);
-          take(va, c);
-          tmem_wait_ld();
-          if (c + 2 < TC_BN / 32) tmem_ld32(s_addr + (uint32_t)((c + 2) * 32), va);
-          take(vb, c + 1);
+        for (int i = 0; i < 32; ++i) {
+          const int ka = kbase + i, kb = kbase + 32 + i;
+          if (ka >= lo_r && ka <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(va[i]));
+          if (kb >= lo_r && kb <= pos_r) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(vb[i]));
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      s_mx[j & 1][half][r] = mx_own;
+      mbar_arrive(smem_u32(&sh.mx_full[quad]));
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.mx_full[quad]), (uint32_t)j & 1u, abort_flag) ? 1 : 0);
+      if (!ok) break;
+      const float mx = fmaxf(mx_own, s_mx[j & 1][half ^ 1][r]) * scale_log2;
       m_true = fmaxf(m_true, mx);
       // raise the reference only when the maximum has grown a lot: O and the sum are rescaled then
       const bool raise = m_true > m_ref + TCS_TAU;          // also true while the reference is -inf and a key is visible
@@ -409,12 +415,10 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.p_empty), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
         if (!ok) break;
       }
-      // pass 2: the probabilities of this thread's 64 keys, as bfloat16 into its slab of P
+      // the probabilities of this thread's 64 keys, as bfloat16 into its slab of P
       float sum2[2] = {0.f, 0.f};
       {
-        const int kbase = key0 + half * 64;
         const bool vis = all_visible;
-        uint32_t va[32], vb[32];
         auto take = [&](const uint32_t (&v)[32], int c) {        // keys kbase + c*32 .. +31
           uint32_t pk[16];
           if (vis) {
@@ -447,10 +451,6 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                          "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
           }
         };
-        const uint32_t mine = s_addr + (uint32_t)(half * 64);
-        tmem_ld32(mine, va);
-        tmem_ld32(mine + 32u, vb);
-        tmem_wait_ld();
         take(va, 0);
         take(vb, 1);
       }
