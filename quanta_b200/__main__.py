@@ -104,8 +104,8 @@ def main(argv=None) -> int:
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     g.add_argument("--num-pages", type=int, default=None, help="pages in the cache pool")
-    g.add_argument("--max-step-tokens", type=int, default=2048, help="token budget of one step")
-    g.add_argument("--prefill-chunk", type=int, default=512, help="largest prompt portion")
+    g.add_argument("--max-step-tokens", type=int, default=4096, help="token budget of one step")
+    g.add_argument("--prefill-chunk", type=int, default=4096, help="largest prompt portion (chunk_tokens of the reference's chunked prefill)")
     g.add_argument("--max-requests", type=int, default=64, help="requests live at a time")
     g.add_argument("--stats", action="store_true", help="print run statistics to standard error")
     g.set_defaults(fn=_cmd_generate)

@@ -38,8 +38,8 @@ class LLM:
     """
 
     def __init__(self, model, *, dtype="bfloat16", device="cuda:0", page_size: int = 16,
-                 num_pages: int | None = None, max_requests: int = 64, max_step_tokens: int = 2048,
-                 prefill_chunk: int = 512, max_position: int | None = None):
+                 num_pages: int | None = None, max_requests: int = 64, max_step_tokens: int = 4096,
+                 prefill_chunk: int = 4096, max_position: int | None = None):
         if isinstance(model, (str, Path)):
             model, cfg = load_model(model, dtype=dtype, device=device)
             self.config = cfg

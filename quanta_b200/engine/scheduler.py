@@ -11,7 +11,10 @@ nothing else advances, src/quanta/shim/omlx.py:1449-1510; here prompts are cut s
    that cannot get pages even alone is finished with reason ``out_of_pages``.
 2. What is left of the step's token budget goes to prompt portions, in admission order: first the
    running requests that still have prompt to feed, then waiting requests while a state slot is free
-   and the pages of their next portion fit.  A portion is at most ``prefill_chunk`` tokens.
+   and the pages of their next portion fit.  A portion is at most ``prefill_chunk`` tokens (default 4,096,
+   the ``chunk_tokens`` of the reference's chunked prefill, src/quanta/minimax/runtime_m3.py:190-192; a
+   step of a model with routed experts reads every expert's weights whatever its size, so up to some
+   thousand tokens a larger portion costs no more time than a small one).
 3. After the step, a request whose last fed token was the newest one gets a token sampled from that
    position's logits.  It finishes on an eos id (not returned), on ``max_new_tokens`` (``length``) or
    at the position limit (``length``); its pages and slot are freed in the same pass.
@@ -75,7 +78,7 @@ class PlannedEntry:
 
 
 class Scheduler:
-    def __init__(self, manager: CacheManager, *, max_step_tokens: int = 2048, prefill_chunk: int = 512,
+    def __init__(self, manager: CacheManager, *, max_step_tokens: int = 4096, prefill_chunk: int = 4096,
                  max_position: int | None = None):
         if max_step_tokens <= 0 or prefill_chunk <= 0:
             raise ValueError("max_step_tokens and prefill_chunk must be positive")

@@ -455,7 +455,7 @@ def test_expert_products(dtype, T, H, I, E, k, path):
     # sizes that are no multiple of the 64-wide k block, feature counts that end inside a block's 128 or leave
     # the pair's second block without any, experts of three tiles with a ragged last one)
     bm = kern.expert_tile_rows(T, T * k / E) if path == "tc" else kern.MOE_SIMT_BM
-    assert path != "tc" or bm == (256 if T * k / E >= 96 else min(128, max(16, 1 << (T - 1).bit_length())))
+    assert path != "tc" or bm == (256 if T * k / E >= 112 else min(128, max(16, 1 << (T - 1).bit_length())))
     torch.manual_seed(3)
     x = torch.randn(T, H, device=DEV).to(dtype)
     # scaled so that outputs stay of order one at every size (the tolerance is absolute)
