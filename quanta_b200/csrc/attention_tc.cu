@@ -108,6 +108,13 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
+// the same with the A operand in TMEM (a row a lane, two bfloat16 a column, K along the columns)
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -148,20 +155,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // ------------------------------------------------------------------------------------------------
 // One query tile per block, O accumulated in TMEM, two softmax threads per row.
 //
-//   warp 0: TMA producer of K blocks, warp 1: of V blocks (two stages each), warp 2: MMA issuer,
-//   warps 3-10: softmax; warps 3-6 take keys 0..63 of a block, warps 7-10 keys 64..127, of the row that is
-//   their TMEM lane.  TMEM: two S buffers and ONE O of 128 columns that every P V adds to.
+//   warps 0-1: TMA producers of K blocks, warps 2-3: of V blocks (two stages each; a warp takes one 64-dim slab of
+//   every page, since an instruction that starts a copy holds its warp for some hundred cycles and a block of
+//   128 keys in pages of 16 is sixteen boxes), warp 4: MMA issuer,
+//   warps 5-12: softmax; warps 5-8 take keys 0..63 of a block, warps 9-12 keys 64..127, of the row that is
+//   their TMEM lane.  TMEM: two S buffers, ONE O of 128 columns that every P V adds to, and two P buffers
+//   of 64 columns (bfloat16 pairs): the probabilities never pass through shared memory, P V takes them as
+//   its TMEM operand, and the softmax of the next block runs while P V of this one does.
 //   The exponentials use a reference maximum that is only raised when the row maximum has grown by more
 //   than 2^8 since (then the row's O and sum are rescaled, each thread its 64 columns, after the P V
 //   before has finished); otherwise P V (j) needs nothing from the threads but P(j), and the threads
 //   never read O until the end.  Both threads of a row take the maximum over all 128 keys (the same
 //   decision without talking to each other) and the exponentials of their own 64.
 // ------------------------------------------------------------------------------------------------
-constexpr int TCS_THREADS = 11 * 32;
+constexpr int TCS_THREADS = 13 * 32;
 constexpr float TCS_TAU = 8.0f;
 
 struct TcsShared {
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full, p_full, p_empty, fin;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full, p_full[2], p_empty[2], fin;
   uint64_t mx_full[4];      // the two warps of a lane quadrant have both written their maxima of a block
   uint32_t tmem_base;
   int abort_flag;
@@ -182,7 +193,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                      float scale_log2, int window, int* status) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  const uint32_t q_s = smem_u32(base), p_s = q_s + TC_TILE_BYTES, k_s = p_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
+  const uint32_t q_s = smem_u32(base), k_s = q_s + TC_TILE_BYTES, v_s = k_s + 2 * TC_TILE_BYTES;
   __shared__ TcsShared sh;
   __shared__ int s_page[TC_MAX_PAGES];
   __shared__ float s_l[2][TC_BM];
@@ -215,7 +226,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   }
   asm volatile("cp.async.commit_group;\n" ::);
   for (uint32_t i = tid; i < 4 * TC_TILE_BYTES / 16; i += TCS_THREADS)
-    reinterpret_cast<uint4*>(base + 2 * TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
+    reinterpret_cast<uint4*>(base + TC_TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
   const int pi0 = key_begin / page_size;
   const int n_pi = key_end / page_size - pi0 + 1;
   const bool pages_in_smem = n_pi <= TC_MAX_PAGES;
@@ -223,21 +234,23 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     for (int i = tid; i < n_pi; i += TCS_THREADS) s_page[i] = bt[pi0 + i];
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&sh.k_full[s]), 1);
+      mbar_init(smem_u32(&sh.k_full[s]), 2);      // the two producer warps
       mbar_init(smem_u32(&sh.k_empty[s]), 1);
-      mbar_init(smem_u32(&sh.v_full[s]), 1);
+      mbar_init(smem_u32(&sh.v_full[s]), 2);
       mbar_init(smem_u32(&sh.v_empty[s]), 1);
       mbar_init(smem_u32(&sh.s_full[s]), 1);
     }
     mbar_init(smem_u32(&sh.o_full), 1);
-    mbar_init(smem_u32(&sh.p_full), 256);
-    mbar_init(smem_u32(&sh.p_empty), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh.p_full[b]), 256);
+      mbar_init(smem_u32(&sh.p_empty[b]), 1);
+    }
     mbar_init(smem_u32(&sh.fin), 256);
     for (int q4 = 0; q4 < 4; ++q4) mbar_init(smem_u32(&sh.mx_full[q4]), 64);
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 2) {      // two S buffers and O: 384 columns, allocated as 512
+  if (warp == 4) {      // two S buffers and O: 384 columns, allocated as 512
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(&sh.tmem_base)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -248,14 +261,17 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = sh.tmem_base;
-  const uint32_t o_col = 2 * TC_BN;
+  const uint32_t o_col = 2 * TC_BN;                 // S(0), S(1), O, then
+  const uint32_t p_col = 2 * TC_BN + TC_HD;         // P(0), P(1): 64 columns each
 
-  if (warp < 2) {
-    // ---------------- TMA producers: warp 0 streams K blocks, warp 1 V blocks ----------------
-    const CUtensorMap* map = warp == 0 ? &tm_k : &tm_v;
-    uint64_t* full = warp == 0 ? sh.k_full : sh.v_full;
-    uint64_t* empty = warp == 0 ? sh.k_empty : sh.v_empty;
-    const uint32_t ring = warp == 0 ? k_s : v_s;
+  if (warp < 4) {
+    // ---------------- TMA producers: warps 0-1 stream K blocks, warps 2-3 V blocks, each one slab ----------------
+    const bool is_k = warp < 2;
+    const int slab = warp & 1;
+    const CUtensorMap* map = is_k ? &tm_k : &tm_v;
+    uint64_t* full = is_k ? sh.k_full : sh.v_full;
+    uint64_t* empty = is_k ? sh.k_empty : sh.v_empty;
+    const uint32_t ring = is_k ? k_s : v_s;
     const int box_rows = min(page_size, TC_BN);
     bool ok = true;
     for (int b = 0; b < n_blocks && ok; ++b) {
@@ -265,11 +281,11 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       if (!ok) break;
       const int key0 = key_begin + b * TC_BN;
       const int n_keys = min(TC_BN, key_end - key0 + 1);
-      const int n_req = 2 * ((n_keys + box_rows - 1) / box_rows);      // boxes: pages with visible keys x two slabs
+      const int n_req = (n_keys + box_rows - 1) / box_rows;      // boxes of this warp: the pages with visible keys
       const uint32_t bar = smem_u32(&full[slot]);
       int skipped = 0;
       for (int i = lane; i < n_req; i += 32) {
-        const int key = key0 + (i >> 1) * box_rows;
+        const int key = key0 + i * box_rows;
         if (key + box_rows - 1 < lo_min) { ++skipped; continue; }
         const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
         if (pg < 0 || pg >= num_pages) { qb_set_status(status, QB_STATUS_BAD_PAGE, pg, 7); ++skipped; }
@@ -277,8 +293,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       skipped = __reduce_add_sync(0xffffffffu, skipped);
       if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_req - skipped) * (uint32_t)box_rows * 128u);
       __syncwarp();
-      for (int i = lane; i < n_req; i += 32) {
-        const int slab = i & 1, box = i >> 1;
+      for (int box = lane; box < n_req; box += 32) {
         const int key = key0 + box * box_rows;
         if (key + box_rows - 1 < lo_min) continue;
         const int pg = pages_in_smem ? s_page[key / page_size - pi0] : bt[key / page_size];
@@ -291,7 +306,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       const uint64_t t0 = global_ns();
       while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
-  } else if (warp == 2) {
+  } else if (warp == 4) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc_qk = umma_idesc(TC_BM, TC_BN, false), idesc_pv = umma_idesc(TC_BM, TC_HD, true);
@@ -315,27 +330,28 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       if (ok && n_blocks > 1) issue_qk(1);
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int slot = j & 1;
-        ok = mbar_wait(smem_u32(&sh.p_full), (uint32_t)j & 1u, abort_flag);      // P(j) written, S(j) read, O rescaled if need be
+        ok = mbar_wait(smem_u32(&sh.p_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag);      // P(j) written, S(j) read, O rescaled if need be
         if (!ok) break;
         ok = mbar_wait(smem_u32(&sh.v_full[slot]), (uint32_t)(j >> 1) & 1u, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t vt = v_s + slot * TC_TILE_BYTES;
+        const uint32_t pt = tmem_base + p_col + (uint32_t)(slot * (TC_BN / 2));
 #pragma unroll
         for (int k16 = 0; k16 < TC_BN / 16; ++k16) {
-          const uint32_t a_off = (k16 >> 2) * TC_SLAB_BYTES + (k16 & 3) * 32;
-          umma_bf16(tmem_base + o_col, umma_desc(p_s + a_off, 0), umma_desc(vt + k16 * 2048, TC_SLAB_BYTES), idesc_pv,
-                    (j | k16) != 0 ? 1u : 0u);
+          // 16 keys further: 8 columns of P, 16 rows of V
+          umma_bf16_ta(tmem_base + o_col, pt + (uint32_t)(k16 * 8), umma_desc(vt + k16 * 2048, TC_SLAB_BYTES), idesc_pv,
+                       (j | k16) != 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&sh.v_empty[slot]));
-        umma_commit(smem_u32(&sh.p_empty));
+        umma_commit(smem_u32(&sh.p_empty[slot]));
         umma_commit(smem_u32(&sh.o_full));
         if (j + 2 < n_blocks) issue_qk(j + 2);
       }
     }
   } else {
     // ---------------- softmax: two threads a row, 64 keys of a block each ----------------
-    const int quad = warp & 3, half = (warp - 3) >> 2;
+    const int quad = warp & 3, half = (warp - 5) >> 2;
     const int r = quad * 32 + lane;
     const int R = row0 + r;
     const bool valid = r < n_rows;
@@ -343,7 +359,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const int lo_r = (window > 0 && pos_r - window + 1 > 0) ? pos_r - window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t o_addr = lane_addr + o_col + (uint32_t)(half * 64);       // this thread's 64 columns of O
-    const uint32_t p_row = p_s + half * TC_SLAB_BYTES + r * 128;             // its 64 keys are one slab of P
+    const uint32_t p_addr = lane_addr + p_col + (uint32_t)(half * 32);       // its 64 keys: 32 columns of a P buffer
     float m_true = -INFINITY, m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks; ++j) {
@@ -410,12 +426,12 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       }
       if (raise) m_ref = m_true;
       const float msafe = m_ref == -INFINITY ? 0.f : m_ref;
-      // P's tile is free once the P V of the block before has read it
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.p_empty), (uint32_t)(j - 1) & 1u, abort_flag) ? 1 : 0);
+      // the P buffer of this block is free once the P V of the block before the last has read it
+      if (j > 1) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&sh.p_empty[slot]), (uint32_t)((j >> 1) - 1) & 1u, abort_flag) ? 1 : 0);
         if (!ok) break;
       }
-      // the probabilities of this thread's 64 keys, as bfloat16 into its slab of P
+      // the probabilities of this thread's 64 keys, as bfloat16 pairs into its columns of P
       float sum2[2] = {0.f, 0.f};
       {
         const bool vis = all_visible;
@@ -443,21 +459,15 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               pk[i >> 1] = pack_bf16(p0, p1);
             }
           }
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const int chunk = c * 4 + h;
-            const uint32_t dst = p_row + ((chunk ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[h * 4]), "r"(pk[h * 4 + 1]),
-                         "r"(pk[h * 4 + 2]), "r"(pk[h * 4 + 3]) : "memory");
-          }
+          tmem_st16(p_addr + (uint32_t)(slot * (TC_BN / 2) + c * 16), pk);
         };
         take(va, 0);
         take(vb, 1);
       }
       l += sum2[0] + sum2[1];
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, before the MMA reads it
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");      // P, before the MMA reads it
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(&sh.p_full));
+      mbar_arrive(smem_u32(&sh.p_full[slot]));
     }
     if (ok) {
       // the end: both halves' sums, then each thread its 64 columns of O
@@ -492,7 +502,7 @@ attn_span_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 2) {
+  if (warp == 4) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
   if (tid == 0 && sh.abort_flag) qb_set_status(status, QB_STATUS_WAIT_TIMEOUT, blockIdx.x / nkv, 7);
@@ -560,7 +570,7 @@ extern "C" int qb_attn_span_tc(const void* q, const void* k_cache, const void* v
   int rc = make_kv_map(&tm_k, k_cache, rows, box_rows);
   if (rc == 0) rc = make_kv_map(&tm_v, v_cache, rows, box_rows);
   if (rc) return rc;
-  const size_t smem = 6 * (size_t)TC_TILE_BYTES + 1024;
+  const size_t smem = 5 * (size_t)TC_TILE_BYTES + 1024;      // Q and two stages each of K and V
   cudaError_t err = cudaFuncSetAttribute(attn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) return (int)err;
   attn_span_tc_kernel<<<dim3((unsigned)n_tiles * (unsigned)nkv), TCS_THREADS, smem, stream>>>(
