@@ -209,8 +209,21 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, i
   const int lo = part * chunk, hi = min(V, lo + chunk);
   const float* row = logits + (size_t)r * V;
   float bv = -INFINITY; int bi = -1;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x)
-    if (bi < 0 || row[i] > bv) { bv = row[i]; bi = i; }
+  // eight loads in flight a thread (the chunk is a few thousand logits: its time is the loads' latency), taken in
+  // index order so that the first maximum wins
+  for (int i0 = lo + threadIdx.x; i0 < hi; i0 += 8 * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      v[u] = i < hi ? __ldg(row + i) : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < hi && (bi < 0 || v[u] > bv)) { bv = v[u]; bi = i; }
+    }
+  }
   const ArgBest b = block_argmax(bv, bi, sv, si);
   if (threadIdx.x == 0) { pv[r * parts + part] = b.v; pi[r * parts + part] = b.i; }
 }
